@@ -1,0 +1,175 @@
+/*
+ * lux_cuda_quant.h -- C ABI of libluxgpu_backend_cuda.so beyond the base vtable.
+ *
+ * The plugin is a drop-in backend for the Lux GPU core: it exports
+ * `lux_gpu_backend_init` (include/lux/gpu/backend_plugin.h:423-445) and fills
+ * the unchanged 64-slot `lux_gpu_backend_vtbl` (backend_plugin.h:82-382),
+ * ABI version 2 (backend_plugin.h:24).  The base vtable has no slot for a
+ * quantized matmul, so the entry points of that path are published, without
+ * touching the header, in three additive ways:
+ *
+ *   (i)   `vtbl->_reserved[0]` (backend_plugin.h:379-380, "reserved for future
+ *         expansion") holds a `const lux_gpu_quant_vtbl*`; other backends leave
+ *         it NULL, and cores that do not know it never read it;
+ *   (ii)  the exported getter `lux_gpu_cuda_quant_vtbl()` returns the same table
+ *         (for `dlsym`);
+ *   (iii) `kernel_load(ctx, NULL, "lux.qmm.affine")` + `kernel_dispatch` with
+ *         the buffer list {x, wq, scales, biases, y, params} reaches the same
+ *         code through the existing custom-kernel slots
+ *         (backend_plugin.h:103-114); `params` is a `lux_qmm_params` buffer.
+ *
+ * Every function mirrors the argument shape of the nearest base op,
+ * `op_matmul_f32(ctx, a, b, out, M, K, N)` (backend_plugin.h:129; CPU
+ * implementation src/cpu_backend.cpp:243-266): context first, input buffers,
+ * output buffer, then dimensions.  All work is enqueued on the context's
+ * stream; `sync` / `buffer_copy_to_host` of the base vtable order after it.
+ * Errors are `LuxBackendError` values (backend_plugin.h:49-56); nothing throws
+ * or aborts across this boundary and there is no CPU fallback: on a machine
+ * without a usable GPU `lux_gpu_backend_init` returns false.
+ *
+ * Packed format (w^ = scale*q + bias per group along K):
+ *   wq      uint32[N][K*bits/32], LSB-first along K
+ *             4-bit: q[n][k] = (wq[n][k>>3] >> (4*(k&7))) & 0xF
+ *             8-bit: q[n][k] = (wq[n][k>>2] >> (8*(k&3))) & 0xFF
+ *   scales, biases  [N][K/group]  (fp32 or bf16), group in {32, 64, 128}
+ *   y[m][n] = sum_k x[m][k] * w^[n][k]
+ * Supported dtype combinations (x, scales/biases) -> w^ precision:
+ *   (F32, F32|BF16): w^ = fl32(fl32(s*q)+b), fp32 math, fp32 accumulate
+ *   (BF16, BF16)   : w^ = RNE_bf16(exact s*q+b) (one bf16 FMA), fp32 accumulate
+ *   y may be F32 or BF16 (RNE of the fp32 sum).  (BF16, F32) is NOT_SUPPORTED.
+ */
+#ifndef LUX_CUDA_QUANT_H
+#define LUX_CUDA_QUANT_H
+
+#include "lux/gpu/backend_plugin.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LUX_CUDA_QUANT_MAGIC 0x4C515854u /* "LQXT" */
+#define LUX_CUDA_QUANT_VERSION 1u
+#define LUX_CUDA_QMM_KERNEL_NAME "lux.qmm.affine"
+#define LUX_CUDA_NCCL_UID_BYTES 128
+
+/* parameter block of the kernel_dispatch route (iii); 32 bytes */
+typedef struct lux_qmm_params {
+    int32_t M, K, N, bits, group, x_dtype, sb_dtype, y_dtype;
+} lux_qmm_params;
+
+/* One rank of a column-sharded layer (see shard_* below). */
+typedef struct LuxCudaShardComm LuxCudaShardComm;
+
+typedef struct lux_gpu_quant_vtbl {
+    uint32_t magic;   /* LUX_CUDA_QUANT_MAGIC */
+    uint32_t version; /* LUX_CUDA_QUANT_VERSION */
+    uint32_t size;    /* sizeof(lux_gpu_quant_vtbl) of the library that filled it */
+    uint32_t _pad;
+
+    /* y[M,N] = x[M,K] . dequant(wq[N,K])^T.  M <= 16 runs the decode GEMV
+     * kernels, larger M the tcgen05 GEMM.  Replaces (for quantized weights)
+     * op_matmul_f32, backend_plugin.h:129 / src/cpu_backend.cpp:243-266. */
+    LuxBackendError (*qmatmul)(LuxBackendContext* ctx, LuxBackendBuffer* x, LuxBackendBuffer* wq,
+                               LuxBackendBuffer* scales, LuxBackendBuffer* biases, LuxBackendBuffer* y,
+                               int M, int K, int N, int bits, int group,
+                               LuxBackendDtype x_dtype, LuxBackendDtype sb_dtype, LuxBackendDtype y_dtype);
+
+    /* out[N,K] = dequant(wq): F32 (two-rounding rule) or BF16 (single-rounding
+     * rule).  Exists so the dequantised weights can be checked bit for bit.
+     * No counterpart in the reference (it has no quantized format). */
+    LuxBackendError (*dequantize)(LuxBackendContext* ctx, LuxBackendBuffer* wq, LuxBackendBuffer* scales,
+                                  LuxBackendBuffer* biases, LuxBackendBuffer* out, int N, int K, int bits,
+                                  int group, LuxBackendDtype sb_dtype, LuxBackendDtype out_dtype);
+
+    /* q[N,K] (one byte per element) = unpack(wq).  Bit-exact check of the packing. */
+    LuxBackendError (*unpack)(LuxBackendContext* ctx, LuxBackendBuffer* wq, LuxBackendBuffer* q_out,
+                              int N, int K, int bits);
+
+    /* Affine min/max quantiser, the producer of the format: w fp32 [N,K] ->
+     * (wq, scales, biases).  No counterpart in the reference. */
+    LuxBackendError (*quantize)(LuxBackendContext* ctx, LuxBackendBuffer* w, LuxBackendBuffer* wq,
+                                LuxBackendBuffer* scales, LuxBackendBuffer* biases, int N, int K, int bits,
+                                int group, LuxBackendDtype sb_dtype);
+
+    /* Row-wise rms-norm with unit or given weight, fp32 math, in/out dtype
+     * F32 or BF16.  Formula of op_rms_norm_f32 (backend_plugin.h:178;
+     * kernels/cpu/tensor_ops.c:546-566). weight may be NULL. */
+    LuxBackendError (*rms_norm)(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out,
+                                LuxBackendBuffer* weight, size_t rows, size_t dim, float eps,
+                                LuxBackendDtype in_dtype, LuxBackendDtype out_dtype);
+
+    /* --- buffer interop ---------------------------------------------------- */
+    /* Device address of a buffer (valid until buffer_free). */
+    void* (*buffer_device_ptr)(LuxBackendContext* ctx, LuxBackendBuffer* buf);
+    /* Size in bytes the buffer was allocated with. */
+    size_t (*buffer_size)(LuxBackendContext* ctx, LuxBackendBuffer* buf);
+    /* Non-owning buffer around device memory that someone else allocated on the
+     * context's device (buffer_free releases only the handle). */
+    LuxBackendBuffer* (*buffer_wrap)(LuxBackendContext* ctx, void* device_ptr, size_t bytes);
+    /* Stream-ordered host->device copy that does NOT wait: `src` must be pinned
+     * and stay untouched until the next sync.  buffer_copy_from_host of the
+     * base vtable keeps the reference's blocking semantics
+     * (src/cpu_backend.cpp:155-160). */
+    LuxBackendError (*buffer_copy_from_host_async)(LuxBackendContext* ctx, LuxBackendBuffer* buf,
+                                                   const void* src, size_t bytes);
+    /* Pinned host memory for the two copies above. */
+    void* (*host_alloc_pinned)(size_t bytes);
+    void (*host_free_pinned)(void* p);
+    /* The context's CUDA stream (a cudaStream_t), for callers that enqueue their own work. */
+    void* (*context_stream)(LuxBackendContext* ctx);
+    /* Allocator statistics of the context's device: bytes held from the
+     * driver, bytes handed out, number of driver allocations so far. */
+    LuxBackendError (*allocator_stats)(LuxBackendContext* ctx, uint64_t* reserved, uint64_t* in_use,
+                                       uint64_t* driver_allocs);
+    /* Return cached, unused device memory to the driver. */
+    LuxBackendError (*allocator_trim)(LuxBackendContext* ctx);
+
+    /* --- device-side timing (CUDA events on the context's stream) ----------- */
+    /* slot 0..15; elapsed_ms synchronises on the stop event. */
+    LuxBackendError (*timer_record)(LuxBackendContext* ctx, int slot);
+    LuxBackendError (*timer_elapsed_ms)(LuxBackendContext* ctx, int start_slot, int stop_slot, float* ms);
+    /* Write `bytes` (> L2) of the context's flush buffer so the next kernel
+     * starts with a cold L2. */
+    LuxBackendError (*flush_l2)(LuxBackendContext* ctx);
+    /* Name of the kernel the last qmatmul on this context launched, number of
+     * kernels launched by the plugin on this context so far. */
+    const char* (*last_kernel)(LuxBackendContext* ctx);
+    uint64_t (*launch_count)(LuxBackendContext* ctx);
+
+    /* --- column-sharded layers: rank r owns columns [r*Nl, (r+1)*Nl) -------- */
+    /* rank 0 obtains an id and hands it to the others (any host channel). */
+    LuxBackendError (*shard_unique_id)(void* out_uid /* LUX_CUDA_NCCL_UID_BYTES */);
+    /* one process per GPU */
+    LuxBackendError (*shard_comm_create)(LuxBackendContext* ctx, int rank, int world, const void* uid,
+                                         LuxCudaShardComm** out);
+    /* one process driving `world` contexts */
+    LuxBackendError (*shard_comm_create_all)(LuxBackendContext** ctxs, int world, LuxCudaShardComm** out);
+    void (*shard_comm_destroy)(LuxCudaShardComm* comm);
+    /* y_full[M, world*Nl] on every rank: local slice = x . dequant(wq_local)^T,
+     * then all-gather of the slices (NCCL over NVLink) and the column
+     * interleave.  `staging` holds world*M*Nl elements of y_dtype.
+     * In the single-process form call it once per rank between
+     * shard_group_begin / shard_group_end. */
+    LuxBackendError (*qmatmul_sharded)(LuxCudaShardComm* comm, LuxBackendBuffer* x, LuxBackendBuffer* wq_local,
+                                       LuxBackendBuffer* scales_local, LuxBackendBuffer* biases_local,
+                                       LuxBackendBuffer* y_full, LuxBackendBuffer* staging,
+                                       int M, int K, int N_local, int bits, int group,
+                                       LuxBackendDtype x_dtype, LuxBackendDtype sb_dtype, LuxBackendDtype y_dtype);
+    LuxBackendError (*shard_group_begin)(void);
+    LuxBackendError (*shard_group_end)(void);
+} lux_gpu_quant_vtbl;
+
+/* Entry points exported with default visibility. */
+LUX_GPU_BACKEND_EXPORT bool lux_gpu_backend_init(lux_gpu_backend_desc* out); /* backend_plugin.h:423 */
+LUX_GPU_BACKEND_EXPORT const lux_gpu_quant_vtbl* lux_gpu_cuda_quant_vtbl(void);
+/* Layout facts of the ABI the library was compiled against, for bindings that
+ * mirror the struct by hand: sizeof(vtbl), offsetof(op_matmul_f32),
+ * offsetof(op_ntt_forward), offsetof(_reserved), sizeof(desc). */
+LUX_GPU_BACKEND_EXPORT void lux_gpu_cuda_abi_layout(uint32_t out[5]);
+/* Last error text of the calling thread ("" if none). */
+LUX_GPU_BACKEND_EXPORT const char* lux_gpu_cuda_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUX_CUDA_QUANT_H */

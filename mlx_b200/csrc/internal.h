@@ -1,0 +1,188 @@
+// Internal types of the CUDA backend plugin: per-device state (caching
+// allocator, stream pool), contexts, buffers, and the launch interfaces of the
+// kernels.  Nothing here crosses the C ABI.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "lux_cuda_quant.h"
+
+namespace luxcuda {
+
+// ---------------------------------------------------------------------------
+// error plumbing: CUDA errors never escape as exceptions; they become a
+// LuxBackendError and a thread-local message.
+// ---------------------------------------------------------------------------
+void set_last_error(const char* fmt, ...);
+const char* last_error();
+LuxBackendError map_cuda_error(cudaError_t e, const char* what);
+
+#define LUX_CUDA_TRY(expr)                                                        \
+    do {                                                                          \
+        cudaError_t _e = (expr);                                                  \
+        if (_e != cudaSuccess) return ::luxcuda::map_cuda_error(_e, #expr);       \
+    } while (0)
+
+// ---------------------------------------------------------------------------
+// Per-device state.  Shared (ref-counted) by every context and every buffer of
+// that device, so a buffer outlives the context that allocated it: the core
+// frees tensors after it has destroyed their context (src/gpu_core.cpp:216-233).
+// ---------------------------------------------------------------------------
+struct Block {
+    void* ptr = nullptr;
+    size_t size = 0;
+    cudaStream_t last_stream = nullptr;  // stream the block was last used on
+    cudaEvent_t idle = nullptr;          // recorded on last_stream when the block was freed
+    bool has_event = false;
+};
+
+class DeviceState {
+public:
+    explicit DeviceState(int device);
+    ~DeviceState();
+    DeviceState(const DeviceState&) = delete;
+
+    int device() const { return device_; }
+
+    // Caching allocator.  Sizes are rounded to 512 B below 1 MiB and to 2 MiB
+    // above; a freed block is kept and handed to the next request of a fitting
+    // size (at most 25 % slack for large blocks).  Reuse on another stream
+    // first waits for the event recorded at free time.
+    Block* acquire(size_t bytes, cudaStream_t stream, cudaError_t* err);
+    void release(Block* b, cudaStream_t stream);
+    void trim();
+    void stats(uint64_t* reserved, uint64_t* in_use, uint64_t* driver_allocs);
+
+    cudaStream_t acquire_stream();
+    void release_stream(cudaStream_t s);
+
+    // L2 flush buffer (lazy, 256 MiB)
+    void* flush_buffer(size_t* bytes, cudaError_t* err);
+
+    int sm_count = 0;
+    size_t l2_bytes = 0;
+    size_t smem_optin = 0;
+    cudaDeviceProp prop{};
+
+private:
+    static size_t round_size(size_t bytes);
+    int device_;
+    std::mutex mu_;
+    std::multimap<size_t, Block*> free_;
+    std::vector<cudaStream_t> stream_pool_;
+    std::vector<cudaStream_t> all_streams_;
+    uint64_t reserved_ = 0, in_use_ = 0, driver_allocs_ = 0;
+    void* flush_ = nullptr;
+    size_t flush_bytes_ = 0;
+};
+
+std::shared_ptr<DeviceState> device_state(int device, cudaError_t* err);
+
+constexpr uint32_t kCtxMagic = 0x4C435458u;  // "LCTX"
+constexpr uint32_t kBufMagic = 0x4C425546u;  // "LBUF"
+constexpr uint32_t kKernMagic = 0x4C4B524Eu; // "LKRN"
+constexpr int kTimerSlots = 16;
+
+struct Context {
+    uint32_t magic = kCtxMagic;
+    std::shared_ptr<DeviceState> dev;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t timers[kTimerSlots] = {};
+    // split-K workspace of the decode GEMV (partials + arrival counters), grown on demand
+    Block* qmv_ws = nullptr;
+    size_t qmv_ws_bytes = 0;
+    const char* last_kernel = "";
+    std::atomic<uint64_t> launches{0};
+    std::mutex mu;  // one thread at a time per context
+};
+
+struct Buffer {
+    uint32_t magic = kBufMagic;
+    std::shared_ptr<DeviceState> dev;
+    Block* block = nullptr;  // null for wrapped (non-owning) buffers
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    cudaStream_t last_stream = nullptr;
+};
+
+struct Kernel {
+    uint32_t magic = kKernMagic;
+    int builtin_id = 0;  // 1 = lux.qmm.affine
+};
+
+inline Context* as_ctx(LuxBackendContext* c) {
+    auto* p = reinterpret_cast<Context*>(c);
+    return (p && p->magic == kCtxMagic) ? p : nullptr;
+}
+inline Buffer* as_buf(LuxBackendBuffer* b) {
+    auto* p = reinterpret_cast<Buffer*>(b);
+    return (p && p->magic == kBufMagic) ? p : nullptr;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+        if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        int cur = -1;
+        if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+    }
+};
+
+// ---------------------------------------------------------------------------
+// kernel launchers (each enqueues on `stream`, returns the launch status)
+// ---------------------------------------------------------------------------
+struct QmmArgs {
+    const void* x;
+    const uint32_t* wq;
+    const void* scales;
+    const void* biases;
+    void* y;
+    int M, K, N, bits, group;
+    int x_dtype, sb_dtype, y_dtype;  // LuxBackendDtype values
+};
+
+// decode GEMV, bf16 activations: mma.sync m16n8k16 with in-register dequant
+bool qmv_mma_supported(const QmmArgs& a);
+size_t qmv_mma_workspace_bytes(const QmmArgs& a, int sm_count);
+cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name);
+// decode / small-M, any supported dtype combination: CUDA cores + warp shuffles
+cudaError_t launch_qmv_simt(const QmmArgs& a, cudaStream_t stream, const char** name);
+// prefill GEMM, bf16 activations: TMA + tcgen05 + TMEM
+bool qmm_tc_supported(const QmmArgs& a);
+cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, const char** name);
+
+cudaError_t launch_dequantize(const uint32_t* wq, const void* scales, const void* biases, void* out, int N, int K,
+                              int bits, int group, int sb_dtype, int out_dtype, cudaStream_t stream);
+cudaError_t launch_unpack(const uint32_t* wq, uint8_t* q, int N, int K, int bits, cudaStream_t stream);
+cudaError_t launch_quantize(const float* w, uint32_t* wq, void* scales, void* biases, int N, int K, int bits,
+                            int group, int sb_dtype, cudaStream_t stream);
+cudaError_t launch_rms_norm(const void* in, void* out, const float* weight, size_t rows, size_t dim, float eps,
+                            int in_dtype, int out_dtype, cudaStream_t stream);
+cudaError_t launch_gather_columns(const void* staging, void* y_full, int world, int M, int n_local, int elem_size,
+                                  cudaStream_t stream);
+cudaError_t launch_flush(void* buf, size_t bytes, cudaStream_t stream);
+
+enum class BinOp { Add, Sub, Mul, Div };
+cudaError_t launch_binary_f32(BinOp op, const float* a, const float* b, float* out, size_t n, cudaStream_t stream);
+cudaError_t launch_matmul_f32(const float* a, const float* b, float* out, int M, int K, int N, cudaStream_t stream);
+cudaError_t ntt_device(uint64_t* host_data, size_t n, uint64_t modulus, bool inverse, cudaStream_t stream);
+
+// extension table (quant_api.cu) and sharding (shard.cu)
+const lux_gpu_quant_vtbl* quant_vtbl();
+LuxBackendError qmatmul_on_stream(Context* c, const QmmArgs& a);
+void fill_shard_entries(lux_gpu_quant_vtbl* t);
+
+}  // namespace luxcuda

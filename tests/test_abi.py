@@ -1,0 +1,99 @@
+"""The C-ABI shared library loads without a GPU, exports every symbol that
+include/*.h declares, and its descriptor / table layout match the plugin ABI
+(include/lux/gpu/backend_plugin.h:82-394).  No compute calls here."""
+import ctypes as C
+import glob
+import os
+import re
+import subprocess
+
+import pytest
+
+import mlx_b200
+from mlx_b200 import plugin as P
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = set()
+    for h in glob.glob(os.path.join(ROOT, "include", "*.h")):
+        text = open(h).read()
+        names.update(re.findall(r"LUX_GPU_BACKEND_EXPORT\s+[\w\s\*]+?\b(\w+)\s*\(", text))
+    return names
+
+
+def test_library_exports_every_declared_symbol():
+    decl = declared_symbols()
+    assert set(P.EXPORTED_SYMBOLS) <= decl and len(decl) >= 4
+    lib = P.load_library()
+    for name in decl:
+        assert getattr(lib, name) is not None, name
+    out = subprocess.run(["nm", "-D", "--defined-only", P.LIB_PATH], capture_output=True, text=True).stdout
+    exported = {l.split()[-1] for l in out.splitlines() if " T " in l}
+    assert decl <= exported
+    # nothing else of ours leaks (hidden visibility): only the declared entry points are global text symbols
+    assert {s for s in exported if s.startswith("lux")} == decl
+
+
+def test_descriptor_and_layout():
+    p = mlx_b200.Plugin(require_gpu=False)
+    assert p.desc.abi_version == 2
+    assert p.desc.backend_name == b"cuda"  # registry key of the core's loader (src/plugin_loader.hpp:227-230)
+    assert p.desc.capabilities & 0x3 == 0x3  # TENSOR_OPS | MATMUL
+    sizeof_vtbl, off_matmul, off_ntt, off_reserved, sizeof_desc = p.abi_layout()
+    assert sizeof_vtbl == C.sizeof(P.BackendVtbl) == 512
+    assert off_matmul == P.BackendVtbl.op_matmul_f32.offset
+    assert off_ntt == P.BackendVtbl.op_ntt_forward.offset
+    assert off_reserved == P.BackendVtbl._reserved.offset == 480
+    assert sizeof_desc == C.sizeof(P.BackendDesc) == 40
+    v = p.vtbl
+    for name in ("create_context", "destroy_context", "get_device_count", "get_device_info", "sync", "buffer_alloc",
+                 "buffer_alloc_with_data", "buffer_free", "buffer_copy_to_host", "buffer_copy_from_host",
+                 "kernel_load", "kernel_dispatch", "op_add_f32", "op_sub_f32", "op_mul_f32", "op_matmul_f32",
+                 "op_ntt_forward", "op_ntt_inverse"):
+        assert C.cast(getattr(v, name), C.c_void_p).value, name
+    for name in ("op_msm", "op_kzg_verify", "op_blake3_hash"):  # unsupported = NULL slot
+        assert not getattr(v, name)
+    assert not v._reserved[1] and not v._reserved[2] and not v._reserved[3]
+
+
+def test_quant_table():
+    p = mlx_b200.Plugin(require_gpu=False)
+    q = p.quant
+    assert q.magic == P.QUANT_MAGIC and q.version == 1 and q.size == C.sizeof(P.QuantVtbl)
+    getter = p.lib.lux_gpu_cuda_quant_vtbl()
+    assert C.addressof(getter.contents) == p.vtbl._reserved[0]
+    for name, _ in P.QuantVtbl._fields_[4:]:
+        assert C.cast(getattr(q, name), C.c_void_p).value, name
+
+
+def test_null_arguments_are_errors_not_crashes():
+    p = mlx_b200.Plugin(require_gpu=False)
+    v, q = p.vtbl, p.quant
+    assert v.sync(None) == P.ERR_INVALID
+    assert v.get_device_count(None) == P.ERR_INVALID
+    assert v.buffer_alloc(None, 16) is None
+    assert v.buffer_copy_to_host(None, None, None, 0) == P.ERR_INVALID
+    assert v.op_add_f32(None, None, None, None, 4) == P.ERR_INVALID
+    assert v.op_matmul_f32(None, None, None, None, 1, 1, 1) == P.ERR_INVALID
+    assert q.qmatmul(None, None, None, None, None, None, 1, 64, 1, 4, 64, 0, 0, 0) == P.ERR_INVALID
+    assert q.dequantize(None, None, None, None, None, 1, 64, 4, 64, 0, 0) == P.ERR_INVALID
+    v.buffer_free(None, None)
+    v.destroy_context(None)
+
+
+def test_no_gpu_means_unavailable_not_fallback():
+    import torch
+    p = mlx_b200.Plugin(require_gpu=False)
+    if torch.cuda.is_available():
+        pytest.skip("GPU present")
+    assert not p.available
+    with pytest.raises(RuntimeError):
+        mlx_b200.Plugin(require_gpu=True)
+
+
+def test_product_does_not_touch_the_oracle():
+    for path in glob.glob(os.path.join(ROOT, "mlx_b200", "**", "*"), recursive=True):
+        if os.path.isfile(path) and path.endswith((".py", ".cu", ".h", ".cpp")):
+            assert "oracle" not in open(path, errors="ignore").read().lower(), path
