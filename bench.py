@@ -1,0 +1,377 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul hot path on B200, through the plugin's C ABI.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload at N = 1 (BASELINE.json configs[1], the one the metric is quoted on):
+the decode GEMV sweep  x bf16 [M in {1,4,8,16}, K=4096] . W^T,  W [N=11008,
+K=4096] 4-bit affine, group 64, bf16 scales/biases, fp32 accumulate, bf16 out.
+A "step" is REPS passes over the sweep; every launch reads a different one of
+R resident weight sets (R * 25.4 MB = 305 MB > 2 x L2), so each launch streams
+its weights from HBM, never from L2.  value = algorithmic bytes of all
+launches / device time (CUDA events on the launching stream), GB/s.
+
+At N > 1 (torchrun, one process per GPU) the layer is column-sharded: every
+rank holds its own 11008-column slice (weak scaling: the logical layer has
+N * 11008 columns), computes it, and the slices are all-gathered over NVLink
+after every launch (qmatmul_sharded).  Time = max over ranks.
+
+`e2e` is the same metric through the reference-facing calls with HOST buffers:
+buffer_copy_from_host(x) -> qmatmul -> buffer_copy_to_host(y) per launch.
+`--impl reference` times the CPU implementation of the path (the oracle, in
+the reference CPU backend's loop style, all host threads) on a bounded sample.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "4-bit qmatmul: decode GEMV HBM GB/s; prefill GEMM TFLOPS; % of roofline"
+K_DEC, N_DEC, BITS, GROUP = 4096, 11008, 4, 64
+M_SWEEP = (1, 4, 8, 16)
+R_SETS = 12
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d, "measured"
+    return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def alg_bytes(M, K=K_DEC, N=N_DEC):
+    # every operand exactly once: packed weights + scales + biases + x + y  (bf16 = 2 B)
+    return N * K * BITS // 8 + 2 * (N * K // GROUP) * 2 + M * K * 2 + M * N * 2
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.thread.join(timeout=5)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------
+# CPU baseline (the oracle; test infrastructure used here only as the baseline)
+# ---------------------------------------------------------------------------
+def cpu_baseline(budget_s=12.0):
+    import oracle as O
+    wq, s, b = O.make_layer(N_DEC, K_DEC, BITS, GROUP, O.BF16, config_id=2)
+    xs = {M: O.make_x(M, K_DEC, O.BF16, config_id=2, tag=M) for M in M_SWEEP}
+    O.qmatmul_ref_rowcache(xs[1], wq, s, b, BITS, GROUP)  # warm
+    t0 = time.perf_counter()
+    nbytes, sweeps = 0, 0
+    while True:
+        for M in M_SWEEP:
+            O.qmatmul_ref_rowcache(xs[M], wq, s, b, BITS, GROUP)
+            nbytes += alg_bytes(M)
+        sweeps += 1
+        dt = time.perf_counter() - t0
+        if dt > budget_s or sweeps >= 50:
+            break
+    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+            "sample": f"{sweeps} sweep(s) of M in {list(M_SWEEP)} over one 11008x4096 4-bit layer, "
+                      f"{dt:.1f} s, OpenMP over output rows, fp32 sequential k-sum (reference CPU backend style)"}, dt, sweeps
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    import oracle as O
+    O.build()
+    wq, s, b = O.make_layer(N_DEC, K_DEC, BITS, GROUP, O.BF16, config_id=2)
+    xs = {M: O.make_x(M, K_DEC, O.BF16, config_id=2, tag=M) for M in M_SWEEP}
+
+    def step():
+        for M in M_SWEEP:
+            O.qmatmul_ref_rowcache(xs[M], wq, s, b, BITS, GROUP)
+
+    for _ in range(max(1, min(args.warmup, 3))):
+        step()
+    steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = time.perf_counter() - t0
+    nbytes = steps * sum(alg_bytes(M) for M in M_SWEEP)
+    val = nbytes / dt / 1e9
+    sample = (f"{steps} step(s), each one sweep of M in {list(M_SWEEP)} over one 11008x4096 4-bit layer "
+              f"(the GPU arm's step is {args.reps} such sweeps over {R_SETS} weight sets)")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "decode_gemv_sweep", "M": list(M_SWEEP), "K": K_DEC, "N": N_DEC, "bits": BITS, "group": GROUP},
+        "cpu_baseline": {"value": val, "unit": "GB/s", "cores": O.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference has no quantized matmul; this is its CPU backend's matmul loop "
+                "(src/cpu_backend.cpp:243-266) with unpack+dequant fused, from oracle/qmm_oracle.c",
+    }))
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def run_ours(args, rank, world):
+    import mlx_b200
+    from mlx_b200 import BF16
+    import oracle as O  # input generation + CPU baseline only
+
+    local_rank = int(os.environ.get("LOCAL_RANK", rank))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    plugin = mlx_b200.Plugin(require_gpu=True)
+    ctx = plugin.context(local_rank)
+    q = plugin.quant
+
+    # resident inputs: R weight sets (each rank: its own column slice), x per M
+    layers = []
+    for r in range(R_SETS):
+        wq, s, b = O.make_layer(N_DEC, K_DEC, BITS, GROUP, O.BF16, config_id=2, layer=r, proj=rank)
+        layers.append((ctx.upload(wq), ctx.upload(s), ctx.upload(b)))
+    x_host = {M: O.make_x(M, K_DEC, O.BF16, config_id=2, tag=M) for M in M_SWEEP}
+    x_dev = {M: ctx.upload(x_host[M]) for M in M_SWEEP}
+    n_total = N_DEC * world
+    y_dev = {M: ctx.empty((M, n_total), np.uint16) for M in M_SWEEP}
+    comm, staging = None, {}
+    if world > 1:
+        import ctypes as C
+        import torch
+        uid = (C.c_ubyte * 128)()
+        if rank == 0:
+            plugin.check(q.shard_unique_id(uid), "shard_unique_id")
+        t = torch.tensor(list(uid), dtype=torch.uint8, device="cuda")
+        dist.broadcast(t, 0)
+        uid = (C.c_ubyte * 128)(*t.cpu().tolist())
+        comm = C.c_void_p(None)
+        plugin.check(q.shard_comm_create(ctx.handle, rank, world, uid, C.byref(comm)), "shard_comm_create")
+        staging = {M: ctx.empty((world, M, N_DEC), np.uint16) for M in M_SWEEP}
+
+    def launch(M, r):
+        w, s, b = layers[r]
+        if world == 1:
+            ctx.qmatmul(x_dev[M], w, s, b, y_dev[M], M, K_DEC, N_DEC, BITS, GROUP, BF16, BF16, BF16)
+        else:
+            plugin.check(q.qmatmul_sharded(comm, x_dev[M].handle, w.handle, s.handle, b.handle, y_dev[M].handle,
+                                           staging[M].handle, M, K_DEC, N_DEC, BITS, GROUP, BF16, BF16, BF16),
+                         "qmatmul_sharded")
+
+    # eager pass: creates workspaces, checks one result against the oracle
+    for M in M_SWEEP:
+        launch(M, 0)
+    ctx.sync()
+    if rank == 0:
+        y = y_dev[4].to_host()[:, :N_DEC]
+        wq0, s0, b0 = O.make_layer(N_DEC, K_DEC, BITS, GROUP, O.BF16, config_id=2, layer=0, proj=0)
+        err, _ = O.rel_err(y, O.qmatmul_truth(x_host[4], wq0, s0, b0, BITS, GROUP))
+        assert err <= O.TOL[O.BF16], f"parity check failed before timing: {err}"
+
+    # one sweep = len(M_SWEEP) * R launches, recorded once as a CUDA graph per M
+    l0 = ctx.launch_count()
+    graphs = {}
+    use_graph = world == 1 and not args.no_graph
+    if use_graph:
+        for M in M_SWEEP:
+            ctx.graph_begin()
+            for r in range(R_SETS):
+                launch(M, r)
+            graphs[M] = ctx.graph_end()
+
+    def sweep():
+        for M in M_SWEEP:
+            if use_graph:
+                ctx.graph_launch(graphs[M])
+            else:
+                for r in range(R_SETS):
+                    launch(M, r)
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+        ctx.sync()
+
+    def timed(fn, slot0=0, slot1=1):
+        barrier()
+        ctx.timer_record(slot0)
+        fn()
+        ctx.timer_record(slot1)
+        ms = ctx.timer_elapsed_ms(slot0, slot1)
+        barrier()
+        if dist is not None:
+            import torch
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def step():
+        for _ in range(args.reps):
+            sweep()
+
+    for _ in range(args.warmup):
+        step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    lc0 = ctx.launch_count()
+    ms_total = timed(lambda: [step() for _ in range(args.steps)])
+    launches = ctx.launch_count() - lc0
+    clocks = sampler.stop() if rank == 0 else None
+
+    # per-M timing (same graphs, one M at a time) for the roofline of the dominant kernel
+    per_m = {}
+    reps_m = max(10, args.reps)
+    for M in M_SWEEP:
+        def run_m(M=M):
+            for _ in range(reps_m):
+                if use_graph:
+                    ctx.graph_launch(graphs[M])
+                else:
+                    for r in range(R_SETS):
+                        launch(M, r)
+        run_m()
+        ms = timed(run_m, 2, 3)
+        n_launch = reps_m * R_SETS
+        per_m[M] = {"us_per_launch": ms * 1e3 / n_launch, "GBps": alg_bytes(M) * world * n_launch / ms / 1e6,
+                    "kernel": ctx.last_kernel()}
+
+    sweep_bytes = sum(alg_bytes(M) for M in M_SWEEP) * R_SETS * world
+    total_bytes = sweep_bytes * args.reps * args.steps
+    value = total_bytes / ms_total / 1e6  # GB/s
+    n_launches_alg = len(M_SWEEP) * R_SETS * args.reps * args.steps
+
+    # e2e: host buffers in, host buffers out, through the base vtable copies (blocking, reference semantics)
+    e2e_calls = 0
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_reps = max(1, min(args.reps, 20))
+    y_host = {M: np.empty((M, n_total), np.uint16) for M in M_SWEEP}
+
+    def e2e_step():
+        nonlocal e2e_calls
+        for _ in range(e2e_reps):
+            for M in M_SWEEP:
+                for r in range(R_SETS):
+                    x_dev[M].from_host(x_host[M])
+                    launch(M, r)
+                    y_host[M][...] = y_dev[M].to_host()
+                    e2e_calls += 1
+    if args.kernel_only:
+        e2e_steps = e2e_reps = 0
+    e2e_step()
+    e2e_calls = 0
+    ms_e2e = timed(lambda: [e2e_step() for _ in range(e2e_steps)], 4, 5) if e2e_steps else float("nan")
+    e2e_value = sweep_bytes * e2e_reps * e2e_steps / ms_e2e / 1e6
+    h2d = sum(M * K_DEC * 2 for M in M_SWEEP) * R_SETS * e2e_reps
+    d2h = sum(M * n_total * 2 for M in M_SWEEP) * R_SETS * e2e_reps
+
+    if rank != 0:
+        return
+    peaks, which = measured_peaks()
+    peak = float(peaks["hbm_gbs"])
+    dom = max(M_SWEEP, key=lambda M: 1)  # all launches are the same kernel family; report the sweep average
+    avg_us = ms_total * 1e3 / n_launches_alg
+    achieved = value / world  # per-GPU GB/s of the kernel, averaged over the timed region
+    cpu, _, _ = cpu_baseline() if (world == 1 and not args.kernel_only) else ({"value": None, "unit": "GB/s", "cores": None, "kind": "port",
+                                                   "sample": "run at N=1 only"}, 0, 0)
+    out = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "decode_gemv_sweep" if world == 1 else "decode_gemv_sweep_column_sharded_allgather",
+                   "M": list(M_SWEEP), "K": K_DEC, "N": N_DEC, "N_total": n_total, "bits": BITS, "group": GROUP,
+                   "weight_sets": R_SETS, "sweeps_per_step": args.reps, "cuda_graph": use_graph,
+                   "l2": f"inputs larger than L2: {R_SETS} rotating weight sets = {R_SETS * alg_bytes(1) / 1e6:.0f} MB, "
+                         "each launch reads a set last touched 11 launches earlier"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": which, "frac_of_nominal_8TBps": achieved / NOMINAL_HBM_GBS,
+                     "kernel": "qmv_mma<4,m8|m16>", "avg_us_per_launch": avg_us,
+                     "alg_bytes_per_launch": {str(M): alg_bytes(M) for M in M_SWEEP},
+                     "traffic": args.traffic_bytes},
+        "per_M": {str(M): per_m[M] for M in M_SWEEP},
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "calls": e2e_calls, "us_per_call": ms_e2e * 1e3 / max(1, e2e_calls),
+                "note": "per call: buffer_copy_from_host(x) + qmatmul + buffer_copy_to_host(y); weights stay resident "
+                        "like the core's tensors (src/gpu_core.cpp:47-76)"},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--reps", type=int, default=50, help="sweeps per step")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the e2e and CPU-baseline legs (for short runs under a profiler)")
+    ap.add_argument("--traffic-bytes", type=float, default=None,
+                    help="dram bytes per launch from the committed ncu summary (profiles/), echoed into roofline.traffic")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print(f"launch with torchrun --nproc-per-node {args.gpus} for --gpus {args.gpus}", file=sys.stderr)
+            sys.exit(2)
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        run_ours(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -59,6 +59,8 @@ typedef struct lux_qmm_params {
 
 /* One rank of a column-sharded layer (see shard_* below). */
 typedef struct LuxCudaShardComm LuxCudaShardComm;
+/* A recorded sequence of calls on one context (see graph_*). */
+typedef struct LuxCudaGraph LuxCudaGraph;
 
 typedef struct lux_gpu_quant_vtbl {
     uint32_t magic;   /* LUX_CUDA_QUANT_MAGIC */
@@ -135,6 +137,17 @@ typedef struct lux_gpu_quant_vtbl {
      * kernels launched by the plugin on this context so far. */
     const char* (*last_kernel)(LuxBackendContext* ctx);
     uint64_t (*launch_count)(LuxBackendContext* ctx);
+
+    /* --- CUDA graphs over the context's stream ------------------------------ */
+    /* Calls made on the context between graph_begin and graph_end are recorded
+     * instead of run (no sync / copy_to_host in between; run each shape once
+     * eagerly first so workspaces exist).  graph_launch replays them
+     * stream-ordered.  The reference has no counterpart (its stream API is a
+     * stub, src/gpu_core.cpp:791-828). */
+    LuxBackendError (*graph_begin)(LuxBackendContext* ctx);
+    LuxBackendError (*graph_end)(LuxBackendContext* ctx, LuxCudaGraph** out);
+    LuxBackendError (*graph_launch)(LuxBackendContext* ctx, LuxCudaGraph* graph);
+    void (*graph_destroy)(LuxCudaGraph* graph);
 
     /* --- column-sharded layers: rank r owns columns [r*Nl, (r+1)*Nl) -------- */
     /* rank 0 obtains an id and hands it to the others (any host channel). */

@@ -306,6 +306,67 @@ uint64_t launch_count(LuxBackendContext* ctx) {
     return c ? c->launches.load() : 0;
 }
 
+// --- CUDA graphs --------------------------------------------------------------
+}  // namespace
+}  // namespace luxcuda
+struct LuxCudaGraph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int device = 0;
+    uint64_t launches = 0;  // plugin kernels recorded in the graph
+};
+namespace luxcuda {
+namespace {
+thread_local uint64_t t_capture_base = 0;
+
+LuxBackendError graph_begin(LuxBackendContext* ctx) {
+    Context* c = as_ctx(ctx);
+    if (!c) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    DeviceGuard g(c->dev->device());
+    LUX_CUDA_TRY(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    t_capture_base = c->launches.load();
+    return LUX_BACKEND_OK;
+}
+LuxBackendError graph_end(LuxBackendContext* ctx, LuxCudaGraph** out) {
+    Context* c = as_ctx(ctx);
+    if (!c || !out) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    DeviceGuard g(c->dev->device());
+    cudaGraph_t graph = nullptr;
+    LUX_CUDA_TRY(cudaStreamEndCapture(c->stream, &graph));
+    auto* gr = new (std::nothrow) LuxCudaGraph();
+    if (!gr) {
+        cudaGraphDestroy(graph);
+        return LUX_BACKEND_ERROR_OUT_OF_MEMORY;
+    }
+    gr->graph = graph;
+    gr->device = c->dev->device();
+    gr->launches = c->launches.load() - t_capture_base;
+    c->launches -= gr->launches;  // recorded, not run
+    cudaError_t e = cudaGraphInstantiate(&gr->exec, graph, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(graph);
+        delete gr;
+        return map_cuda_error(e, "cudaGraphInstantiate");
+    }
+    *out = gr;
+    return LUX_BACKEND_OK;
+}
+LuxBackendError graph_launch(LuxBackendContext* ctx, LuxCudaGraph* gr) {
+    Context* c = as_ctx(ctx);
+    if (!c || !gr || !gr->exec || gr->device != c->dev->device()) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    DeviceGuard g(c->dev->device());
+    LUX_CUDA_TRY(cudaGraphLaunch(gr->exec, c->stream));
+    c->launches += gr->launches;
+    return LUX_BACKEND_OK;
+}
+void graph_destroy(LuxCudaGraph* gr) {
+    if (!gr) return;
+    DeviceGuard g(gr->device);
+    if (gr->exec) cudaGraphExecDestroy(gr->exec);
+    if (gr->graph) cudaGraphDestroy(gr->graph);
+    delete gr;
+}
+
 lux_gpu_quant_vtbl g_quant;
 std::once_flag g_quant_once;
 
@@ -333,6 +394,10 @@ void fill_quant() {
     g_quant.flush_l2 = flush_l2;
     g_quant.last_kernel = last_kernel;
     g_quant.launch_count = launch_count;
+    g_quant.graph_begin = graph_begin;
+    g_quant.graph_end = graph_end;
+    g_quant.graph_launch = graph_launch;
+    g_quant.graph_destroy = graph_destroy;
     fill_shard_entries(&g_quant);
 }
 

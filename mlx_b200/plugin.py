@@ -116,6 +116,10 @@ class QuantVtbl(C.Structure):  # include/lux_cuda_quant.h: lux_gpu_quant_vtbl
         ("flush_l2", _fn(_i, _vp)),
         ("last_kernel", _fn(C.c_char_p, _vp)),
         ("launch_count", _fn(_u64, _vp)),
+        ("graph_begin", _fn(_i, _vp)),
+        ("graph_end", _fn(_i, _vp, C.POINTER(_vp))),
+        ("graph_launch", _fn(_i, _vp, _vp)),
+        ("graph_destroy", _fn(None, _vp)),
         ("shard_unique_id", _fn(_i, _vp)),
         ("shard_comm_create", _fn(_i, _vp, _i, _i, _vp, C.POINTER(_vp))),
         ("shard_comm_create_all", _fn(_i, C.POINTER(_vp), _i, C.POINTER(_vp))),
@@ -353,6 +357,24 @@ class Context:
 
     def stream(self):
         return self.plugin.quant.context_stream(self.handle)
+
+    def graph_begin(self):
+        self.plugin.check(self.plugin.quant.graph_begin(self.handle), "graph_begin")
+
+    def graph_end(self):
+        g = _vp(None)
+        self.plugin.check(self.plugin.quant.graph_end(self.handle, C.byref(g)), "graph_end")
+        return g
+
+    def graph_launch(self, g):
+        self.plugin.check(self.plugin.quant.graph_launch(self.handle, g), "graph_launch")
+
+    def graph_destroy(self, g):
+        self.plugin.quant.graph_destroy(g)
+
+    def upload_async(self, buf, pinned_ptr, nbytes):
+        self.plugin.check(self.plugin.quant.buffer_copy_from_host_async(self.handle, buf.handle, pinned_ptr, nbytes),
+                          "buffer_copy_from_host_async")
 
 
 class QuantizedLinear:
