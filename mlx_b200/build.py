@@ -48,8 +48,8 @@ def build(verbose=False, force=False, ptxas_info=False):
         raise RuntimeError("cannot build the plugin: reference ABI header (lux/gpu/backend_plugin.h) not found "
                            "and no prebuilt library present")
     os.makedirs(OBJ_DIR, exist_ok=True)
-    headers = [os.path.join(CSRC, "internal.h"), os.path.join(ROOT, "include", "lux_cuda_quant.h"),
-               os.path.join(ref_inc, "lux", "gpu", "backend_plugin.h")]
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))] + \
+              [os.path.join(ROOT, "include", "lux_cuda_quant.h"), os.path.join(ref_inc, "lux", "gpu", "backend_plugin.h")]
     objs, procs = [], []
     for src in SOURCES:
         sp = os.path.join(CSRC, src)

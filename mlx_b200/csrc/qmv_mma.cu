@@ -1,73 +1,86 @@
 // Decode-regime quantized GEMV for bf16 activations, M <= 16:
 //   y[M,N] = x[M,K] . dequant(Wq[N,K])^T,  w^ = RNE_bf16(s*q + b)  (one bf16 FMA)
 //
-// HBM-bound: every packed weight word, scale and bias is read exactly once
-// with 256-bit coalesced loads straight into registers, dequantised there and
-// fed to mma.sync.m16n8k16 (bf16 x bf16 -> fp32), so the M <= 16 rows of x
-// cost no extra instruction per weight.  Algorithmic bytes per output row:
-// K*bits/8 + 2*(K/group)*2.
+// HBM-bound: every packed weight word, scale and bias is read from HBM exactly
+// once.  Algorithmic bytes per output row: K*bits/8 + 2*(K/group)*2.
 //
-// Work decomposition ("task" = 16 rows of W x one k-block of KB = 1024/bits
-// columns, 2 KiB of packed weights):
-//   * tasks are numbered row-tile major, k-block minor; CTA c of G (one per
-//     SM, persistent) takes the contiguous range [c*T/G, (c+1)*T/G), so every
-//     SM streams the same number of bytes (+-1 task) whatever N is;
-//   * inside a CTA the 16 warps take tasks round-robin; lane (g = lane/4,
-//     t = lane%4) loads 32 contiguous bytes of row g and of row g+8, i.e. the
-//     KT = 256/bits weights k = kb*KB + t*KT + [0,KT) -- one 256-bit load per
-//     row, one quantisation group per load (group >= KT);
-//   * the dot product is invariant under a permutation of k applied to both
-//     operands, so the eight 4-bit values of a word are used in the order the
-//     shift/mask unpack yields them (pairs (i, i+4)) and x is staged into
-//     shared memory once per CTA in exactly that fragment order;
-//   * each task leaves a 16 x 8*MT fp32 partial in shared memory; when all
-//     k-blocks of a row tile are done the partials are summed in k-block order
-//     (fixed order => the result does not depend on N, on the number of CTAs
-//     or on how the columns of a layer are sharded over GPUs);
-//   * a row tile whose k-blocks straddle two or more CTAs goes through a global
-//     scratch slot: each CTA exports its partials and bumps an arrival
-//     counter; the last arriver sums all of them, again in k-block order, and
-//     resets the counter.  No CTA ever waits for another one.
-//
-// Registers hold three tasks in flight per warp (2 being loaded while 1 is
-// computed): 16 warps x 2 x 2 KiB = 64 KiB of loads in flight per SM.
+// A 25 MB layer is a ~4 us stream, shorter than the memory latency ramp, so
+// the kernel is built to put as many bytes in flight per SM as early as
+// possible and never to make one warp wait for another:
+//   * "task" = 16 rows of W x one k-block (128 bytes per row: 256 four-bit or
+//     128 eight-bit weights) = 2 KiB of packed weights + its scales/biases;
+//   * CTA (one per SM, 16 warps) owns a range of 16-row tiles and a range of
+//     k-blocks; warp w owns the k-blocks kb_lo + w + 16*s of that range and
+//     walks them over the CTA's tiles;
+//   * each warp keeps a private ring of kDepth task buffers in shared memory,
+//     filled with cp.async (16-byte pieces, L1 bypass): kDepth-1 tasks
+//     (2.5 KiB each) are in flight per warp -- 120 KiB per SM -- with no
+//     registers tied up and no block-wide barrier in the streaming loop;
+//   * lane (g = lane/4, t = lane%4) copies and later reads back exactly its own
+//     pieces: rows g and g+8, the 16-byte pieces t and t+4 of the 128-byte
+//     k-block row (so each quad copies 64 contiguous bytes per instruction);
+//   * weights are dequantised in registers (dequant.cuh) and fed to
+//     mma.sync.m16n8k16 (bf16 x bf16 -> fp32): the <= 16 rows of x cost no
+//     extra instruction per weight.  The dot product is invariant under a
+//     permutation of k applied to both operands, so the weights are used in
+//     the order the mask/shift unpack yields them and the x fragments of the
+//     warp's k-block are loaded once, in that order, into registers;
+//   * every task leaves a 16 x 8*MT fp32 partial in shared memory; at the end
+//     of a batch of tiles the partials of a tile are summed in k-block order
+//     (fixed order => the result does not depend on N, on the grid or on how
+//     the columns of a layer are sharded over GPUs);
+//   * when a layer has too few tiles to fill the GPU, K is split over KS CTAs
+//     per tile range: each exports its partials to a global scratch slot and
+//     bumps the tile's arrival counter; the last arriver sums all of them,
+//     again in k-block order, and resets the counter.  Nobody waits.
 #include <cuda_bf16.h>
 
+#include <algorithm>
+
+#include "dequant.cuh"
 #include "internal.h"
 
 namespace luxcuda {
 
 namespace {
 
+#ifdef QMV_TRACE
+__device__ long long g_trace[148][16][16];
+__device__ __forceinline__ long long gtime() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TRACE(i) do { if ((threadIdx.x & 31) == 0 && (i) < 16) g_trace[blockIdx.x][threadIdx.x >> 5][(i)] = gtime(); } while (0)
+#else
+#define TRACE(i) do {} while (0)
+#endif
+
 constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
+#ifndef QMV_DEPTH
+#define QMV_DEPTH 2
+#endif
+constexpr int kDepth = QMV_DEPTH;          // ring stages per warp (2 measured best: deeper rings only delay the first data)
+constexpr int kStageBytes = 2048 + 512;    // 4 x 32 x 16 B of weights + 32 x 16 B of scales/biases
+constexpr int kRingBytes = kWarps * kDepth * kStageBytes;
+constexpr int kSmemLimit = 227 * 1024 - 256;
+constexpr int kMaxTb = 32;                 // tiles per reduction batch (flags array)
 
-__device__ __forceinline__ void ldg256(const void* p, uint32_t (&r)[8]) {
-    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "l"(p));
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
 }
-__device__ __forceinline__ uint32_t ldg_u16(const void* p) {
-    uint16_t v;
-    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
-    return v;
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src));
 }
-__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src));
 }
-template <int LUT>
-__device__ __forceinline__ uint32_t lop3(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("lop3.b32 %0, %1, %2, %3, %4;" : "=r"(d) : "r"(a), "r"(b), "r"(c), "n"(LUT));
-    return d;
-}
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
-}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
     asm volatile(
@@ -76,297 +89,438 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Eight 4-bit values of `w` -> four bf16x2 registers, out[i] = (w^_i, w^_{i+4}).
-// (w >> 4i) & 0x000F000F | 0x43004300 is the bf16 pair (128+q_i, 128+q_{i+4});
-// one FMA by 1.0 with -128 recovers q exactly, one FMA applies scale and bias.
-__device__ __forceinline__ void dequant4(uint32_t w, uint32_t s2, uint32_t b2, uint32_t (&out)[4]) {
-    constexpr uint32_t MASK = 0x000F000Fu, MAGIC = 0x43004300u, ONE = 0x3F803F80u, NEG128 = 0xC300C300u;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const uint32_t v = lop3<0xEA>(w >> (4 * i), MASK, MAGIC);  // (a & b) | c
-        out[i] = fma_bf16x2(fma_bf16x2(v, ONE, NEG128), s2, b2);
-    }
-}
-// Four 8-bit values of `w` -> two bf16x2 registers (w^_0, w^_1), (w^_2, w^_3).
-// byte | 0x4B000000 is the float 2^23 + q; subtracting 2^23 gives q exactly.
-__device__ __forceinline__ void dequant8(uint32_t w, uint32_t s2, uint32_t b2, uint32_t (&out)[2]) {
-    const float f0 = __uint_as_float(prmt(w, 0x4B000000u, 0x7540u)) - 8388608.0f;
-    const float f1 = __uint_as_float(prmt(w, 0x4B000000u, 0x7541u)) - 8388608.0f;
-    const float f2 = __uint_as_float(prmt(w, 0x4B000000u, 0x7542u)) - 8388608.0f;
-    const float f3 = __uint_as_float(prmt(w, 0x4B000000u, 0x7543u)) - 8388608.0f;
-    uint32_t p01, p23;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(p01) : "f"(f1), "f"(f0));
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(p23) : "f"(f3), "f"(f2));
-    out[0] = fma_bf16x2(p01, s2, b2);
-    out[1] = fma_bf16x2(p23, s2, b2);
-}
-
-template <int BITS, int GPT>
-struct Stage {
-    uint32_t w[2][8];      // rows g and g+8: 32 bytes of packed weights each
-    uint32_t s[2][GPT];    // bf16 scale(s) of the lane's k-range, raw bits
-    uint32_t b[2][GPT];
-};
-
 struct Params {
     const __nv_bfloat16* x;
     const uint32_t* wq;
     const __nv_bfloat16* scales;
     const __nv_bfloat16* biases;
     void* y;
-    float* scratch;          // [G][nkb][128*MT] partials of row tiles shared between CTAs
-    unsigned int* counters;  // [G] arrival counters (zero between launches)
-    int M, K, N, group, y_bf16;
+    float* scratch;          // [n_rt][nkb][128*MT] partials of k-split tiles
+    unsigned int* counters;  // [n_rt] arrival counters (zero between launches)
+    int M, K, N, gshift, y_bf16;
     int nkb, n_rt;
-    long long T;             // n_rt * nkb tasks
+    int chunks, ks;          // grid = chunks (tile ranges) x ks (k-block ranges)
+    int tb;                  // tiles per reduction batch
+    int sb_bytes;            // bytes of scales per row per k-block: 2, 4, 8 or 16
 };
 
-// BITS: 4 | 8.  MT: number of 8-row blocks of x (M <= 8*MT).  GPT: groups per lane chunk (1 | 2).
-template <int BITS, int MT, int GPT>
-__global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const Params p) {
-    constexpr int KT = 256 / BITS;        // weights per lane per row per task
-    constexpr int KB = 4 * KT;            // k-block
-    constexpr int XV = BITS == 4 ? 8 : 4; // uint4 of x per lane per task per 8-row block
-    extern __shared__ __align__(16) unsigned char smem[];
-    uint4* xs = reinterpret_cast<uint4*>(smem);                                   // [MT][nkb][XV][32]
-    float4* part = reinterpret_cast<float4*>(smem + (size_t)MT * p.nkb * XV * 512);  // [2][nkb][MT][32]
-    __shared__ int s_last;
-
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int G = gridDim.x, c = blockIdx.x;
-    const int nkb = p.nkb;
-    const long long t_begin = p.T * c / G, t_end = p.T * (c + 1) / G;
-    const size_t row_bytes = (size_t)p.K * BITS / 8;
-    const int gpr = p.K / p.group;
-
-    // ---- per-warp task iterators (issue runs two tasks ahead of compute) ----
-    // warp takes tasks t_begin + warp + i*kWarps
-    long long tau_i = t_begin + warp;                      // next task to issue loads for
-    int rt_i = (int)(tau_i / nkb), kb_i = (int)(tau_i % nkb);
-
-    auto issue = [&](Stage<BITS, GPT>& st) {
-        if (tau_i < t_end) {
-            const int n0 = rt_i * 16;
-            const int r0 = min(n0 + g, p.N - 1), r1 = min(n0 + g + 8, p.N - 1);
-            const size_t off = (size_t)kb_i * (KB * BITS / 8) + t * 32;
-            ldg256(reinterpret_cast<const unsigned char*>(p.wq) + r0 * row_bytes + off, st.w[0]);
-            ldg256(reinterpret_cast<const unsigned char*>(p.wq) + r1 * row_bytes + off, st.w[1]);
-            const int k0 = kb_i * KB + t * KT;
-#pragma unroll
-            for (int q = 0; q < GPT; q++) {
-                const int gi = (k0 + q * (KT / GPT)) / p.group;
-                st.s[0][q] = ldg_u16(p.scales + (size_t)r0 * gpr + gi);
-                st.b[0][q] = ldg_u16(p.biases + (size_t)r0 * gpr + gi);
-                st.s[1][q] = ldg_u16(p.scales + (size_t)r1 * gpr + gi);
-                st.b[1][q] = ldg_u16(p.biases + (size_t)r1 * gpr + gi);
-            }
-        }
-        tau_i += kWarps;
-        kb_i += kWarps;
-        while (kb_i >= nkb) {
-            kb_i -= nkb;
-            rt_i++;
-        }
-    };
-
-    Stage<BITS, GPT> st0, st1, st2;
-    issue(st0);
-    issue(st1);
-
-    // ---- stage x into shared memory in fragment order (weights already in flight) ----
-    {
-        const int octs_per_row = p.K / 8;
-        const int total = MT * 8 * octs_per_row;
-        for (int i = tid; i < total; i += kThreads) {
-            const int m = i / octs_per_row, o = i - m * octs_per_row;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (m < p.M) v = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)m * p.K) + o);
-            const int mt = m >> 3, gg = m & 7;
-            int kb, tt, j, dst_lane;
-            if (BITS == 4) {
-                kb = o >> 5; tt = (o >> 3) & 3; j = o & 7;
-                dst_lane = (gg * 4 + tt) ^ j;
-                // order within the octet: (0,4,1,5 | 2,6,3,7)
-                uint4 r;
-                r.x = prmt(v.x, v.z, 0x5410u);  // x0, x4
-                r.y = prmt(v.x, v.z, 0x7632u);  // x1, x5
-                r.z = prmt(v.y, v.w, 0x5410u);  // x2, x6
-                r.w = prmt(v.y, v.w, 0x7632u);  // x3, x7
-                v = r;
-            } else {
-                kb = o >> 4; tt = (o >> 2) & 3; j = o & 3;
-                dst_lane = (gg * 4 + tt) ^ (j * 2);
-            }
-            xs[(((size_t)mt * nkb + kb) * XV + j) * 32 + dst_lane] = v;
-        }
+template <int MT>
+__device__ __forceinline__ void store_tile(const Params& p, int rt, int e, float sum) {
+    const int mt = e >> 7, rem = e & 127, ln = rem >> 2, ci = rem & 3;
+    const int row = rt * 16 + (ln >> 2) + 8 * (ci >> 1);
+    const int m = mt * 8 + 2 * (ln & 3) + (ci & 1);
+    if (row < p.N && m < p.M) {
+        const size_t idx = (size_t)m * p.N + row;
+        if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(sum);
+        else reinterpret_cast<float*>(p.y)[idx] = sum;
     }
+}
+
+// Sum n partials (stride floats apart) in order; loads are issued eight at a
+// time so their latencies overlap, the additions stay in order.
+template <bool GLOBAL>
+__device__ __forceinline__ float ordered_sum(const float* src, int n, int stride, float sum) {
+    int i = 0;
+    for (; i + 8 <= n; i += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = GLOBAL ? __ldcg(src + (size_t)(i + u) * stride) : src[(i + u) * stride];
+#pragma unroll
+        for (int u = 0; u < 8; u++) sum += v[u];
+    }
+    for (; i < n; i++) sum += GLOBAL ? __ldcg(src + (size_t)i * stride) : src[i * stride];
+    return sum;
+}
+
+// End of a batch of row tiles (all threads call it): sum the per-k-block
+// partials of every tile in k-block order and write y.  With K split over
+// several CTAs the partials go through the tile's scratch slot and the tile
+// is finished by whichever CTA arrives last.
+template <int MT>
+__device__ __noinline__ void batch_end(const Params& p, const float* part, int first_tile, int ntiles, int kb_lo, int nkl,
+                                       int* flags, bool more) {
+    constexpr int E = 128 * MT;  // fp32 elements per partial
+    const int tid = threadIdx.x;
     __syncthreads();
-
-    // ---- main loop ----
-    long long tau_c = t_begin + warp;                      // next task to compute
-    int rt_c = (int)(tau_c / nkb), kb_c = (int)(tau_c % nkb);
-    const int rt_first = (int)(t_begin / nkb);
-    const int rt_last = t_end > t_begin ? (int)((t_end - 1) / nkb) : rt_first - 1;
-    int cur_tile = rt_first;  // next row tile whose barrier this warp has not passed yet
-
-    // finish row tile rt: reduce the per-k-block partials in order, write y (or export)
-    auto tile_end = [&](int rt) {
-        const int buf = (rt - rt_first) & 1;
+    if (p.ks == 1) {
+        for (int ti = tid / E; ti < ntiles; ti += kThreads / E)
+            store_tile<MT>(p, first_tile + ti, tid % E, ordered_sum<false>(part + ti * nkl * E + tid % E, nkl, E, 0.0f));
+    } else {
+        for (int ti = 0; ti < ntiles; ti++) {
+            float* dst = p.scratch + ((size_t)(first_tile + ti) * p.nkb + kb_lo) * E;
+            const float* src = part + ti * nkl * E;
+            for (int i = tid; i < nkl * E; i += kThreads) __stcg(dst + i, src[i]);
+        }
         __syncthreads();
-        const long long base = (long long)rt * nkb;
-        const int kb_lo = (int)(max(t_begin, base) - base), kb_hi = (int)(min(t_end, base + nkb) - base);
-        const float* pf = reinterpret_cast<const float*>(part) + (size_t)buf * nkb * MT * 128;
-        const bool whole = kb_lo == 0 && kb_hi == nkb;
-        bool reduce_here = whole;
-        const float* src = pf;
-        size_t src_stride = (size_t)MT * 128;
-        if (!whole) {
-            // slot = CTA that owns the first task of the tile
-            int slot = (int)(base * G / p.T);
-            while (slot > 0 && p.T * slot / G > base) slot--;
-            while (p.T * (slot + 1) / G <= base) slot++;
-            float* sc = p.scratch + (size_t)slot * nkb * MT * 128;
-            if (tid < 128 * MT)
-                for (int kb = kb_lo; kb < kb_hi; kb++) __stcg(sc + (size_t)kb * MT * 128 + tid, pf[(size_t)kb * MT * 128 + tid]);
-            __threadfence();
-            __syncthreads();
-            if (tid == 0) {
-                const unsigned int mine = (unsigned int)(kb_hi - kb_lo);
-                const unsigned int old = atomicAdd(p.counters + slot, mine);
-                s_last = (old + mine == (unsigned int)nkb);
-                if (s_last) p.counters[slot] = 0;  // every contributor has arrived: safe to reset
+        if (tid < ntiles) {
+            __threadfence();  // cumulative: publishes the CTA's partials (ordered before by the barrier)
+            const unsigned int old = atomicAdd(p.counters + first_tile + tid, (unsigned int)nkl);
+            const int last = (old + (unsigned int)nkl == (unsigned int)p.nkb);
+            if (last) {
+                p.counters[first_tile + tid] = 0;  // every contributor has arrived: leave the counter clean
+                __threadfence();
             }
-            __syncthreads();
-            reduce_here = s_last != 0;
-            if (reduce_here) __threadfence();
-            src = sc;
+            flags[tid] = last;
         }
-        if (reduce_here && tid < 128 * MT) {
-            float sum = 0.0f;
-            if (whole) {
-                for (int kb = 0; kb < nkb; kb++) sum += src[(size_t)kb * src_stride + tid];
-            } else {
-                for (int kb = 0; kb < nkb; kb++) sum += __ldcg(src + (size_t)kb * src_stride + tid);
-            }
-            const int mt = tid >> 7, rem = tid & 127, ln = rem >> 2, ci = rem & 3;
-            const int row = rt * 16 + (ln >> 2) + 8 * (ci >> 1);
-            const int m = mt * 8 + 2 * (ln & 3) + (ci & 1);
-            if (row < p.N && m < p.M) {
-                const size_t idx = (size_t)m * p.N + row;
-                if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(sum);
-                else reinterpret_cast<float*>(p.y)[idx] = sum;
-            }
-        }
-    };
+        __syncthreads();
+        for (int ti = tid / E; ti < ntiles; ti += kThreads / E)
+            if (flags[ti])
+                store_tile<MT>(p, first_tile + ti, tid % E,
+                               ordered_sum<true>(p.scratch + (size_t)(first_tile + ti) * p.nkb * E + tid % E, p.nkb, E, 0.0f));
+    }
+    if (more) __syncthreads();  // the partial buffer and the flags are reused by the next batch
+}
 
-    auto compute = [&](const Stage<BITS, GPT>& st) {
-        // pass the barriers of the tiles before this task's tile
-        while (cur_tile < rt_c) tile_end(cur_tile++);
-        float acc[MT][4];
+// One task out of the warp's ring stage: 4 x 16 bytes of packed weights per
+// lane (rows g, g+8; pieces t, t+4), their scales/biases, times the x fragments.
+// stage layout: [piece = r*2+h][lane] 16 B  |  [row 0..15 scales][row 0..15 biases] 16 B each
+template <int BITS, int MT, bool FAST>
+__device__ __forceinline__ void task_mma(const uint4 (&w)[2][2], const uint32_t (&s)[2][2], const uint32_t (&b)[2][2],
+                                         const uint4 (&xr)[MT][BITS == 4 ? 8 : 4], float (&acc)[MT][2][4]) {
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.0f;
-        uint32_t s2[2][GPT], b2[2][GPT];
+    for (int h = 0; h < 2; h++) {
+        uint32_t sa[2], sb[2], b2[2];
 #pragma unroll
-        for (int r = 0; r < 2; r++)
-#pragma unroll
-            for (int q = 0; q < GPT; q++) {
-                s2[r][q] = st.s[r][q] | (st.s[r][q] << 16);
-                b2[r][q] = st.b[r][q] | (st.b[r][q] << 16);
-            }
+        for (int r = 0; r < 2; r++) {
+            b2[r] = dup_bf16(b[r][h]);
+            sa[r] = FAST ? scale_x2_133(s[r][h]) : dup_bf16(s[r][h]);
+            sb[r] = FAST ? scale_x2_129(s[r][h]) : 0u;
+        }
+        const uint32_t w0[4] = {w[0][h].x, w[0][h].y, w[0][h].z, w[0][h].w};
+        const uint32_t w1[4] = {w[1][h].x, w[1][h].y, w[1][h].z, w[1][h].w};
         if (BITS == 4) {
 #pragma unroll
-            for (int j = 0; j < 8; j++) {
-                const int q = (GPT == 2 && j >= 4) ? GPT - 1 : 0;
+            for (int i = 0; i < 4; i++) {
                 uint32_t lo[4], hi[4];
-                dequant4(st.w[0][j], s2[0][q], b2[0][q], lo);
-                dequant4(st.w[1][j], s2[1][q], b2[1][q], hi);
+                if (FAST) {
+                    dequant4_fast(w0[i], sa[0], sb[0], b2[0], lo);
+                    dequant4_fast(w1[i], sa[1], sb[1], b2[1], hi);
+                } else {
+                    dequant4_general(w0[i], sa[0], b2[0], lo);
+                    dequant4_general(w1[i], sa[1], b2[1], hi);
+                }
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++) {
-                    const uint4 bx = xs[(((size_t)mt * nkb + kb_c) * XV + j) * 32 + (lane ^ j)];
-                    mma_bf16(acc[mt], lo[0], hi[0], lo[1], hi[1], bx.x, bx.y);
-                    mma_bf16(acc[mt], lo[2], hi[2], lo[3], hi[3], bx.z, bx.w);
+                    const uint4 bx = xr[mt][h * 4 + i];
+                    mma_bf16(acc[mt][0], lo[0], hi[0], lo[1], hi[1], bx.x, bx.y);
+                    mma_bf16(acc[mt][1], lo[2], hi[2], lo[3], hi[3], bx.z, bx.w);
                 }
             }
         } else {
 #pragma unroll
-            for (int jj = 0; jj < 4; jj++) {
+            for (int i = 0; i < 2; i++) {
                 uint32_t lo0[2], hi0[2], lo1[2], hi1[2];
-                dequant8(st.w[0][2 * jj], s2[0][0], b2[0][0], lo0);
-                dequant8(st.w[1][2 * jj], s2[1][0], b2[1][0], hi0);
-                dequant8(st.w[0][2 * jj + 1], s2[0][0], b2[0][0], lo1);
-                dequant8(st.w[1][2 * jj + 1], s2[1][0], b2[1][0], hi1);
+                if (FAST) {
+                    dequant8_fast(w0[2 * i], sa[0], b2[0], lo0);
+                    dequant8_fast(w1[2 * i], sa[1], b2[1], hi0);
+                    dequant8_fast(w0[2 * i + 1], sa[0], b2[0], lo1);
+                    dequant8_fast(w1[2 * i + 1], sa[1], b2[1], hi1);
+                } else {
+                    dequant8_general(w0[2 * i], sa[0], b2[0], lo0);
+                    dequant8_general(w1[2 * i], sa[1], b2[1], hi0);
+                    dequant8_general(w0[2 * i + 1], sa[0], b2[0], lo1);
+                    dequant8_general(w1[2 * i + 1], sa[1], b2[1], hi1);
+                }
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++) {
-                    const uint4 bx = xs[(((size_t)mt * nkb + kb_c) * XV + jj) * 32 + (lane ^ (jj * 2))];
-                    mma_bf16(acc[mt], lo0[0], hi0[0], lo0[1], hi0[1], bx.x, bx.y);
-                    mma_bf16(acc[mt], lo1[0], hi1[0], lo1[1], hi1[1], bx.z, bx.w);
+                    const uint4 bx = xr[mt][h * 2 + i];
+                    mma_bf16(acc[mt][0], lo0[0], hi0[0], lo0[1], hi0[1], bx.x, bx.y);
+                    mma_bf16(acc[mt][1], lo1[0], hi1[0], lo1[1], hi1[1], bx.z, bx.w);
                 }
             }
         }
-        const int buf = (rt_c - rt_first) & 1;
+    }
+}
+
+// x fragments of k-block kb for lane (g, t), in the order the unpack yields the weights.
+//   4-bit: fragment j = h*4+i covers k = kb*256 + h*128 + t*32 + i*8 + (0,4,1,5 | 2,6,3,7)
+//   8-bit: fragment j = h*2+i covers k = kb*128 + h*64  + t*16 + i*8 + (0,2,1,3 | 4,6,5,7)
+template <int BITS, int MT>
+__device__ __forceinline__ void load_x_raw(const Params& p, int kb, int g, int t, uint4 (&xr)[MT][BITS == 4 ? 8 : 4]) {
+    constexpr int XV = BITS == 4 ? 8 : 4;
+    constexpr int KB = 1024 / BITS;
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++)
-            part[(((size_t)buf * nkb + kb_c) * MT + mt) * 32 + lane] = make_float4(acc[mt][0], acc[mt][1], acc[mt][2], acc[mt][3]);
-        tau_c += kWarps;
-        kb_c += kWarps;
-        while (kb_c >= nkb) {
-            kb_c -= nkb;
-            rt_c++;
+    for (int mt = 0; mt < MT; mt++) {
+        const int m = mt * 8 + g;
+        const __nv_bfloat16* row = p.x + (size_t)m * p.K + kb * KB + t * (KB / 8);
+#pragma unroll
+        for (int j = 0; j < XV; j++) {
+            const int h = j / (XV / 2), i = j % (XV / 2);
+            xr[mt][j] = make_uint4(0, 0, 0, 0);
+            if (m < p.M) {
+                const uint4* src = reinterpret_cast<const uint4*>(row + h * (KB / 2) + i * 8);
+                asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(xr[mt][j].x), "=r"(xr[mt][j].y), "=r"(xr[mt][j].z), "=r"(xr[mt][j].w) : "l"(src));
+            }
+        }
+    }
+}
+template <int BITS, int MT>
+__device__ __forceinline__ void permute_x(uint4 (&xr)[MT][BITS == 4 ? 8 : 4]) {
+    constexpr int XV = BITS == 4 ? 8 : 4;
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int j = 0; j < XV; j++) {
+            const uint4 v = xr[mt][j];
+            if (BITS == 4) {
+                xr[mt][j].x = prmt(v.x, v.z, 0x5410u);  // x0, x4
+                xr[mt][j].y = prmt(v.x, v.z, 0x7632u);  // x1, x5
+                xr[mt][j].z = prmt(v.y, v.w, 0x5410u);  // x2, x6
+                xr[mt][j].w = prmt(v.y, v.w, 0x7632u);  // x3, x7
+            } else {
+                xr[mt][j].x = prmt(v.x, v.y, 0x5410u);  // x0, x2
+                xr[mt][j].y = prmt(v.x, v.y, 0x7632u);  // x1, x3
+                xr[mt][j].z = prmt(v.z, v.w, 0x5410u);  // x4, x6
+                xr[mt][j].w = prmt(v.z, v.w, 0x7632u);  // x5, x7
+            }
+        }
+}
+
+// all four scales (raw bf16 bits) usable by the exponent-trick dequantiser?  Packed form of
+// scale_fast_ok: exponent field e in [1, 121]  <=>  ((s - 0x80) & 0x7F80) <= 0x3C00 per half.
+__device__ __forceinline__ bool scales_fast_ok4(uint32_t s00, uint32_t s01, uint32_t s10, uint32_t s11) {
+    const uint32_t a = (((s00 | (s10 << 16)) - 0x00800080u) & 0x7F807F80u) + 0x43804380u;
+    const uint32_t b = (((s01 | (s11 << 16)) - 0x00800080u) & 0x7F807F80u) + 0x43804380u;
+    return ((a | b) & 0x80008000u) == 0u;
+}
+
+// BITS: 4 | 8.  MT: number of 8-row blocks of x (M <= 8*MT).
+template <int BITS, int MT>
+__global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_constant__ Params p) {
+    constexpr int XV = BITS == 4 ? 8 : 4;  // x fragments (uint4) per lane per k-block per 8-row block
+    constexpr int KB = 1024 / BITS;        // weights per k-block (128 bytes per row)
+    constexpr int E4 = MT * 32;            // float4 per partial
+    extern __shared__ __align__(16) unsigned char smem[];
+    float4* part = reinterpret_cast<float4*>(smem + kRingBytes);   // [tb][nkl][MT][32]; ring: [kWarps][kDepth][kStageBytes]
+    __shared__ int s_flags[kMaxTb];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int ci = blockIdx.x % p.chunks, ksi = blockIdx.x / p.chunks;
+    const int rt_lo = (int)((long long)p.n_rt * ci / p.chunks), rt_hi = (int)((long long)p.n_rt * (ci + 1) / p.chunks);
+    const int kb_lo = (int)((long long)p.nkb * ksi / p.ks), kb_hi = (int)((long long)p.nkb * (ksi + 1) / p.ks);
+    const int nkl = kb_hi - kb_lo;
+    const int tb = p.tb;
+    const size_t row_bytes = (size_t)p.K * BITS / 8;
+    const int gpr = p.K >> p.gshift;   // groups per row
+    const int gpk = KB >> p.gshift;    // groups per k-block
+    const unsigned char* wbase = reinterpret_cast<const unsigned char*>(p.wq) + t * 16;
+    const __nv_bfloat16* sb_src = lane < 16 ? p.scales : p.biases;
+    const uint32_t ring_lo = smem_u32(smem) + warp * (kDepth * kStageBytes) + lane * 16;  // this lane's slot, stage 0
+    const uint32_t ring_hi = ring_lo + kDepth * kStageBytes;
+    const int tail_tile = (p.N & 15) ? p.n_rt - 1 : -1;  // the tile whose rows must be clamped to N-1
+
+    // The warp's tasks: for each batch of tb tiles, for each of its k-blocks, for each tile of the
+    // batch.  Pointers advance by one tile per task; everything else is recomputed only when the
+    // k-block or the batch changes.
+    struct Iter {
+        int b0, kb, rt, rt_end;
+        bool valid;
+        const unsigned char* p0;       // row rt*16+g of Wq, k-block kb, piece t
+        const __nv_bfloat16* sbp;      // scales (lanes 0-15) / biases (16-31) of row rt*16+(lane&15), k-block kb
+    };
+    auto it_setup = [&](Iter& it) {
+        it.rt_end = min(it.b0 + tb, rt_hi);
+        it.p0 = wbase + (size_t)(it.rt * 16 + g) * row_bytes + it.kb * 128;
+        int elem = (it.rt * 16 + (lane & 15)) * gpr + it.kb * gpk;
+        if (p.sb_bytes == 2) elem &= ~1;  // a single 2-byte scale is copied with its neighbour
+        it.sbp = sb_src + elem;
+    };
+    auto it_init = [&](Iter& it) {
+        it.b0 = rt_lo; it.kb = kb_lo + warp; it.rt = rt_lo;
+        it.valid = it.kb < kb_hi && rt_lo < rt_hi;
+        if (it.valid) it_setup(it);
+    };
+    auto it_next = [&](Iter& it) {
+        it.rt++;
+        it.p0 += 16 * row_bytes;
+        it.sbp += 16 * gpr;
+        if (it.rt >= it.rt_end) {
+            it.kb += kWarps;
+            it.rt = it.b0;
+            if (it.kb >= kb_hi) {
+                it.b0 += tb;
+                it.kb = kb_lo + warp;
+                it.rt = it.b0;
+                if (it.b0 >= rt_hi) it.valid = false;
+            }
+            if (it.valid) it_setup(it);
         }
     };
+    auto issue = [&](const Iter& it, uint32_t dst) {
+        const unsigned char* p0 = it.p0;
+        const unsigned char* p1 = p0 + 8 * row_bytes;
+        const __nv_bfloat16* sbp = it.sbp;
+        if (it.rt == tail_tile) {  // rows past N read row N-1 (their results are never stored)
+            const int n0 = it.rt * 16;
+            p0 = wbase + (size_t)min(n0 + g, p.N - 1) * row_bytes + it.kb * 128;
+            p1 = wbase + (size_t)min(n0 + g + 8, p.N - 1) * row_bytes + it.kb * 128;
+            int elem = min(n0 + (lane & 15), p.N - 1) * gpr + it.kb * gpk;
+            if (p.sb_bytes == 2) elem &= ~1;
+            sbp = sb_src + elem;
+        }
+        cp_async16(dst, p0);
+        cp_async16(dst + 512, p0 + 64);
+        cp_async16(dst + 1024, p1);
+        cp_async16(dst + 1536, p1 + 64);
+        if (p.sb_bytes == 16) cp_async16(dst + 2048, sbp);
+        else if (p.sb_bytes == 8) cp_async8(dst + 2048, sbp);
+        else cp_async4(dst + 2048, sbp);
+    };
 
+    TRACE(0);
+    Iter it_i, it_c;
+    it_init(it_i);
+    it_init(it_c);
+
+    // prime the ring: kDepth-1 tasks in flight before anything else
+    uint32_t dst_i = ring_lo;
 #pragma unroll 1
-    while (tau_c < t_end) {
-        issue(st2);
-        compute(st0);
-        if (tau_c >= t_end) break;
-        issue(st0);
-        compute(st1);
-        if (tau_c >= t_end) break;
-        issue(st1);
-        compute(st2);
+    for (int d = 0; d < kDepth - 1; d++) {
+        if (it_i.valid) {
+            issue(it_i, dst_i);
+            it_next(it_i);
+        }
+        cp_async_commit();
+        dst_i += kStageBytes;
     }
-    while (cur_tile <= rt_last) tile_end(cur_tile++);
+
+    // per-k-block state of the compute side
+    uint4 xr[MT][XV];
+    uint32_t sboff[2][2];   // byte offsets of this lane's scales inside a stage, by row half r and piece h
+    int cur_kb = -1, cur_b0 = rt_lo;
+    uint32_t src_c = ring_lo;   // stage being computed (this lane's slot)
+    float4* dstp = part;
+    TRACE(1);
+    int trace_i = 2;
+    (void)trace_i;
+#pragma unroll 1
+    while (it_c.valid) {
+        if (it_i.valid) {
+            issue(it_i, dst_i);
+            it_next(it_i);
+        }
+        cp_async_commit();
+        dst_i += kStageBytes;
+        if (dst_i == ring_hi) dst_i = ring_lo;
+
+        if (it_c.b0 != cur_b0 || it_c.kb != cur_kb) {  // new k-block or new batch (rare)
+            while (cur_b0 < it_c.b0) {
+                batch_end<MT>(p, reinterpret_cast<const float*>(part), cur_b0, min(tb, rt_hi - cur_b0), kb_lo, nkl, s_flags, true);
+                cur_b0 += tb;
+            }
+            if (it_c.kb != cur_kb) {
+                cur_kb = it_c.kb;
+                load_x_raw<BITS, MT>(p, cur_kb, g, t, xr);
+                permute_x<BITS, MT>(xr);
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    const int slot = g + 8 * r;
+                    const int par = p.sb_bytes == 2 ? ((slot * gpr + cur_kb) & 1) : 0;
+#pragma unroll
+                    for (int h = 0; h < 2; h++)
+                        sboff[r][h] = 2048 - lane * 16 + slot * 16 + ((((h * (KB / 2) + t * (KB / 8)) >> p.gshift) + par) << 1);
+                }
+            }
+            dstp = part + ((it_c.rt - it_c.b0) * nkl + (cur_kb - kb_lo)) * E4 + lane;
+        }
+        cp_async_wait<kDepth - 1>();
+        __syncwarp();
+        uint4 w[2][2];
+        uint32_t s[2][2], b[2][2];
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(w[r][h].x), "=r"(w[r][h].y), "=r"(w[r][h].z), "=r"(w[r][h].w)
+                             : "r"(src_c + (r * 2 + h) * 512));
+                uint16_t sv, bv;
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sv) : "r"(src_c + sboff[r][h]));
+                asm volatile("ld.shared.u16 %0, [%1+256];" : "=h"(bv) : "r"(src_c + sboff[r][h]));
+                s[r][h] = sv;
+                b[r][h] = bv;
+            }
+        const bool fast = scales_fast_ok4(s[0][0], s[0][1], s[1][0], s[1][1]);
+        float acc[MT][2][4];  // two independent accumulation chains per 8-row block of x
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+            for (int c = 0; c < 2; c++) acc[mt][c][0] = acc[mt][c][1] = acc[mt][c][2] = acc[mt][c][3] = 0.0f;
+#ifdef QMV_LOADONLY
+        acc[0][0][0] = __uint_as_float(w[0][0].x ^ w[0][1].y ^ w[1][0].z ^ w[1][1].w ^ s[0][0] ^ b[1][1] ^ xr[0][0].x ^ (fast ? 1u : 0u));
+#else
+        if (__all_sync(0xffffffffu, fast)) task_mma<BITS, MT, true>(w, s, b, xr, acc);
+        else task_mma<BITS, MT, false>(w, s, b, xr, acc);
+#endif
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+            dstp[mt * 32] = make_float4(acc[mt][0][0] + acc[mt][1][0], acc[mt][0][1] + acc[mt][1][1],
+                                        acc[mt][0][2] + acc[mt][1][2], acc[mt][0][3] + acc[mt][1][3]);
+        dstp += nkl * E4;
+        __syncwarp();  // every lane is done with the stage before it is refilled
+        it_next(it_c);
+        src_c += kStageBytes;
+        if (src_c == ring_hi) src_c = ring_lo;
+        TRACE(trace_i);
+        trace_i++;
+    }
+    cp_async_wait<0>();
+    while (cur_b0 < rt_hi) {
+        batch_end<MT>(p, reinterpret_cast<const float*>(part), cur_b0, min(tb, rt_hi - cur_b0), kb_lo, nkl, s_flags,
+                      cur_b0 + tb < rt_hi);
+        cur_b0 += tb;
+    }
+    TRACE(15);
 }
 
 struct Plan {
-    int nkb, n_rt, grid, mt, gpt;
-    long long T;
-    size_t smem, scratch_floats;
+    int nkb, n_rt, mt, chunks, ks, tb, gshift, sb_bytes;
+    size_t smem, ctr_bytes, scratch_bytes;
 };
 
 bool make_plan(const QmmArgs& a, int sm_count, Plan* pl) {
     if (a.x_dtype != LUX_DTYPE_BFLOAT16 || a.sb_dtype != LUX_DTYPE_BFLOAT16) return false;
-    if (a.M < 1 || a.M > 16 || a.N < 1) return false;
-    const int KT = 256 / a.bits, KB = 4 * KT;
+    if (a.bits != 4 && a.bits != 8) return false;
+    if (a.M < 1 || a.M > 16 || a.N < 1 || sm_count < 1) return false;
+    const int KB = 1024 / a.bits;
     if (a.K % KB) return false;
-    int gpt = 1;
-    if (a.group < KT) {
-        if (KT / a.group != 2) return false;
-        gpt = 2;
-    } else if (a.group % KT) {
-        return false;
-    }
-    if (a.bits == 8 && gpt != 1) return false;
-    const int XV = a.bits == 4 ? 8 : 4;
+    if (a.group != 32 && a.group != 64 && a.group != 128) return false;
+    pl->gshift = a.group == 32 ? 5 : (a.group == 64 ? 6 : 7);
+    const int gpk = KB >> pl->gshift, gpr = a.K >> pl->gshift;
+    if (gpk < 1) return false;
+    pl->sb_bytes = gpk * 2;
+    if (pl->sb_bytes == 2 && (((long long)a.N * gpr) & 1)) return false;  // pairs of scales are copied
     pl->mt = a.M <= 8 ? 1 : 2;
-    pl->gpt = gpt;
     pl->nkb = a.K / KB;
     pl->n_rt = (a.N + 15) / 16;
-    pl->T = (long long)pl->n_rt * pl->nkb;
-    pl->grid = (int)std::min<long long>(sm_count, pl->T);
-    pl->smem = (size_t)pl->mt * pl->nkb * XV * 512 + (size_t)2 * pl->nkb * pl->mt * 512;
-    pl->scratch_floats = (size_t)pl->grid * pl->nkb * pl->mt * 128;
-    if (pl->smem > 227 * 1024 - 64) return false;  // 16 B of static shared memory besides
-    if (((uintptr_t)a.wq & 31) || ((uintptr_t)a.x & 15)) return false;
+    // 32-bit row/group indices and per-matrix byte offsets inside the kernel
+    if ((long long)a.N * gpr > (1ll << 30) || (long long)pl->n_rt * pl->nkb > (1ll << 30)) return false;
+    // K is split over several CTAs only when the tiles alone cannot fill the GPU and a
+    // CTA's 16 warps would each still own more than one k-block
+    int ks = 1;
+    if (pl->n_rt * 2 <= sm_count) ks = std::max(1, std::min((pl->nkb + kWarps - 1) / kWarps, sm_count / pl->n_rt));
+    if (const char* env = getenv("LUXCUDA_QMV_KSPLIT")) ks = std::max(1, std::min(atoi(env), pl->nkb));
+    pl->ks = ks;
+    pl->chunks = std::max(1, std::min(pl->n_rt, sm_count / ks));
+    const int tiles_max = (pl->n_rt + pl->chunks - 1) / pl->chunks;
+    const int nkl_max = (pl->nkb + ks - 1) / ks;
+    const size_t per_tile = (size_t)nkl_max * pl->mt * 512;
+    const size_t avail = (size_t)kSmemLimit - kRingBytes;
+    if (per_tile > avail) return false;
+    pl->tb = (int)std::min<size_t>(std::min<size_t>(tiles_max, avail / per_tile), kMaxTb);
+    pl->smem = kRingBytes + pl->tb * per_tile;
+    pl->ctr_bytes = ((size_t)pl->n_rt * sizeof(unsigned int) + 255) & ~size_t(255);
+    pl->scratch_bytes = ks > 1 ? (size_t)pl->n_rt * pl->nkb * pl->mt * 128 * sizeof(float) : 0;
+    if (((uintptr_t)a.wq & 15) || ((uintptr_t)a.x & 15) || ((uintptr_t)a.scales & 15) || ((uintptr_t)a.biases & 15)) return false;
     return true;
 }
 
-template <int BITS, int MT, int GPT>
+template <int BITS, int MT>
 cudaError_t launch_t(const Params& p, const Plan& pl, cudaStream_t stream) {
-    auto kern = qmv_mma_kernel<BITS, MT, GPT>;
-    // opt in to large dynamic shared memory (static + dynamic must stay within the 227 KiB per-block limit)
+    auto kern = qmv_mma_kernel<BITS, MT>;
+    // opt in to large dynamic shared memory (static + dynamic stay within the 227 KiB per-block limit)
     static std::atomic<size_t> attr_smem[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -375,7 +529,7 @@ cudaError_t launch_t(const Params& p, const Plan& pl, cudaStream_t stream) {
         if (e != cudaSuccess) return e;
         attr_smem[dev & 63].store(pl.smem);
     }
-    kern<<<pl.grid, kThreads, pl.smem, stream>>>(p);
+    kern<<<pl.chunks * pl.ks, kThreads, pl.smem, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -386,14 +540,16 @@ bool qmv_mma_supported(const QmmArgs& a) {
     return make_plan(a, 148, &pl);
 }
 
+// Scratch memory (global memory beyond inputs and outputs): arrival counters
+// (always present, zero between launches) and, when K is split, the partials.
 size_t qmv_mma_workspace_bytes(const QmmArgs& a, int sm_count) {
     Plan pl;
     if (!make_plan(a, sm_count, &pl)) return 0;
-    return pl.scratch_floats * sizeof(float) + (size_t)pl.grid * sizeof(unsigned int) + 256;
+    return pl.ctr_bytes + pl.scratch_bytes;
 }
 
-// workspace layout: [counters: grid x u32, padded to 256 B][scratch floats]; the
-// counters must be zero before the first launch and are left zero by every launch.
+// workspace layout: [counters: n_rt x u32, padded to 256 B][partials]; the counters must
+// be zero before the first launch and are left zero by every launch.
 cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name) {
     Plan pl;
     if (!make_plan(a, sm_count, &pl)) return cudaErrorInvalidValue;
@@ -403,19 +559,19 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
     p.scales = (const __nv_bfloat16*)a.scales;
     p.biases = (const __nv_bfloat16*)a.biases;
     p.y = a.y;
-    const size_t ctr_bytes = ((size_t)pl.grid * sizeof(unsigned int) + 255) & ~size_t(255);
     p.counters = (unsigned int*)workspace;
-    p.scratch = (float*)((unsigned char*)workspace + ctr_bytes);
-    p.M = a.M; p.K = a.K; p.N = a.N; p.group = a.group;
+    p.scratch = (float*)((unsigned char*)workspace + pl.ctr_bytes);
+    p.M = a.M; p.K = a.K; p.N = a.N;
+    p.gshift = pl.gshift;
     p.y_bf16 = a.y_dtype == LUX_DTYPE_BFLOAT16;
-    p.nkb = pl.nkb; p.n_rt = pl.n_rt; p.T = pl.T;
+    p.nkb = pl.nkb; p.n_rt = pl.n_rt;
+    p.chunks = pl.chunks; p.ks = pl.ks; p.tb = pl.tb; p.sb_bytes = pl.sb_bytes;
     if (a.bits == 4) {
         if (name) *name = pl.mt == 1 ? "qmv_mma<4,m8>" : "qmv_mma<4,m16>";
-        if (pl.mt == 1) return pl.gpt == 1 ? launch_t<4, 1, 1>(p, pl, stream) : launch_t<4, 1, 2>(p, pl, stream);
-        return pl.gpt == 1 ? launch_t<4, 2, 1>(p, pl, stream) : launch_t<4, 2, 2>(p, pl, stream);
+        return pl.mt == 1 ? launch_t<4, 1>(p, pl, stream) : launch_t<4, 2>(p, pl, stream);
     }
     if (name) *name = pl.mt == 1 ? "qmv_mma<8,m8>" : "qmv_mma<8,m16>";
-    return pl.mt == 1 ? launch_t<8, 1, 1>(p, pl, stream) : launch_t<8, 2, 1>(p, pl, stream);
+    return pl.mt == 1 ? launch_t<8, 1>(p, pl, stream) : launch_t<8, 2>(p, pl, stream);
 }
 
 }  // namespace luxcuda

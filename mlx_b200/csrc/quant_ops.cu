@@ -5,6 +5,7 @@
 // they are written for exactness and coalesced access, not for peak speed.
 #include <cuda_bf16.h>
 
+#include "dequant.cuh"
 #include "internal.h"
 
 namespace luxcuda {
@@ -53,15 +54,35 @@ __global__ void dequantize_kernel(const uint32_t* __restrict__ wq, const void* _
     for (; w < words; w += stride) {
         const int n = (int)(w / wpr), kw = (int)(w % wpr);
         const uint32_t v = wq[w];
-        for (int j = 0; j < per; j++) {
-            const int k = kw * per + j;
-            const uint32_t q = (v >> (bits * j)) & ((1u << bits) - 1);
-            const size_t gi = (size_t)n * gpr + k / group;
-            if (OUT_BF16) {
-                // one bf16 FMA: the correctly rounded bf16 of the exact s*q + b
-                const __nv_bfloat16 s = ((const __nv_bfloat16*)scales)[gi], b = ((const __nv_bfloat16*)biases)[gi];
-                ((__nv_bfloat16*)out)[(size_t)n * K + k] = __hfma(__float2bfloat16_rn((float)q), s, b);
+        if (OUT_BF16) {
+            // same in-register dequantiser as the matmul kernels (dequant.cuh), so the
+            // bit-exactness check of the dequantised weights covers their arithmetic
+            const size_t gi = (size_t)n * gpr + (kw * per) / group;
+            const uint32_t s = ((const uint16_t*)scales)[gi], b = ((const uint16_t*)biases)[gi];
+            __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)n * K + (size_t)kw * per;
+            const bool fast = scale_fast_ok(s);
+            if (bits == 4) {
+                uint32_t r[4];
+                if (fast) dequant4_fast(v, scale_x2_133(s), scale_x2_129(s), dup_bf16(b), r);
+                else dequant4_general(v, dup_bf16(s), dup_bf16(b), r);
+                for (int i = 0; i < 4; i++) {  // r[i] = (w^_i, w^_{i+4})
+                    ((uint16_t*)o)[i] = (uint16_t)(r[i] & 0xFFFFu);
+                    ((uint16_t*)o)[i + 4] = (uint16_t)(r[i] >> 16);
+                }
             } else {
+                uint32_t r[2];
+                if (fast) dequant8_fast(v, scale_x2_133(s), dup_bf16(b), r);
+                else dequant8_general(v, dup_bf16(s), dup_bf16(b), r);
+                ((uint16_t*)o)[0] = (uint16_t)(r[0] & 0xFFFFu);  // r[0] = (w^_0, w^_2), r[1] = (w^_1, w^_3)
+                ((uint16_t*)o)[2] = (uint16_t)(r[0] >> 16);
+                ((uint16_t*)o)[1] = (uint16_t)(r[1] & 0xFFFFu);
+                ((uint16_t*)o)[3] = (uint16_t)(r[1] >> 16);
+            }
+        } else {
+            for (int j = 0; j < per; j++) {
+                const int k = kw * per + j;
+                const uint32_t q = (v >> (bits * j)) & ((1u << bits) - 1);
+                const size_t gi = (size_t)n * gpr + k / group;
                 const float s = load_sb(scales, gi, sb_dtype), b = load_sb(biases, gi, sb_dtype);
                 ((float*)out)[(size_t)n * K + k] = __fadd_rn(__fmul_rn(s, (float)q), b);
             }

@@ -218,3 +218,28 @@ def test_rms_norm(ctx, oracle):
     got, want = oracle.from_bf16(bo.to_host()), oracle.from_bf16(oracle.rms_norm(x, eps=1e-6))
     assert np.abs(got - want).max() <= 2 ** -7 * np.abs(want).max()  # one bf16 ulp of the largest value
     bi.free(); bo.free()
+
+
+@pytest.mark.parametrize("bits,group", [(4, 64), (8, 128), (4, 32)])
+def test_scale_extremes_bit_exact(ctx, oracle, bits, group):
+    """Scales outside the range of the fast in-register dequantiser (zero,
+    subnormal, >= 2^-5, huge, negative) and right at its edges: dequantised
+    weights stay bit-exact and the matmul stays within tolerance."""
+    K, N = 512, 64
+    wq, s, b = oracle.make_layer(N, K, bits, group, oracle.BF16, config_id=12)
+    special = np.array([0.0, 1.0, 0.03125, 0.0311, 1e-39, -0.01, 3.0e4, 2.0 ** -126, 2.0 ** -120, -0.5, 0.0078125],
+                       np.float32)
+    sf = oracle.from_bf16(s)
+    sf.reshape(-1)[:special.size * 3:3] = special
+    s = oracle.to_bf16(sf)
+    b = oracle.to_bf16(oracle.gen_normal(5, b.shape, 0.0, 0.05))
+    bw, bs, bb = ctx.upload(wq), ctx.upload(s), ctx.upload(b)
+    bo = ctx.empty((N, K), np.uint16)
+    ctx.dequantize(bw, bs, bb, bo, N, K, bits, group, BF16, BF16)
+    assert np.array_equal(bo.to_host(), oracle.dequantize(wq, s, b, K, bits, group, oracle.BF16))
+    for h in (bw, bs, bb, bo):
+        h.free()
+    x = oracle.make_x(3, K, oracle.BF16, config_id=12)
+    y, kern = run_qmatmul(ctx, x, wq, s, b, bits, group, F32)
+    assert kern.startswith("qmv_mma")
+    check(oracle, y, x, wq, s, b, bits, group, oracle.BF16)
