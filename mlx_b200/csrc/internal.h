@@ -163,6 +163,8 @@ cudaError_t launch_qmv_simt(const QmmArgs& a, cudaStream_t stream, const char** 
 // prefill GEMM, bf16 activations: TMA + tcgen05 + TMEM
 bool qmm_tc_supported(const QmmArgs& a);
 cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, const char** name);
+// non-zero once a kernel gave up on one of its bounded waits since the last call (clears it)
+int take_device_error();
 
 cudaError_t launch_dequantize(const uint32_t* wq, const void* scales, const void* biases, void* out, int N, int K,
                               int bits, int group, int sb_dtype, int out_dtype, cudaStream_t stream);

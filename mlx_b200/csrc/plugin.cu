@@ -100,6 +100,10 @@ LuxBackendError sync(LuxBackendContext* ctx) {
     if (!c) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     DeviceGuard g(c->dev->device());
     LUX_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    if (take_device_error()) {
+        set_last_error("a kernel timed out on an internal wait and returned early; results are invalid");
+        return LUX_BACKEND_ERROR_INTERNAL;
+    }
     return LUX_BACKEND_OK;
 }
 
@@ -180,6 +184,10 @@ LuxBackendError buffer_copy_to_host(LuxBackendContext* ctx, LuxBackendBuffer* bu
     DeviceGuard g(c->dev->device());
     LUX_CUDA_TRY(cudaMemcpyAsync(dst, b->ptr, n, cudaMemcpyDeviceToHost, c->stream));
     LUX_CUDA_TRY(cudaStreamSynchronize(c->stream));
+    if (take_device_error()) {
+        set_last_error("a kernel timed out on an internal wait and returned early; results are invalid");
+        return LUX_BACKEND_ERROR_INTERNAL;
+    }
     return LUX_BACKEND_OK;
 }
 
