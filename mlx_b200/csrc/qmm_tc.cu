@@ -47,10 +47,18 @@ constexpr int kStages = 4;
 constexpr int kTileN = 128;        // rows of W per tile (MMA M)
 constexpr int kMaxBM = 256;        // rows of x per tile (MMA N)
 constexpr int kABytes = kTileN * 128;
-constexpr int kNumThreads = 320;
+constexpr int kDqWarps = 8;         // dequantising warps: kDqWarps/4 threads per row of the tile
+constexpr int kDqThreads = kDqWarps * 32;
+constexpr int kTpr = kDqWarps / 4; // threads per row
+constexpr int kCpt = 8 / kTpr;     // 16-byte output chunks (8 weights) per thread per stage
+constexpr int kNumThreads = 128 + kDqThreads + 64;
+constexpr int kTmaWarp = 4 + kDqWarps, kMmaWarp = 5 + kDqWarps;
 constexpr uint32_t kSpinLimit = 1u << 20;
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16_ca(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
 __device__ __forceinline__ void mbar_init(uint64_t* b, uint32_t n) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(n));
 }
@@ -144,6 +152,18 @@ struct GemmParams {
     uint32_t tmem_cols;      // allocated TMEM columns (power of two >= 32), 2 accumulators of tmem_cols/2
 };
 
+#ifdef QMM_TRACE
+__device__ unsigned long long g_qtrace[32];
+__device__ __forceinline__ unsigned long long qgt() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define QT_MARK(i) do { if (blockIdx.x == 0) g_qtrace[i] = qgt(); } while (0)
+#define QT_BEGIN long long _qt0 = (long long)qgt()
+#define QT_ADD(i) do { if (blockIdx.x == 0) { long long _t = (long long)qgt(); atomicAdd(&g_qtrace[i], (unsigned long long)(_t - _qt0)); _qt0 = _t; } } while (0)
+#else
+#define QT_BEGIN do {} while (0)
+#define QT_MARK(i) do {} while (0)
+#define QT_ADD(i) do {} while (0)
+#endif
+
 struct SmemLayout {
     uint64_t full_a[kStages], full_b[kStages], empty[kStages], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
@@ -151,8 +171,8 @@ struct SmemLayout {
 };
 
 // eight dequantised weights (natural k order) from one 4-bit word / two 8-bit words
-template <int BITS>
-__device__ __forceinline__ uint4 dequant_chunk(const uint32_t* w, uint32_t s_bits, uint32_t b_bits, bool fast) {
+template <int BITS, bool fast>
+__device__ __forceinline__ uint4 dequant_chunk(const uint32_t* w, uint32_t s_bits, uint32_t b_bits) {
     uint4 o;
     const uint32_t b2 = dup_bf16(b_bits);
     if (BITS == 4) {
@@ -181,6 +201,26 @@ __device__ __forceinline__ uint4 dequant_chunk(const uint32_t* w, uint32_t s_bit
     return o;
 }
 
+// One thread's share of a k-stage: kCpt chunks of 8 weights -> swizzled 16-byte stores into its A row.
+template <int BITS, bool FAST>
+__device__ __forceinline__ void dequant_store(const uint32_t* w, const uint32_t* sc, const uint32_t* bi, unsigned char* dst,
+                                              int part, int r7) {
+    constexpr int WPC = kBK * BITS / 32 / 8;   // packed words per chunk
+    constexpr int KPT = kBK / kTpr;
+#pragma unroll
+    for (int c = 0; c < kCpt; c++) {
+        const int q = (KPT > 32 && c >= 4) ? 1 : 0;
+        const uint4 v = dequant_chunk<BITS, FAST>(&w[c * WPC], sc[q], bi[q]);
+        *reinterpret_cast<uint4*>(dst + (((part * kCpt + c) ^ r7) << 4)) = v;
+    }
+}
+// the general (any scale) variant is kept out of line so the common path stays branch-free and small
+template <int BITS>
+__device__ __noinline__ void dequant_store_general(const uint32_t* w, const uint32_t* sc, const uint32_t* bi,
+                                                   unsigned char* dst, int part, int r7) {
+    dequant_store<BITS, false>(w, sc, bi, dst, part, r7);
+}
+
 template <int BITS>
 __global__ void __launch_bounds__(kNumThreads, 1)
 qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ GemmParams p) {
@@ -191,16 +231,18 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
     unsigned char* sB = smem + kStages * kABytes;              // [kStages][bm rows][128 B], swizzled (TMA)
     const uint32_t b_bytes = (uint32_t)p.bm * 128;
     SmemLayout* sl = reinterpret_cast<SmemLayout*>(sB + kStages * (size_t)kMaxBM * 128);
+    unsigned char* sSB = reinterpret_cast<unsigned char*>(sl) + 256;   // [kDqThreads][2 buffers][scales 16 B | biases 16 B]
     volatile int* abort_flag = &sl->abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) QT_MARK(16);
     const int nks = p.K / kBK;
     const int total_tiles = p.n_tiles * p.m_tiles;
     const uint32_t acc_cols = p.tmem_cols / 2;
 
     if (tid == 0) {
         for (int s = 0; s < kStages; s++) {
-            mbar_init(&sl->full_a[s], 128);
+            mbar_init(&sl->full_a[s], kDqThreads);
             mbar_init(&sl->full_b[s], 1);
             mbar_init(&sl->empty[s], 1);
         }
@@ -211,13 +253,14 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
         sl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 9) tmem_alloc(&sl->tmem_base, p.tmem_cols);
+    if (warp == kMmaWarp) tmem_alloc(&sl->tmem_base, p.tmem_cols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = sl->tmem_base;
+    if (tid == 0) QT_MARK(17);
 
-    if (warp == 8) {
+    if (warp == kTmaWarp) {
         // ---------------- TMA producer: x tiles ----------------
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
@@ -228,13 +271,15 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
                 for (int ks = 0; ks < nks; ks++, it++) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
+                    QT_BEGIN;
                     if (!mbar_wait(&sl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+                    QT_ADD(0);
                     mbar_expect_tx(&sl->full_b[s], b_bytes);
                     tma_load_2d(sB + (size_t)s * kMaxBM * 128, &tmap_x, ks * kBK, m0, &sl->full_b[s]);
                 }
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == kMmaWarp) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(kTileN, p.bm);
@@ -242,13 +287,17 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, tile_i++) {
                 const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
-                if (!mbar_wait(&sl->tmem_empty[acc], acc_ph ^ 1, abort_flag)) break;
+                { QT_BEGIN; if (!mbar_wait(&sl->tmem_empty[acc], acc_ph ^ 1, abort_flag)) break; QT_ADD(4); }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * acc_cols;
                 for (int ks = 0; ks < nks; ks++, it++) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1;
-                    if (!mbar_wait(&sl->full_a[s], ph, abort_flag) || !mbar_wait(&sl->full_b[s], ph, abort_flag)) { ok = false; break; }
+                    QT_BEGIN;
+                    if (!mbar_wait(&sl->full_a[s], ph, abort_flag)) { ok = false; break; }
+                    QT_ADD(1);
+                    if (!mbar_wait(&sl->full_b[s], ph, abort_flag)) { ok = false; break; }
+                    QT_ADD(2);
                     tc_fence_after();
                     const uint64_t da = umma_desc_sw128(s32(sA + (size_t)s * kABytes));
                     const uint64_t db = umma_desc_sw128(s32(sB + (size_t)s * kMaxBM * 128));
@@ -256,51 +305,129 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
                     for (int kk = 0; kk < kBK / 16; kk++)  // 32 bytes (2 x 16 B units) further along K per step
                         tc_mma(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
                     tc_commit(&sl->empty[s]);  // arrives when the MMAs above have finished reading the stage
+                    QT_ADD(3);
                 }
                 if (ok) tc_commit(&sl->tmem_full[acc]);
+                QT_MARK(18 + (tile_i & 1));
             }
         }
     } else if (warp >= 4) {
-        // ---------------- dequantisers: thread r owns row n0 + r ----------------
-        const int r = tid - 128;
+        // ---------------- dequantisers: kTpr threads per row n0 + r, kCpt chunks of 8 weights each ----------------
+        const int d = tid - 128;
+        const int r = d / kTpr, part = d % kTpr;        // part: which kCpt chunks of the 64-weight stage (adjacent lanes share a row)
+        constexpr int WPT = WPS / kTpr;                 // packed words per thread per stage
+        constexpr int KPT = kBK / kTpr;                 // weights per thread per stage
         const size_t row_bytes = (size_t)p.K * BITS / 8;
         const int gpr = p.K >> p.gshift;
         const uint32_t row_off = (uint32_t)(r >> 3) * 1024 + (uint32_t)(r & 7) * 128;
+        // scales/biases: one strided 2-byte load per row and stage would swamp the L1 tag pipe (every
+        // thread is on its own row), so when rows of the scale matrix are 16-byte multiples they are
+        // fetched eight groups at a time into a per-thread shared-memory slot
+        const bool vec_sb = (gpr & 7) == 0;
+        const int sps = (8 << p.gshift) / kBK;          // k-stages covered by eight groups: 4, 8 or 16
+        const uint32_t sb_slot = s32(sSB) + d * 64;
         uint32_t it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             const int n = min((tile / p.m_tiles) * kTileN + r, p.N - 1);
-            const uint4* wrow = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(p.wq) + (size_t)n * row_bytes);
+            const uint32_t* wrow = reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned char*>(p.wq) + (size_t)n * row_bytes) + part * WPT;
             const uint16_t* srow = reinterpret_cast<const uint16_t*>(p.scales) + (size_t)n * gpr;
             const uint16_t* brow = reinterpret_cast<const uint16_t*>(p.biases) + (size_t)n * gpr;
-            uint4 wn[WPS / 4];
-            uint32_t sn[2], bn[2];
-            auto fetch = [&](int ks) {
+            // kPre stages of packed words + scale/bias are kept in flight in registers (the loads are
+            // L2 hits, but their latency under load is several k-stages long)
+            constexpr int kPre = 4;
+            constexpr int NS = KPT > 32 ? 2 : 1;
+            uint32_t wr[kPre][WPT], sr[kPre][NS], br[kPre][NS];
+            auto fetch = [&](int ks, uint32_t (&w)[WPT], uint32_t (&sc)[NS], uint32_t (&bi)[NS]) {
+                if (ks >= nks) return;
+#ifdef QMM_NOLOAD_W
+                for (int i = 0; i < WPT; i++) w[i] = 0x12345678u * (ks + i);
+                if (false)
+#endif
+                if (WPT >= 4) {
+                    // straight into the registers that hold the stage (no copy that would wait for the load)
 #pragma unroll
-                for (int i = 0; i < WPS / 4; i++) wn[i] = __ldg(wrow + ks * (WPS / 4) + i);
-                const int g0 = (ks * kBK) >> p.gshift, g1 = (ks * kBK + 32) >> p.gshift;
-                sn[0] = __ldg(srow + g0); bn[0] = __ldg(brow + g0);
-                sn[1] = __ldg(srow + g1); bn[1] = __ldg(brow + g1);
+                    for (int i = 0; i < WPT / 4; i++)
+                        asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3])
+                                     : "l"(wrow + ks * WPS + 4 * i));
+                } else {
+                    asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(w[0]), "=r"(w[WPT - 1]) : "l"(wrow + ks * WPS));
+                }
+                const int k0 = ks * kBK + part * KPT;
+#ifdef QMM_NOLOAD_SB
+                sc[0] = 0x3C00; bi[0] = 0xBC00; sc[NS - 1] = 0x3C00; bi[NS - 1] = 0xBC00;
+                return;
+#endif
+                if (vec_sb) {
+                    // eight groups of scales and biases at a time, 16-byte cp.async into this thread's slot
+                    if ((ks & (sps - 1)) == 0) {
+                        const int j = ks / sps;
+                        cp_async16_ca(sb_slot + (j & 1) * 32, srow + 8 * j);
+                        cp_async16_ca(sb_slot + (j & 1) * 32 + 16, brow + 8 * j);
+                    }
+                    return;
+                }
+#pragma unroll
+                for (int q = 0; q < NS; q++) {
+                    const int gi = (k0 + q * 32) >> p.gshift;
+                    sc[q] = __ldg(srow + gi);
+                    bi[q] = __ldg(brow + gi);
+                }
             };
-            fetch(0);
-            for (int ks = 0; ks < nks; ks++, it++) {
-                uint32_t w[WPS];
-#pragma unroll
-                for (int i = 0; i < WPS / 4; i++) { w[4 * i] = wn[i].x; w[4 * i + 1] = wn[i].y; w[4 * i + 2] = wn[i].z; w[4 * i + 3] = wn[i].w; }
-                const uint32_t s0 = sn[0], s1 = sn[1], b0 = bn[0], b1 = bn[1];
-                if (ks + 1 < nks) fetch(ks + 1);
+            int ks_cur = 0;
+            auto stage = [&](const uint32_t (&w)[WPT], const uint32_t (&sc)[NS], const uint32_t (&bi)[NS]) -> bool {
                 const int s = it % kStages;
                 const uint32_t ph = (it / kStages) & 1;
-                if (!mbar_wait(&sl->empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+                QT_BEGIN;
+                if (!mbar_wait(&sl->empty[s], ph ^ 1, abort_flag)) return false;
+                if (d == 0) QT_ADD(8);
                 unsigned char* dst = sA + (size_t)s * kABytes + row_off;
-                const bool f0 = scale_fast_ok(s0), f1 = scale_fast_ok(s1);
+                uint32_t scv[NS], biv[NS];
 #pragma unroll
-                for (int c = 0; c < 8; c++) {
-                    const uint4 v = dequant_chunk<BITS>(&w[c * (WPS / 8)], c < 4 ? s0 : s1, c < 4 ? b0 : b1, c < 4 ? f0 : f1);
-                    *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = v;
+                for (int q = 0; q < NS; q++) { scv[q] = sc[q]; biv[q] = bi[q]; }
+#ifdef QMM_NOLOAD_SB
+                if (false) {
+#else
+                if (vec_sb) {
+#endif
+                    const int ks = ks_cur;
+                    if ((ks & (sps - 1)) == 0) {  // first stage of a block of eight groups: its copy must have landed
+                        asm volatile("cp.async.wait_all;" ::: "memory");
+                    }
+                    const uint32_t base = sb_slot + ((ks / sps) & 1) * 32;
+#pragma unroll
+                    for (int q = 0; q < NS; q++) {
+                        const uint32_t off = ((((ks & (sps - 1)) * kBK + part * KPT + q * 32) >> p.gshift) << 1);
+                        uint16_t sv, bv;
+                        asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sv) : "r"(base + off));
+                        asm volatile("ld.shared.u16 %0, [%1+16];" : "=h"(bv) : "r"(base + off));
+                        scv[q] = sv; biv[q] = bv;
+                    }
                 }
+                bool fast = true;
+#pragma unroll
+                for (int q = 0; q < NS; q++) fast = fast && scale_fast_ok(scv[q]);
+                if (fast) dequant_store<BITS, true>(w, scv, biv, dst, part, r & 7);
+                else dequant_store_general<BITS>(w, scv, biv, dst, part, r & 7);
+                if (d == 0) QT_ADD(9);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA
                 mbar_arrive(&sl->full_a[s]);
+                if (d == 0) QT_ADD(10);
+                it++;
+                return true;
+            };
+#pragma unroll
+            for (int i = 0; i < kPre; i++) fetch(i, wr[i], sr[i], br[i]);
+            for (int ks = 0; ks < nks && ok; ks += kPre) {
+#pragma unroll
+                for (int i = 0; i < kPre; i++) {
+                    if (ks + i < nks) {
+                        ks_cur = ks + i;
+                        if (!stage(wr[i], sr[i], br[i])) { ok = false; break; }
+                        { QT_BEGIN; fetch(ks + i + kPre, wr[i], sr[i], br[i]); if (d == 0) QT_ADD(11); }
+                    }
+                }
             }
         }
     } else {
@@ -310,23 +437,36 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
             const uint32_t acc = tile_i & 1, acc_ph = (tile_i >> 1) & 1;
             const int n = (tile / p.m_tiles) * kTileN + warp * 32 + lane;
             const int m0 = (tile % p.m_tiles) * p.bm;
+            QT_BEGIN;
             if (!mbar_wait(&sl->tmem_full[acc], acc_ph, abort_flag)) break;
+            if (tid == 0) QT_ADD(12);
             tc_fence_after();
+            // this thread: column n of y, rows m0 .. m0+bm-1 (32 consecutive n per warp: 64-byte row segments)
+            const int m_end = min(p.bm, p.M - m0);
             for (int c0 = 0; c0 < p.bm; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + acc * acc_cols + c0, v);
                 if (n < p.N) {
+                    const size_t idx0 = (size_t)(m0 + c0) * p.N + n;
+                    if (p.y_bf16) {
+                        __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(p.y) + idx0;
+                        if (c0 + 32 <= m_end) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int m = m0 + c0 + j;
-                        if (c0 + j < p.bm && m < p.M) {
-                            const size_t idx = (size_t)m * p.N + n;
-                            if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(__uint_as_float(v[j]));
-                            else reinterpret_cast<float*>(p.y)[idx] = __uint_as_float(v[j]);
+                            for (int j = 0; j < 32; j++) yp[(size_t)j * p.N] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (c0 + j < m_end) yp[(size_t)j * p.N] = __float2bfloat16_rn(__uint_as_float(v[j]));
                         }
+                    } else {
+                        float* yp = reinterpret_cast<float*>(p.y) + idx0;
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (c0 + j < m_end) yp[(size_t)j * p.N] = __uint_as_float(v[j]);
                     }
                 }
             }
+            if (tid == 0) QT_ADD(13);
             tc_fence_before();
             mbar_arrive(&sl->tmem_empty[acc]);
         }
@@ -334,8 +474,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
     // ---------------- teardown ----------------
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) QT_MARK(20);
     if (tid == 0 && sl->abort_flag) *p.error = 1;
-    if (warp == 9) {
+    if (warp == kMmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem_base, p.tmem_cols);
     }
@@ -393,7 +534,8 @@ bool make_gemm_plan(const QmmArgs& a, GemmPlan* pl) {
     uint32_t acc = 32;
     while ((int)acc < pl->bm) acc *= 2;
     pl->tmem_cols = 2 * acc;
-    pl->smem = 1024 + (size_t)kStages * (kABytes + kMaxBM * 128) + sizeof(SmemLayout) + 64;
+    pl->smem = 1024 + (size_t)kStages * (kABytes + kMaxBM * 128) + 256 + (size_t)kDqThreads * 64;
+    static_assert(sizeof(SmemLayout) <= 256, "barrier block");
     return encode_tiled_fn() != nullptr;
 }
 
