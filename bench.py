@@ -153,6 +153,43 @@ def run_reference(args, rank):
     }))
 
 
+def prefill_legs(ctx, O, BF16, peaks):
+    """Tensor-bound legs (BASELINE.json configs[2] and [3] at one GPU): TFLOP/s = 2*M*N*K / device time.
+    Rotating input sets keep every launch's operands colder than L2 capacity in total."""
+    out = {}
+    for name, (M, K, N, bits, group, R, iters) in {
+        "prefill_4bit_M2048_K4096_N4096": (2048, 4096, 4096, 4, 64, 4, 10),
+        "gemm_8bit_M512_K8192_N28672": (512, 8192, 28672, 8, 128, 2, 5),
+    }.items():
+        sets = []
+        for r in range(R):
+            wq, s, b = O.make_layer(N, K, bits, group, O.BF16, config_id=3 if bits == 4 else 4, layer=r)
+            x = O.make_x(M, K, O.BF16, config_id=3 if bits == 4 else 4, layer=r)
+            sets.append((ctx.upload(x), ctx.upload(wq), ctx.upload(s), ctx.upload(b), ctx.empty((M, N), np.uint16)))
+
+        def go():
+            for (bx, bw, bs, bb, by) in sets:
+                ctx.qmatmul(bx, bw, bs, bb, by, M, K, N, bits, group, BF16, BF16, BF16)
+        for _ in range(3):
+            go()
+        ctx.sync()
+        ctx.timer_record(6)
+        for _ in range(iters):
+            go()
+        ctx.timer_record(7)
+        ms = ctx.timer_elapsed_ms(6, 7) / (iters * R)
+        tf = 2.0 * M * N * K / ms / 1e9
+        out[name] = {"us_per_launch": ms * 1e3, "TFLOPS": tf, "kernel": ctx.last_kernel(),
+                     "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                  "frac": tf / peaks["bf16_tflops"], "frac_of_sustained": tf / peaks["bf16_tflops_sustained"],
+                                  "frac_of_nominal_2250": tf / 2250.0},
+                     "input_bytes_rotated": R * (M * K * 2 + N * K * bits // 8 + 4 * N * K // group + M * N * 2)}
+        for t in sets:
+            for h in t:
+                h.free()
+    return out
+
+
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
@@ -217,6 +254,7 @@ def run_ours(args, rank, world):
     # one sweep = len(M_SWEEP) * R launches, recorded once as a CUDA graph per M
     l0 = ctx.launch_count()
     graphs = {}
+    # one process per GPU: the NCCL all-gathers are launched eagerly (a capture of them hung a 2-rank run)
     use_graph = world == 1 and not args.no_graph
     if use_graph:
         for M in M_SWEEP:
@@ -313,9 +351,16 @@ def run_ours(args, rank, world):
     h2d = sum(M * K_DEC * 2 for M in M_SWEEP) * R_SETS * e2e_reps
     d2h = sum(M * n_total * 2 for M in M_SWEEP) * R_SETS * e2e_reps
 
+    peaks, which = measured_peaks()
+    prefill = prefill_legs(ctx, O, BF16, peaks) if (world == 1 and not args.kernel_only) else None
+    if dist is not None:
+        ctx.sync()
+        dist.barrier()
+        if comm:
+            q.shard_comm_destroy(comm)
+        dist.destroy_process_group()
     if rank != 0:
         return
-    peaks, which = measured_peaks()
     peak = float(peaks["hbm_gbs"])
     dom = max(M_SWEEP, key=lambda M: 1)  # all launches are the same kernel family; report the sweep average
     avg_us = ms_total * 1e3 / n_launches_alg
@@ -337,6 +382,7 @@ def run_ours(args, rank, world):
                      "alg_bytes_per_launch": {str(M): alg_bytes(M) for M in M_SWEEP},
                      "traffic": args.traffic_bytes},
         "per_M": {str(M): per_m[M] for M in M_SWEEP},
+        "prefill": prefill,
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "calls": e2e_calls, "us_per_call": ms_e2e * 1e3 / max(1, e2e_calls),
