@@ -179,6 +179,29 @@ LUX_GPU_BACKEND_EXPORT const lux_gpu_quant_vtbl* lux_gpu_cuda_quant_vtbl(void);
  * mirror the struct by hand: sizeof(vtbl), offsetof(op_matmul_f32),
  * offsetof(op_ntt_forward), offsetof(_reserved), sizeof(desc). */
 LUX_GPU_BACKEND_EXPORT void lux_gpu_cuda_abi_layout(uint32_t out[5]);
+/* Decode-regime quantized matmul (bf16 x, bf16 scales/biases, 1 <= M <= 16) that allocates nothing.
+ * No counterpart in the reference.
+ *
+ * For hosts that must not allocate device memory once they are running: a serving process that
+ * has handed every free byte of HBM to its own arena (so a driver allocation would fail or stall
+ * the device while it trims), or code running under a no-allocation policy after start-up.  The
+ * ordinary qmatmul grows a per-context workspace through the plugin's allocator the first time a
+ * shape needs it; this variant instead uses a 4 MiB scratch array compiled into the library
+ * image.  Every GPU that loads the library carries those 4 MiB until the process exits.
+ *
+ * Same arguments and results as qmatmul (bit-identical output); the caller still owns x, wq,
+ * scales, biases and y.  Shapes whose scratch need exceeds 4 MiB (only layers with very few
+ * rows and a very long K) are refused with INVALID_ARGUMENT and a message in
+ * lux_gpu_cuda_last_error(); shapes the decode kernel does not take return NOT_SUPPORTED.
+ * The first call on a device looks up the scratch array's device address (once per device);
+ * make that first call before starting any stream capture.  All calls on a device share the one
+ * array: it keeps whatever the last call left, the kernel itself restores the part that must be
+ * zero, and two calls that overlap on the GPU (different contexts of one device) would corrupt
+ * each other -- run them one after the other. */
+LUX_GPU_BACKEND_EXPORT LuxBackendError lux_gpu_cuda_qmatmul_decode_noalloc(
+    LuxBackendContext* ctx, LuxBackendBuffer* x, LuxBackendBuffer* wq, LuxBackendBuffer* scales,
+    LuxBackendBuffer* biases, LuxBackendBuffer* y, int M, int K, int N, int bits, int group,
+    LuxBackendDtype y_dtype);
 /* Last error text of the calling thread ("" if none). */
 LUX_GPU_BACKEND_EXPORT const char* lux_gpu_cuda_last_error(void);
 

@@ -574,4 +574,76 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
     return pl.mt == 1 ? launch_t<8, 1>(p, pl, stream) : launch_t<8, 2>(p, pl, stream);
 }
 
+
+// ---------------------------------------------------------------------------------
+// Decode GEMV without any allocation: the scratch lives in the library image.
+// ---------------------------------------------------------------------------------
+namespace {
+// Arrival counters + k-split partials of the decode kernel, 4 MiB per GPU that loads the
+// library (held until the process exits).  Zero at load; every launch leaves the counters zero.
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+std::mutex g_static_mu;
+void* g_static_ptr[64];  // device address of g_static_scratch, per device ordinal
+
+// The array's name is only a host-side handle: the address a kernel may use has to be asked
+// for, once per device, with that device current.
+cudaError_t static_scratch_ptr(int device, void** out) {
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_ptr[device]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return e;
+        g_static_ptr[device] = p;
+    }
+    *out = g_static_ptr[device];
+    return cudaSuccess;
+}
+}  // namespace
 }  // namespace luxcuda
+
+extern "C" LUX_GPU_BACKEND_EXPORT LuxBackendError lux_gpu_cuda_qmatmul_decode_noalloc(
+    LuxBackendContext* ctx, LuxBackendBuffer* x, LuxBackendBuffer* wq, LuxBackendBuffer* scales, LuxBackendBuffer* biases,
+    LuxBackendBuffer* y, int M, int K, int N, int bits, int group, LuxBackendDtype y_dtype) {
+    using namespace luxcuda;
+    Context* c = as_ctx(ctx);
+    Buffer *bx = as_buf(x), *bw = as_buf(wq), *bs = as_buf(scales), *bb = as_buf(biases), *by = as_buf(y);
+    if (!c || !bx || !bw || !bs || !bb || !by) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (y_dtype != LUX_DTYPE_BFLOAT16 && y_dtype != LUX_DTYPE_FLOAT32) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (M < 1 || M > 16 || K < 1 || N < 1 || (bits != 4 && bits != 8) || (group != 32 && group != 64 && group != 128) || K % group) {
+        set_last_error("qmatmul_decode_noalloc: needs 1 <= M <= 16, bits 4|8, group 32|64|128, K a multiple of group");
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    }
+    const size_t ys = y_dtype == LUX_DTYPE_BFLOAT16 ? 2 : 4;
+    if ((size_t)M * K * 2 > bx->bytes || (size_t)N * K * bits / 8 > bw->bytes || (size_t)N * (K / group) * 2 > bs->bytes ||
+        (size_t)N * (K / group) * 2 > bb->bytes || (size_t)M * N * ys > by->bytes) {
+        set_last_error("qmatmul_decode_noalloc: a buffer is smaller than its shape needs");
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    }
+    QmmArgs a{bx->ptr, (const uint32_t*)bw->ptr, bs->ptr, bb->ptr, by->ptr, M, K, N, bits, group,
+              LUX_DTYPE_BFLOAT16, LUX_DTYPE_BFLOAT16, (int)y_dtype};
+    std::lock_guard<std::mutex> lk(c->mu);
+    DeviceGuard g(c->dev->device());
+    const size_t need = qmv_mma_workspace_bytes(a, c->dev->sm_count);
+    if (need == 0) {
+        set_last_error("qmatmul_decode_noalloc: shape not taken by the decode kernel (K must be a multiple of %d)", 1024 / bits);
+        return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    }
+    if (need > kStaticScratchBytes) {
+        set_last_error("qmatmul_decode_noalloc: this shape needs %zu bytes of scratch, the built-in scratch holds %zu",
+                       need, kStaticScratchBytes);
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    }
+    void* scratch = nullptr;
+    cudaError_t e = static_scratch_ptr(c->dev->device(), &scratch);
+    if (e != cudaSuccess) return map_cuda_error(e, "cudaGetSymbolAddress(static scratch)");
+    const char* name = "";
+    e = launch_qmv_mma(a, scratch, c->dev->sm_count, c->stream, &name);
+    if (e != cudaSuccess) return map_cuda_error(e, name);
+    c->last_kernel = name;
+    c->launches++;
+    bx->last_stream = bw->last_stream = bs->last_stream = bb->last_stream = by->last_stream = c->stream;
+    return LUX_BACKEND_OK;
+}

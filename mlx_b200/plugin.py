@@ -131,7 +131,7 @@ class QuantVtbl(C.Structure):  # include/lux_cuda_quant.h: lux_gpu_quant_vtbl
 
 
 EXPORTED_SYMBOLS = ("lux_gpu_backend_init", "lux_gpu_cuda_quant_vtbl", "lux_gpu_cuda_abi_layout",
-                    "lux_gpu_cuda_last_error")
+                    "lux_gpu_cuda_last_error", "lux_gpu_cuda_qmatmul_decode_noalloc")
 
 
 class BackendError(RuntimeError):
@@ -158,6 +158,8 @@ class Plugin:
         self.lib.lux_gpu_backend_init.argtypes = [C.POINTER(BackendDesc)]
         self.lib.lux_gpu_cuda_quant_vtbl.restype = C.POINTER(QuantVtbl)
         self.lib.lux_gpu_cuda_last_error.restype = C.c_char_p
+        self.lib.lux_gpu_cuda_qmatmul_decode_noalloc.restype = _i
+        self.lib.lux_gpu_cuda_qmatmul_decode_noalloc.argtypes = [_vp] * 6 + [_i] * 6
         self.desc = BackendDesc()
         self.available = bool(self.lib.lux_gpu_backend_init(C.byref(self.desc)))
         if self.desc.abi_version != ABI_VERSION:
@@ -299,6 +301,13 @@ class Context:
         self.plugin.check(self.plugin.quant.qmatmul(self.handle, x.handle, wq.handle, scales.handle, biases.handle,
                                                     y.handle, M, K, N, bits, group, x_dtype, sb_dtype, y_dtype),
                           "qmatmul")
+
+    def qmatmul_decode_noalloc(self, x, wq, scales, biases, y, M, K, N, bits, group, y_dtype):
+        """Decode matmul through the entry point that uses the library's built-in scratch
+        instead of the allocator (see include/lux_cuda_quant.h)."""
+        self.plugin.check(self.plugin.lib.lux_gpu_cuda_qmatmul_decode_noalloc(
+            self.handle, x.handle, wq.handle, scales.handle, biases.handle, y.handle, M, K, N, bits, group, y_dtype),
+            "qmatmul_decode_noalloc")
 
     def qmatmul_dispatch(self, x, wq, scales, biases, y, M, K, N, bits, group, x_dtype, sb_dtype, y_dtype):
         """Same op through kernel_load / kernel_dispatch of the base vtable."""
