@@ -15,22 +15,22 @@
 //   D         = 128 lanes x BM columns of fp32 in TMEM.
 // With W on the 128-lane side a weight is dequantised once per BM = 256 rows of
 // x, which keeps the integer pipe (the scarce one) at about a quarter load.
-// TMEM (512 columns): D in columns [0, 256), an 8-slot ring of A k-stages
-// (64 weights = 32 columns each) in [256, 512).  Shared memory: a 6-stage ring
-// of B (32 KiB each).
+// TMEM (512 columns): D in columns [0, 256), a ring of A k-stages
+// (64 weights = 32 columns each) from column 256 on, one slot per k-stage in
+// flight.  Shared memory: the matching ring of B stages (32 KiB each).
 //
-// One persistent CTA per SM, 26 warps:
+// One persistent CTA per SM, 22 warps:
 //   warps 0-7   epilogue: warp w reads TMEM lanes 32*(w%4).., half w/4 of the
 //               columns, rounds to bf16/fp32, stores y[m][n];
-//   warps 8-23  dequantisers in four groups of four warps: group j owns the
-//               k-stages  = j (mod 4); inside a group warp q owns TMEM lanes
+//   warps 8-19  dequantisers in three groups of four warps: group j owns the
+//               pipeline stages = j (mod 3); inside a group warp q owns TMEM lanes
 //               32q.. (a warp may only touch its own lane quarter), so thread
 //               (q, lane) owns row n0 + 32q + lane: per owned stage it reads 32
 //               (4-bit) or 64 (8-bit) packed bytes + scale/bias from global
 //               memory (prefetched one owned stage ahead in registers),
 //               dequantises (dequant.cuh) and writes 32 TMEM columns;
-//   warp 24     TMA producer for x;
-//   warp 25     allocates TMEM, issues tcgen05.mma (one elected thread) and the
+//   warp 20     TMA producer for x;
+//   warp 21     allocates TMEM, issues tcgen05.mma (one elected thread) and the
 //               commits that release A slots / B stages and publish D.
 // Hand-over uses mbarriers; every wait is bounded: on a time-out the kernel
 // raises an error word (host-visible) and all roles drain and return.
@@ -48,15 +48,22 @@ namespace luxcuda {
 namespace {
 
 constexpr int kBK = 64;            // weights (k) per pipeline stage = one 128-byte swizzle row of bf16
-constexpr int kSlotsA = 8;         // A k-stages resident in TMEM
-constexpr int kStagesB = 6;        // B k-stages resident in shared memory
+#ifndef QMM_STAGES_B
+#define QMM_STAGES_B 3
+#endif
+constexpr int kStagesB = QMM_STAGES_B;  // k-stages in flight: B in shared memory, A in TMEM, one barrier pair per stage
 constexpr int kTileN = 128;        // rows of W per tile (MMA M)
 constexpr int kMaxBM = 256;        // rows of x per tile (MMA N)
-constexpr int kBBytes = kMaxBM * 128;
-constexpr int kEpiWarps = 8, kDqWarps = 16, kDqGroups = 4;
+constexpr int kSub = 2;            // 64-weight sub-blocks per pipeline stage (one barrier round per 128 k)
+constexpr int kBBytes = kMaxBM * 128;   // one sub-block of B
+constexpr int kEpiWarps = 8, kDqGroups = 3, kDqWarps = 4 * kDqGroups;
+// A dequantising group goes from stage s straight to stage s + kDqGroups.  Its wait for that slot is by
+// phase parity, which cannot tell "freed once more" from "two frees behind": the group must never be able
+// to get two ring rounds ahead of the MMA, i.e. kDqGroups <= kStagesB.
+static_assert(kDqGroups <= kStagesB, "parity waits would alias");
 constexpr int kTmaWarp = kEpiWarps + kDqWarps, kMmaWarp = kTmaWarp + 1;
 constexpr int kNumThreads = (kMmaWarp + 1) * 32;
-constexpr uint32_t kTmemCols = 512, kAColBase = 256, kAColsPerSlot = kBK / 2;
+constexpr uint32_t kTmemCols = 512, kAColBase = 256, kAColsPerSub = kBK / 2, kAColsPerSlot = kSub * kAColsPerSub;
 constexpr uint32_t kSpinLimit = 1u << 20;
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -80,7 +87,18 @@ __device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag) {
     for (uint32_t i = 0; i < kSpinLimit; i++) {
         if (mbar_try(b, parity)) return true;
+        if (i > 4) __nanosleep(40);  // waiting roles must not steal issue slots from the working ones
         if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+// Same bound, no back-off: for the one thread whose wake-up latency is on the tensor pipe's critical path.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* b, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < kSpinLimit * 8; i++) {
+        if (mbar_try(b, parity)) return true;
+        if ((i & 4095u) == 4095u && *abort_flag) return false;
     }
     *abort_flag = 1;
     return false;
@@ -164,7 +182,7 @@ struct GemmParams {
 };
 
 struct SmemLayout {
-    uint64_t full_a[kSlotsA], empty_a[kSlotsA], full_b[kStagesB], empty_b[kStagesB], tmem_full, tmem_empty;
+    uint64_t full[kStagesB], empty[kStagesB], tmem_full, tmem_empty;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -217,21 +235,18 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* sB = smem;  // [kStagesB][bm rows][128 B], swizzled (TMA)
     const uint32_t b_bytes = (uint32_t)p.bm * 128;
-    SmemLayout* sl = reinterpret_cast<SmemLayout*>(sB + (size_t)kStagesB * kBBytes);
+    SmemLayout* sl = reinterpret_cast<SmemLayout*>(sB + (size_t)kStagesB * kSub * kBBytes);
     volatile int* abort_flag = &sl->abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nks = p.K / kBK;
+    const int nks = p.K / kBK;                  // 64-weight sub-blocks along K
+    const int nst = (nks + kSub - 1) / kSub;    // pipeline stages per tile
     const int total_tiles = p.n_tiles * p.m_tiles;
 
     if (tid == 0) {
-        for (int s = 0; s < kSlotsA; s++) {
-            mbar_init(&sl->full_a[s], 128);
-            mbar_init(&sl->empty_a[s], 1);
-        }
         for (int s = 0; s < kStagesB; s++) {
-            mbar_init(&sl->full_b[s], 1);
-            mbar_init(&sl->empty_b[s], 1);
+            mbar_init(&sl->full[s], 128 + 1);  // 128 dequantising threads + the TMA producer (with its byte count)
+            mbar_init(&sl->empty[s], 1);        // one tcgen05.commit
         }
         mbar_init(&sl->tmem_full, 1);
         mbar_init(&sl->tmem_empty, kEpiWarps * 32);
@@ -250,14 +265,23 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
             uint32_t it = 0;
             bool ok = true;
+#ifdef QMM_MMA_ONLY
+            ok = false;
+#endif
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % p.m_tiles) * p.bm;
-                for (int ks = 0; ks < nks; ks++, it++) {
+                for (int st = 0; st < nst; st++, it++) {
                     const int sb = it % kStagesB;
                     const uint32_t ph = (it / kStagesB) & 1;
-                    if (!mbar_wait(&sl->empty_b[sb], ph ^ 1, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(&sl->full_b[sb], b_bytes);
-                    tma_load_2d(sB + (size_t)sb * kBBytes, &tmap_x, ks * kBK, m0, &sl->full_b[sb]);
+                    const int nsub = min(kSub, nks - st * kSub);
+                    if (!mbar_wait(&sl->empty[sb], ph ^ 1, abort_flag)) { ok = false; break; }
+#ifdef QMM_NO_TMA
+                    mbar_arrive(&sl->full[sb]);
+#else
+                    mbar_expect_tx(&sl->full[sb], b_bytes * nsub);
+                    for (int u = 0; u < nsub; u++)
+                        tma_load_2d(sB + ((size_t)sb * kSub + u) * kBBytes, &tmap_x, (st * kSub + u) * kBK, m0, &sl->full[sb]);
+#endif
                 }
             }
         }
@@ -265,29 +289,35 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(kTileN, p.bm);
-            uint32_t it = 0, tile_i = 0;
+            uint32_t tile_i = 0, slot = 0, phase = 0;
+            const uint64_t db0 = umma_desc_sw128(s32(sB));
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, tile_i++) {
                 if (!mbar_wait(&sl->tmem_empty, (tile_i & 1) ^ 1, abort_flag)) break;
                 tc_fence_after();
-                for (int ks = 0; ks < nks; ks++, it++) {
-                    const int sa = it % kSlotsA, sb = it % kStagesB;
-                    if (!mbar_wait(&sl->full_a[sa], (it / kSlotsA) & 1, abort_flag) ||
-                        !mbar_wait(&sl->full_b[sb], (it / kStagesB) & 1, abort_flag)) { ok = false; break; }
+                for (int st = 0; st < nst; st++) {
+                    const int nsub = min(kSub, nks - st * kSub);
+#ifndef QMM_MMA_ONLY
+                    if (!mbar_wait_spin(&sl->full[slot], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t db = umma_desc_sw128(s32(sB + (size_t)sb * kBBytes));
-                    const uint32_t a_tmem = tmem_base + kAColBase + sa * kAColsPerSlot;
+#endif
+                    for (int u = 0; u < nsub; u++) {
+                        const uint64_t db = db0 + (uint64_t)(slot * kSub + u) * (kBBytes >> 4);
+                        const uint32_t a_tmem = tmem_base + kAColBase + slot * kAColsPerSlot + u * kAColsPerSub;
 #pragma unroll
-                    for (int kk = 0; kk < kBK / 16; kk++)  // 16 k = 8 TMEM columns of A, 32 bytes of each B row
-                        tc_mma_ts(tmem_base, a_tmem + 8 * kk, db + 2 * kk, idesc, (ks | kk) != 0 ? 1u : 0u);
-                    tc_commit(&sl->empty_a[sa]);  // both arrive when the MMAs above have consumed their operands
-                    tc_commit(&sl->empty_b[sb]);
+                        for (int kk = 0; kk < kBK / 16; kk++)  // 16 k = 8 TMEM columns of A, 32 bytes of each B row
+                            tc_mma_ts(tmem_base, a_tmem + 8 * kk, db + 2 * kk, idesc, (st | u | kk) != 0 ? 1u : 0u);
+                    }
+#ifndef QMM_MMA_ONLY
+                    tc_commit(&sl->empty[slot]);  // arrives when the MMAs above have consumed their operands
+#endif
+                    if (++slot == kStagesB) { slot = 0; phase ^= 1; }
                 }
                 if (ok) tc_commit(&sl->tmem_full);
             }
         }
     } else if (warp >= kEpiWarps) {
-        // ---------------- dequantisers: group grp owns the stages it = grp (mod 4); thread owns row n0 + r ----------------
+        // ---------------- dequantisers: group grp owns the stages = grp (mod kDqGroups); thread owns row n0 + r ----------------
         const int q = warp & 3, grp = (warp - kEpiWarps) >> 2;
         const int r = q * 32 + lane;
         const size_t row_bytes = (size_t)p.K * BITS / 8;
@@ -295,12 +325,15 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kAColBase;
         uint32_t it0 = 0;  // stage counter at the start of the tile
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, it0 += nks) {
+#ifdef QMM_MMA_ONLY
+        ok = false;
+#endif
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, it0 += nst) {
             const int n = min((tile / p.m_tiles) * kTileN + r, p.N - 1);
             const uint32_t* wrow = reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned char*>(p.wq) + (size_t)n * row_bytes);
             const uint16_t* srow = reinterpret_cast<const uint16_t*>(p.scales) + (size_t)n * gpr;
             const uint16_t* brow = reinterpret_cast<const uint16_t*>(p.biases) + (size_t)n * gpr;
-            uint32_t wn[WPS], sn[2], bn[2];  // the next owned stage, prefetched
+            uint32_t wn[WPS], sn[2], bn[2];  // the next owned 64-weight sub-block, prefetched
             auto fetch = [&](int ks) {
 #pragma unroll
                 for (int i = 0; i < WPS / 4; i++)
@@ -311,24 +344,39 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
                 sn[0] = ldg_u16(srow + g0); bn[0] = ldg_u16(brow + g0);
                 sn[1] = ldg_u16(srow + g1); bn[1] = ldg_u16(brow + g1);
             };
-            int ks = (int)((grp - it0) & 3u);  // first stage of this tile owned by the group
-            if (ks < nks) fetch(ks);
-            for (; ks < nks; ks += kDqGroups) {
-                uint32_t w[WPS];
+            int st = (int)((grp + kDqGroups - it0 % kDqGroups) % kDqGroups);  // first stage of this tile owned by the group
+            if (st < nst) fetch(st * kSub);
+            for (; st < nst; st += kDqGroups) {
+                const uint32_t it = it0 + st;
+                const int sa = it % kStagesB;
+                const int nsub = min(kSub, nks - st * kSub);
+                for (int u = 0; u < nsub; u++) {
+                    const int ks = st * kSub + u;
+                    uint32_t w[WPS];
 #pragma unroll
-                for (int i = 0; i < WPS; i++) w[i] = wn[i];
-                const uint32_t s0 = sn[0], s1 = sn[1], b0 = bn[0], b1 = bn[1];
-                if (ks + kDqGroups < nks) fetch(ks + kDqGroups);
-                uint32_t out[32];
-                if (scale_fast_ok(s0) && scale_fast_ok(s1)) dequant_row_stage<BITS, true>(w, s0, b0, s1, b1, out);
-                else dequant_row_stage<BITS, false>(w, s0, b0, s1, b1, out);  // whole-stage branch: not if-converted
-                const uint32_t it = it0 + ks;
-                const int sa = it % kSlotsA;
-                if (!mbar_wait(&sl->empty_a[sa], ((it / kSlotsA) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-                tmem_st32(lane_addr + sa * kAColsPerSlot, out);
+                    for (int i = 0; i < WPS; i++) w[i] = wn[i];
+                    const uint32_t s0 = sn[0], s1 = sn[1], b0 = bn[0], b1 = bn[1];
+                    // prefetch the next sub-block this thread will need
+                    const int nxt = (u + 1 < nsub) ? ks + 1 : (st + kDqGroups) * kSub;
+                    if (nxt < nks) fetch(nxt);
+                    uint32_t out[32];
+#ifdef QMM_DQ_NOP
+#pragma unroll
+                    for (int i = 0; i < 32; i++) out[i] = w[i % WPS] ^ s0 ^ b1;
+                    if (false)
+#endif
+                    if (scale_fast_ok(s0) && scale_fast_ok(s1)) dequant_row_stage<BITS, true>(w, s0, b0, s1, b1, out);
+                    else dequant_row_stage<BITS, false>(w, s0, b0, s1, b1, out);  // whole-stage branch: not if-converted
+                    if (u == 0) {
+                        if (!mbar_wait(&sl->empty[sa], ((it / kStagesB) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                        tc_fence_after();
+                    }
+                    __syncwarp();  // tcgen05.st is warp-collective: the scale-dependent branch above may have split the warp
+                    tmem_st32(lane_addr + sa * kAColsPerSlot + u * kAColsPerSub, out);
+                }
+                if (!ok) break;
                 tc_fence_before();
-                mbar_arrive(&sl->full_a[sa]);
+                mbar_arrive(&sl->full[sa]);
             }
         }
     } else {
@@ -346,6 +394,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
             for (int blk = blk_lo; blk < blk_hi; blk++) {
                 const int c0 = blk * 32;
                 uint32_t v[32];
+                __syncwarp();
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
                 if (n < p.N) {
                     const size_t idx0 = (size_t)(m0 + c0) * p.N + n;
@@ -419,17 +468,21 @@ struct GemmPlan {
     size_t smem;
 };
 
-bool make_gemm_plan(const QmmArgs& a, GemmPlan* pl) {
+bool make_gemm_plan(const QmmArgs& a, int sm_count, GemmPlan* pl) {
     if (a.x_dtype != LUX_DTYPE_BFLOAT16 || a.sb_dtype != LUX_DTYPE_BFLOAT16) return false;
     if (a.bits != 4 && a.bits != 8) return false;
     if (a.group != 32 && a.group != 64 && a.group != 128) return false;
     if (a.M <= 16 || a.N < 1 || a.K % kBK) return false;
     if (((uintptr_t)a.x | (uintptr_t)a.wq | (uintptr_t)a.scales | (uintptr_t)a.biases | (uintptr_t)a.y) & 15) return false;
     if ((long long)a.N * (a.K / a.group) > (1ll << 31) - 1) return false;
+    pl->n_tiles = (a.N + kTileN - 1) / kTileN;
+    // rows of x per tile: as many as the MMA takes.  The time of a tile is set by the dequantisation of
+    // its 128 x K weights, not by its height, so fewer, taller tiles always win (measured: 176-row tiles
+    // for M = 512 were 20 % slower than 256-row tiles although they need one round of tiles less).
+    (void)sm_count;
     pl->m_tiles = (a.M + kMaxBM - 1) / kMaxBM;
     pl->bm = (((a.M + pl->m_tiles - 1) / pl->m_tiles) + 15) & ~15;
-    pl->n_tiles = (a.N + kTileN - 1) / kTileN;
-    pl->smem = 1024 + (size_t)kStagesB * kBBytes + sizeof(SmemLayout) + 64;
+    pl->smem = 1024 + (size_t)kStagesB * kSub * kBBytes + sizeof(SmemLayout) + 64;
     return encode_tiled_fn() != nullptr;
 }
 
@@ -453,12 +506,12 @@ cudaError_t launch_gemm_t(const CUtensorMap& tmap, const GemmParams& p, const Ge
 
 bool qmm_tc_supported(const QmmArgs& a) {
     GemmPlan pl;
-    return make_gemm_plan(a, &pl);
+    return make_gemm_plan(a, 148, &pl);
 }
 
 cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, const char** name) {
     GemmPlan pl;
-    if (!make_gemm_plan(a, &pl)) return cudaErrorInvalidValue;
+    if (!make_gemm_plan(a, sm_count, &pl)) return cudaErrorInvalidValue;
     int* err = error_word();
     if (!err) return cudaErrorMemoryAllocation;
     // x as a 2-D tensor [M rows][K], boxes of 64 elements (128 bytes) x bm rows, 128-byte swizzle;
