@@ -208,6 +208,10 @@ def run_ours(args, rank, world):
     plugin = mlx_b200.Plugin(require_gpu=True)
     ctx = plugin.context(local_rank)
     q = plugin.quant
+    if args.prefill_only:
+        peaks, _ = measured_peaks()
+        print(json.dumps({"prefill": prefill_legs(ctx, O, BF16, peaks)}))
+        return
 
     # resident inputs: R weight sets (each rank: its own column slice), x per M
     layers = []
@@ -404,6 +408,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the e2e and CPU-baseline legs (for short runs under a profiler)")
+    ap.add_argument("--prefill-only", action="store_true", help="run only the tensor-bound legs (short, for profiling)")
     ap.add_argument("--traffic-bytes", type=float, default=None,
                     help="dram bytes per launch from the committed ncu summary (profiles/), echoed into roofline.traffic")
     args = ap.parse_args()

@@ -25,10 +25,17 @@
 //   warps 8-19  dequantisers in three groups of four warps: group j owns the
 //               pipeline stages = j (mod 3); inside a group warp q owns TMEM lanes
 //               32q.. (a warp may only touch its own lane quarter), so thread
-//               (q, lane) owns row n0 + 32q + lane: per owned stage it reads 32
-//               (4-bit) or 64 (8-bit) packed bytes + scale/bias from global
-//               memory (prefetched one owned stage ahead in registers),
-//               dequantises (dequant.cuh) and writes 32 TMEM columns;
+//               (q, lane) owns row n0 + 32q + lane.  The group's leader thread
+//               brings the group's next 128 rows x 64 packed bytes into the
+//               group's own shared-memory slot by TMA (64-byte swizzle, so the
+//               row-per-thread reads are bank-conflict free); a thread reads its
+//               64 bytes, the group meets at a named barrier, the leader refills
+//               the slot for the group's next stage.  (Row-per-thread loads from
+//               global memory were one L1 wavefront per lane and kept the load
+//               pipe 70-80 % busy; through the slot it is 4 wavefronts per warp.)
+//               Scales / biases of a stage are one small vector load per thread,
+//               fetched one owned stage ahead.  Then dequantise (dequant.cuh)
+//               and write 32 TMEM columns per 64 weights;
 //   warp 20     TMA producer for x;
 //   warp 21     allocates TMEM, issues tcgen05.mma (one elected thread) and the
 //               commits that release A slots / B stages and publish D.
@@ -48,14 +55,12 @@ namespace luxcuda {
 namespace {
 
 constexpr int kBK = 64;            // weights (k) per pipeline stage = one 128-byte swizzle row of bf16
-#ifndef QMM_STAGES_B
-#define QMM_STAGES_B 3
-#endif
-constexpr int kStagesB = QMM_STAGES_B;  // k-stages in flight: B in shared memory, A in TMEM, one barrier pair per stage
+constexpr int kStagesB = 3;  // k-stages in flight: B in shared memory, A in TMEM, one barrier pair per stage
 constexpr int kTileN = 128;        // rows of W per tile (MMA M)
 constexpr int kMaxBM = 256;        // rows of x per tile (MMA N)
 constexpr int kSub = 2;            // 64-weight sub-blocks per pipeline stage (one barrier round per 128 k)
 constexpr int kBBytes = kMaxBM * 128;   // one sub-block of B
+constexpr int kWUnitBytes = kTileN * 64;  // one unit of packed weights: 128 rows x 64 bytes (128 k at 4 bit, 64 k at 8 bit)
 constexpr int kEpiWarps = 8, kDqGroups = 3, kDqWarps = 4 * kDqGroups;
 // A dequantising group goes from stage s straight to stage s + kDqGroups.  Its wait for that slot is by
 // phase parity, which cannot tell "freed once more" from "two frees behind": the group must never be able
@@ -182,10 +187,19 @@ struct GemmParams {
 };
 
 struct SmemLayout {
-    uint64_t full[kStagesB], empty[kStagesB], tmem_full, tmem_empty;
+    uint64_t full[kStagesB], empty[kStagesB], wfull[kDqGroups], tmem_full, tmem_empty;
     uint32_t tmem_base;
     int abort_flag;
 };
+
+// Barrier `id` over 128 threads that also ANDs a predicate: every participant gets the same answer.
+__device__ __forceinline__ bool group_all(int id, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{ .reg .pred p, q; setp.ne.u32 q, %1, 0; bar.red.and.pred p, %2, 128, q; selp.u32 %0, 1, 0, p; }"
+        : "=r"(r) : "r"((uint32_t)pred), "r"(id) : "memory");
+    return r != 0;
+}
 
 __device__ __forceinline__ uint32_t ldg_u16(const uint16_t* p) {  // zero-extended straight into a 32-bit register
     uint32_t v;
@@ -229,13 +243,15 @@ __device__ __forceinline__ void dequant_row_stage(const uint32_t* w, uint32_t s0
 }
 template <int BITS>
 __global__ void __launch_bounds__(kNumThreads, 1)
-qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ GemmParams p) {
+qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+              const __grid_constant__ GemmParams p) {
     constexpr int WPS = kBK * BITS / 32;  // packed words per row per stage: 8 | 16
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* sB = smem;  // [kStagesB][bm rows][128 B], swizzled (TMA)
     const uint32_t b_bytes = (uint32_t)p.bm * 128;
-    SmemLayout* sl = reinterpret_cast<SmemLayout*>(sB + (size_t)kStagesB * kSub * kBBytes);
+    unsigned char* sW = sB + (size_t)kStagesB * kSub * kBBytes;  // [kDqGroups][128 rows][64 B], 64-byte swizzle (TMA)
+    SmemLayout* sl = reinterpret_cast<SmemLayout*>(sW + (size_t)kDqGroups * kWUnitBytes);
     volatile int* abort_flag = &sl->abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -248,6 +264,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
             mbar_init(&sl->full[s], 128 + 1);  // 128 dequantising threads + the TMA producer (with its byte count)
             mbar_init(&sl->empty[s], 1);        // one tcgen05.commit
         }
+        for (int g = 0; g < kDqGroups; g++) mbar_init(&sl->wfull[g], 1);  // the group leader's expect_tx
         mbar_init(&sl->tmem_full, 1);
         mbar_init(&sl->tmem_empty, kEpiWarps * 32);
         sl->abort_flag = 0;
@@ -263,11 +280,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
         // ---------------- TMA producer: x tiles ----------------
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
             uint32_t it = 0;
             bool ok = true;
-#ifdef QMM_MMA_ONLY
-            ok = false;
-#endif
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % p.m_tiles) * p.bm;
                 for (int st = 0; st < nst; st++, it++) {
@@ -275,13 +290,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
                     const uint32_t ph = (it / kStagesB) & 1;
                     const int nsub = min(kSub, nks - st * kSub);
                     if (!mbar_wait(&sl->empty[sb], ph ^ 1, abort_flag)) { ok = false; break; }
-#ifdef QMM_NO_TMA
-                    mbar_arrive(&sl->full[sb]);
-#else
                     mbar_expect_tx(&sl->full[sb], b_bytes * nsub);
                     for (int u = 0; u < nsub; u++)
                         tma_load_2d(sB + ((size_t)sb * kSub + u) * kBBytes, &tmap_x, (st * kSub + u) * kBK, m0, &sl->full[sb]);
-#endif
                 }
             }
         }
@@ -297,10 +308,8 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
                 tc_fence_after();
                 for (int st = 0; st < nst; st++) {
                     const int nsub = min(kSub, nks - st * kSub);
-#ifndef QMM_MMA_ONLY
                     if (!mbar_wait_spin(&sl->full[slot], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-#endif
                     for (int u = 0; u < nsub; u++) {
                         const uint64_t db = db0 + (uint64_t)(slot * kSub + u) * (kBBytes >> 4);
                         const uint32_t a_tmem = tmem_base + kAColBase + slot * kAColsPerSlot + u * kAColsPerSub;
@@ -308,9 +317,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
                         for (int kk = 0; kk < kBK / 16; kk++)  // 16 k = 8 TMEM columns of A, 32 bytes of each B row
                             tc_mma_ts(tmem_base, a_tmem + 8 * kk, db + 2 * kk, idesc, (st | u | kk) != 0 ? 1u : 0u);
                     }
-#ifndef QMM_MMA_ONLY
                     tc_commit(&sl->empty[slot]);  // arrives when the MMAs above have consumed their operands
-#endif
                     if (++slot == kStagesB) { slot = 0; phase ^= 1; }
                 }
                 if (ok) tc_commit(&sl->tmem_full);
@@ -318,66 +325,126 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
         }
     } else if (warp >= kEpiWarps) {
         // ---------------- dequantisers: group grp owns the stages = grp (mod kDqGroups); thread owns row n0 + r ----------------
+        constexpr int UPS = BITS == 8 ? 2 : 1;  // weight units (128 rows x 64 packed bytes) per pipeline stage
         const int q = warp & 3, grp = (warp - kEpiWarps) >> 2;
         const int r = q * 32 + lane;
-        const size_t row_bytes = (size_t)p.K * BITS / 8;
+        const bool leader = (q == 0 && lane == 0);
+        const int bar_id = 1 + grp;  // named barrier of the group (0 is __syncthreads)
         const int gpr = p.K >> p.gshift;
+        const int ng_full = (kSub * kBK) >> p.gshift;  // scale groups per full stage: 4, 2 or 1
+        const bool vec_ok = (gpr % ng_full) == 0;      // then a stage's scales of one row are one aligned vector
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kAColBase;
-        uint32_t it0 = 0;  // stage counter at the start of the tile
+        // this group's weight unit in shared memory; row r is 64 bytes, its 16-byte chunk c sits at c ^ ((r >> 1) & 3)
+        const unsigned char* wrow = sW + (size_t)grp * kWUnitBytes + r * 64;
+        const uint32_t wsw = (uint32_t)(r >> 1) & 3u;
+        uint64_t* wbar = &sl->wfull[grp];
+        uint32_t wround = 0;  // units of this group consumed so far
+
+        struct Cur { int tile, st; uint32_t it0; };  // an owned stage: tile, stage in the tile, stage counter at tile start
+        auto settle = [&](Cur& c) {  // first stage of c.tile owned by the group; tiles without one are skipped
+            while (c.tile < total_tiles) {
+                c.st = (int)((grp + kDqGroups - c.it0 % kDqGroups) % kDqGroups);
+                if (c.st < nst) break;
+                c.tile += gridDim.x;
+                c.it0 += nst;
+            }
+        };
+        auto advance = [&](Cur& c) {
+            c.st += kDqGroups;
+            if (c.st >= nst) {
+                c.tile += gridDim.x;
+                c.it0 += nst;
+                settle(c);
+            }
+        };
+        auto issue = [&](const Cur& c, int u) {  // leader: bring unit u of stage c into the group's slot
+            mbar_expect_tx(wbar, kWUnitBytes);
+            tma_load_2d(const_cast<unsigned char*>(sW) + (size_t)grp * kWUnitBytes, &tmap_w,
+                        c.st * (kSub * kBK * BITS / 8) + u * 64, (c.tile / p.m_tiles) * kTileN, wbar);
+        };
+        uint32_t sp[2], bp[2];  // scales / biases of the next owned stage of this row, bf16 pairs in group order
+        auto fetch_sb = [&](const Cur& c) {
+            const int n = min((c.tile / p.m_tiles) * kTileN + r, p.N - 1);
+            const int g0 = (c.st * kSub * kBK) >> p.gshift;
+            const int ng = min(gpr - g0, ng_full);
+            const uint16_t* sr = reinterpret_cast<const uint16_t*>(p.scales) + (size_t)n * gpr + g0;
+            const uint16_t* br = reinterpret_cast<const uint16_t*>(p.biases) + (size_t)n * gpr + g0;
+            sp[1] = 0; bp[1] = 0;
+            if (vec_ok && ng == ng_full && ng == 4) {
+                asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(sp[0]), "=r"(sp[1]) : "l"(sr));
+                asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(bp[0]), "=r"(bp[1]) : "l"(br));
+            } else if (vec_ok && ng == ng_full && ng == 2) {
+                asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(sp[0]) : "l"(sr));
+                asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(bp[0]) : "l"(br));
+            } else {
+                sp[0] = ldg_u16(sr); bp[0] = ldg_u16(br);
+                if (ng > 1) { sp[0] |= ldg_u16(sr + 1) << 16; bp[0] |= ldg_u16(br + 1) << 16; }
+                if (ng > 2) { sp[1] = ldg_u16(sr + 2); bp[1] = ldg_u16(br + 2); }
+                if (ng > 3) { sp[1] |= ldg_u16(sr + 3) << 16; bp[1] |= ldg_u16(br + 3) << 16; }
+            }
+        };
+
+        Cur cur{(int)blockIdx.x, 0, 0u};
+        settle(cur);
+        if (cur.tile < total_tiles) {
+            if (leader) issue(cur, 0);
+            fetch_sb(cur);
+        }
         bool ok = true;
-#ifdef QMM_MMA_ONLY
-        ok = false;
-#endif
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, it0 += nst) {
-            const int n = min((tile / p.m_tiles) * kTileN + r, p.N - 1);
-            const uint32_t* wrow = reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned char*>(p.wq) + (size_t)n * row_bytes);
-            const uint16_t* srow = reinterpret_cast<const uint16_t*>(p.scales) + (size_t)n * gpr;
-            const uint16_t* brow = reinterpret_cast<const uint16_t*>(p.biases) + (size_t)n * gpr;
-            uint32_t wn[WPS], sn[2], bn[2];  // the next owned 64-weight sub-block, prefetched
-            auto fetch = [&](int ks) {
+        while (cur.tile < total_tiles) {
+            Cur nxt = cur;
+            advance(nxt);
+            const uint32_t it = cur.it0 + cur.st;
+            const int sa = it % kStagesB;
+            const int nsub = min(kSub, nks - cur.st * kSub);
+            const uint32_t sc[2] = {sp[0], sp[1]}, bc[2] = {bp[0], bp[1]};
+            if (nxt.tile < total_tiles) fetch_sb(nxt);  // three stages ahead of its use
+            uint32_t w[16];
+            bool group_fail = false;
 #pragma unroll
-                for (int i = 0; i < WPS / 4; i++)
-                    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(wn[4 * i]), "=r"(wn[4 * i + 1]), "=r"(wn[4 * i + 2]), "=r"(wn[4 * i + 3])
-                                 : "l"(wrow + ks * WPS + 4 * i));
-                const int g0 = (ks * kBK) >> p.gshift, g1 = (ks * kBK + 32) >> p.gshift;
-                sn[0] = ldg_u16(srow + g0); bn[0] = ldg_u16(brow + g0);
-                sn[1] = ldg_u16(srow + g1); bn[1] = ldg_u16(brow + g1);
-            };
-            int st = (int)((grp + kDqGroups - it0 % kDqGroups) % kDqGroups);  // first stage of this tile owned by the group
-            if (st < nst) fetch(st * kSub);
-            for (; st < nst; st += kDqGroups) {
-                const uint32_t it = it0 + st;
-                const int sa = it % kStagesB;
-                const int nsub = min(kSub, nks - st * kSub);
-                for (int u = 0; u < nsub; u++) {
-                    const int ks = st * kSub + u;
-                    uint32_t w[WPS];
+            for (int u = 0; u < kSub; u++) {
+                if (u >= nsub) break;
+                if (UPS == 2 || u == 0) {
+                    const bool got = ok && mbar_wait(wbar, wround & 1, abort_flag);
+                    wround++;
 #pragma unroll
-                    for (int i = 0; i < WPS; i++) w[i] = wn[i];
-                    const uint32_t s0 = sn[0], s1 = sn[1], b0 = bn[0], b1 = bn[1];
-                    // prefetch the next sub-block this thread will need
-                    const int nxt = (u + 1 < nsub) ? ks + 1 : (st + kDqGroups) * kSub;
-                    if (nxt < nks) fetch(nxt);
-                    uint32_t out[32];
-#ifdef QMM_DQ_NOP
-#pragma unroll
-                    for (int i = 0; i < 32; i++) out[i] = w[i % WPS] ^ s0 ^ b1;
-                    if (false)
-#endif
-                    if (scale_fast_ok(s0) && scale_fast_ok(s1)) dequant_row_stage<BITS, true>(w, s0, b0, s1, b1, out);
-                    else dequant_row_stage<BITS, false>(w, s0, b0, s1, b1, out);  // whole-stage branch: not if-converted
-                    if (u == 0) {
-                        if (!mbar_wait(&sl->empty[sa], ((it / kStagesB) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                        tc_fence_after();
+                    for (int c = 0; c < 4; c++) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(wrow + ((c ^ wsw) << 4));
+                        w[4 * c] = v.x; w[4 * c + 1] = v.y; w[4 * c + 2] = v.z; w[4 * c + 3] = v.w;
                     }
-                    __syncwarp();  // tcgen05.st is warp-collective: the scale-dependent branch above may have split the warp
-                    tmem_st32(lane_addr + sa * kAColsPerSlot + u * kAColsPerSub, out);
+                    // every thread of the group has its bytes: the slot may be refilled.  The same barrier makes
+                    // a failed wait a decision of the whole group, so nobody is left waiting at it.
+                    ok = group_all(bar_id, got);
+                    if (!ok) { group_fail = true; break; }
+                    if (leader) {
+                        if (UPS == 2 && u + 1 < nsub) issue(cur, u + 1);
+                        else if (nxt.tile < total_tiles) issue(nxt, 0);
+                    }
                 }
-                if (!ok) break;
+                // scales of the two 32-weight halves of this sub-block
+                const int h0 = (2 * u * 32) >> p.gshift, h1 = ((2 * u + 1) * 32) >> p.gshift;
+                const uint32_t s0 = (sc[h0 >> 1] >> ((h0 & 1) * 16)) & 0xFFFFu, b0 = (bc[h0 >> 1] >> ((h0 & 1) * 16)) & 0xFFFFu;
+                const uint32_t s1 = (sc[h1 >> 1] >> ((h1 & 1) * 16)) & 0xFFFFu, b1 = (bc[h1 >> 1] >> ((h1 & 1) * 16)) & 0xFFFFu;
+                uint32_t out[32];
+                const uint32_t (&ws)[WPS] = *reinterpret_cast<const uint32_t (*)[WPS]>(&w[BITS == 4 ? 8 * u : 0]);
+                if (scale_fast_ok(s0) && scale_fast_ok(s1)) dequant_row_stage<BITS, true>(ws, s0, b0, s1, b1, out);
+                else dequant_row_stage<BITS, false>(ws, s0, b0, s1, b1, out);  // whole-block branch: not if-converted
+                if (u == 0) {
+                    const bool freed = ok && mbar_wait(&sl->empty[sa], ((it / kStagesB) & 1) ^ 1, abort_flag);
+                    ok = __all_sync(0xFFFFFFFFu, freed);  // tcgen05.st below is warp-collective
+                    tc_fence_after();
+                }
+                __syncwarp();
+                if (ok) tmem_st32(lane_addr + sa * kAColsPerSlot + u * kAColsPerSub, out);
+            }
+            if (ok) {
                 tc_fence_before();
                 mbar_arrive(&sl->full[sa]);
+            } else if (!*abort_flag) {
+                *abort_flag = 1;
             }
+            if (group_fail) break;  // decided by the whole group at its barrier
+            cur = nxt;                // a warp that failed alone goes on to the next barrier, where the group ends
         }
     } else {
         // ---------------- epilogue: warp w reads TMEM lanes 32*(w%4).., half w/4 of the column blocks ----------------
@@ -482,12 +549,12 @@ bool make_gemm_plan(const QmmArgs& a, int sm_count, GemmPlan* pl) {
     (void)sm_count;
     pl->m_tiles = (a.M + kMaxBM - 1) / kMaxBM;
     pl->bm = (((a.M + pl->m_tiles - 1) / pl->m_tiles) + 15) & ~15;
-    pl->smem = 1024 + (size_t)kStagesB * kSub * kBBytes + sizeof(SmemLayout) + 64;
+    pl->smem = 1024 + (size_t)kStagesB * kSub * kBBytes + (size_t)kDqGroups * kWUnitBytes + sizeof(SmemLayout) + 64;
     return encode_tiled_fn() != nullptr;
 }
 
 template <int BITS>
-cudaError_t launch_gemm_t(const CUtensorMap& tmap, const GemmParams& p, const GemmPlan& pl, int sm_count, cudaStream_t stream) {
+cudaError_t launch_gemm_t(const CUtensorMap& tmap, const CUtensorMap& tmap_w, const GemmParams& p, const GemmPlan& pl, int sm_count, cudaStream_t stream) {
     auto kern = qmm_tc_kernel<BITS>;
     static std::atomic<size_t> attr_smem[64];
     int dev = 0;
@@ -498,7 +565,7 @@ cudaError_t launch_gemm_t(const CUtensorMap& tmap, const GemmParams& p, const Ge
         attr_smem[dev & 63].store(pl.smem);
     }
     const int grid = std::min(sm_count, pl.m_tiles * pl.n_tiles);
-    kern<<<grid, kNumThreads, pl.smem, stream>>>(tmap, p);
+    kern<<<grid, kNumThreads, pl.smem, stream>>>(tmap, tmap_w, p);
     return cudaGetLastError();
 }
 
@@ -528,6 +595,20 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, c
         set_last_error("cuTensorMapEncodeTiled failed (%d)", (int)r);
         return cudaErrorInvalidValue;
     }
+    // the packed weights as bytes, [N rows][K*bits/8], boxes of 64 bytes x 128 rows, 64-byte swizzle
+    CUtensorMap tmap_w;
+    {
+        const cuuint64_t wdims[2] = {(cuuint64_t)a.K * a.bits / 8, (cuuint64_t)a.N};
+        const cuuint64_t wstrides[1] = {(cuuint64_t)a.K * a.bits / 8};
+        const cuuint32_t wbox[2] = {64u, (cuuint32_t)kTileN};
+        r = encode_tiled_fn()(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint32_t*>(a.wq), wdims, wstrides, wbox,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) {
+            set_last_error("cuTensorMapEncodeTiled (weights) failed (%d)", (int)r);
+            return cudaErrorInvalidValue;
+        }
+    }
     GemmParams p;
     p.wq = a.wq;
     p.scales = (const __nv_bfloat16*)a.scales;
@@ -542,10 +623,10 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, c
     p.bm = pl.bm; p.n_tiles = pl.n_tiles; p.m_tiles = pl.m_tiles;
     if (a.bits == 4) {
         if (name) *name = "qmm_tc<4>";
-        return launch_gemm_t<4>(tmap, p, pl, sm_count, stream);
+        return launch_gemm_t<4>(tmap, tmap_w, p, pl, sm_count, stream);
     }
     if (name) *name = "qmm_tc<8>";
-    return launch_gemm_t<8>(tmap, p, pl, sm_count, stream);
+    return launch_gemm_t<8>(tmap, tmap_w, p, pl, sm_count, stream);
 }
 
 // Non-zero once a kernel has given up on a bounded wait; reading clears it.
