@@ -102,6 +102,14 @@ struct Context {
     size_t qmv_ws_bytes = 0;
     const char* last_kernel = "";
     std::atomic<uint64_t> launches{0};
+    std::atomic<uint64_t> copies{0};  // memcpy / memset enqueues
+    // Chain of decode kernels: a decode kernel may start fetching its weights while the previous kernel of
+    // the stream drains (programmatic dependent launch) only if that kernel is a decode kernel of this
+    // context, is the last thing the context enqueued, and does not write those weights.
+    uint64_t chain_launches = ~0ull, chain_copies = 0;  // the two counters right after the last decode launch
+    const char* chain_out_lo = nullptr;                 // what that launch writes
+    const char* chain_out_hi = nullptr;
+    bool stream_exposed = false;  // the host holds the raw stream: it may enqueue work the context cannot see
     std::mutex mu;  // one thread at a time per context
 };
 
@@ -157,7 +165,11 @@ struct QmmArgs {
 // decode GEMV, bf16 activations: mma.sync m16n8k16 with in-register dequant
 bool qmv_mma_supported(const QmmArgs& a);
 size_t qmv_mma_workspace_bytes(const QmmArgs& a, int sm_count);
-cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name);
+// overlap_prev: launch as a programmatic dependent of the previous kernel in the stream (see Context)
+cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name,
+                           bool overlap_prev = false);
+bool decode_may_overlap(const Context* c, const QmmArgs& a);
+void note_decode_launch(Context* c, const QmmArgs& a);  // call right after a decode launch, before counting it
 // decode / small-M, any supported dtype combination: CUDA cores + warp shuffles
 cudaError_t launch_qmv_simt(const QmmArgs& a, cudaStream_t stream, const char** name);
 // prefill GEMM, bf16 activations: TMA + tcgen05 + TMEM

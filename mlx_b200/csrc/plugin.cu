@@ -137,6 +137,7 @@ LuxBackendBuffer* buffer_alloc(LuxBackendContext* ctx, size_t bytes) {
     if (!b) return nullptr;
     if (bytes) {
         DeviceGuard g(c->dev->device());
+        c->copies++;
         if (cudaMemsetAsync(b->ptr, 0, bytes, c->stream) != cudaSuccess) {
             cudaGetLastError();
             c->dev->release(b->block, c->stream);
@@ -155,6 +156,7 @@ LuxBackendBuffer* buffer_alloc_with_data(LuxBackendContext* ctx, const void* dat
     if (bytes) {
         DeviceGuard g(c->dev->device());
         // The caller keeps `data` and may change it right after this returns.
+        c->copies++;
         cudaError_t e = cudaMemcpyAsync(b->ptr, data, bytes, cudaMemcpyHostToDevice, c->stream);
         if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
         if (e != cudaSuccess) {
@@ -182,6 +184,7 @@ LuxBackendError buffer_copy_to_host(LuxBackendContext* ctx, LuxBackendBuffer* bu
     size_t n = bytes < b->bytes ? bytes : b->bytes;
     if (!n) return LUX_BACKEND_OK;
     DeviceGuard g(c->dev->device());
+    c->copies++;
     LUX_CUDA_TRY(cudaMemcpyAsync(dst, b->ptr, n, cudaMemcpyDeviceToHost, c->stream));
     LUX_CUDA_TRY(cudaStreamSynchronize(c->stream));
     if (take_device_error()) {
@@ -198,6 +201,7 @@ LuxBackendError buffer_copy_from_host(LuxBackendContext* ctx, LuxBackendBuffer* 
     size_t n = bytes < b->bytes ? bytes : b->bytes;
     if (!n) return LUX_BACKEND_OK;
     DeviceGuard g(c->dev->device());
+    c->copies++;
     LUX_CUDA_TRY(cudaMemcpyAsync(b->ptr, src, n, cudaMemcpyHostToDevice, c->stream));
     LUX_CUDA_TRY(cudaStreamSynchronize(c->stream));  // the caller may reuse src at once
     b->last_stream = c->stream;
@@ -246,6 +250,7 @@ LuxBackendError kernel_dispatch(LuxBackendContext* ctx, LuxBackendKernel* kernel
     lux_qmm_params p;
     {
         DeviceGuard g(c->dev->device());
+        c->copies++;
         LUX_CUDA_TRY(cudaMemcpyAsync(&p, pb->ptr, sizeof(p), cudaMemcpyDeviceToHost, c->stream));
         LUX_CUDA_TRY(cudaStreamSynchronize(c->stream));
     }
@@ -295,6 +300,7 @@ LuxBackendError op_ntt(LuxBackendContext* ctx, uint64_t* data, size_t n, uint64_
     Context* c = as_ctx(ctx);
     if (!c || !data || n == 0 || (n & (n - 1)) != 0 || modulus < 2) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     DeviceGuard g(c->dev->device());
+    c->copies++;
     LUX_CUDA_TRY(ntt_device(data, n, modulus, inverse, c->stream));
     c->launches++;
     return LUX_BACKEND_OK;

@@ -44,24 +44,9 @@ namespace luxcuda {
 
 namespace {
 
-#ifdef QMV_TRACE
-__device__ long long g_trace[148][16][16];
-__device__ __forceinline__ long long gtime() {
-    long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define TRACE(i) do { if ((threadIdx.x & 31) == 0 && (i) < 16) g_trace[blockIdx.x][threadIdx.x >> 5][(i)] = gtime(); } while (0)
-#else
-#define TRACE(i) do {} while (0)
-#endif
-
 constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
-#ifndef QMV_DEPTH
-#define QMV_DEPTH 2
-#endif
-constexpr int kDepth = QMV_DEPTH;          // ring stages per warp (2 measured best: deeper rings only delay the first data)
+constexpr int kDepth = 2;                  // ring stages per warp (measured best: deeper rings only delay the first data)
 constexpr int kStageBytes = 2048 + 512;    // 4 x 32 x 16 B of weights + 32 x 16 B of scales/biases
 constexpr int kRingBytes = kWarps * kDepth * kStageBytes;
 constexpr int kSmemLimit = 227 * 1024 - 256;
@@ -308,171 +293,117 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
     const unsigned char* wbase = reinterpret_cast<const unsigned char*>(p.wq) + t * 16;
     const __nv_bfloat16* sb_src = lane < 16 ? p.scales : p.biases;
     const uint32_t ring_lo = smem_u32(smem) + warp * (kDepth * kStageBytes) + lane * 16;  // this lane's slot, stage 0
-    const uint32_t ring_hi = ring_lo + kDepth * kStageBytes;
     const int tail_tile = (p.N & 15) ? p.n_rt - 1 : -1;  // the tile whose rows must be clamped to N-1
 
-    // The warp's tasks: for each batch of tb tiles, for each of its k-blocks, for each tile of the
-    // batch.  Pointers advance by one tile per task; everything else is recomputed only when the
-    // k-block or the batch changes.
-    struct Iter {
-        int b0, kb, rt, rt_end;
-        bool valid;
-        const unsigned char* p0;       // row rt*16+g of Wq, k-block kb, piece t
-        const __nv_bfloat16* sbp;      // scales (lanes 0-15) / biases (16-31) of row rt*16+(lane&15), k-block kb
-    };
-    auto it_setup = [&](Iter& it) {
-        it.rt_end = min(it.b0 + tb, rt_hi);
-        it.p0 = wbase + (size_t)(it.rt * 16 + g) * row_bytes + it.kb * 128;
-        int elem = (it.rt * 16 + (lane & 15)) * gpr + it.kb * gpk;
-        if (p.sb_bytes == 2) elem &= ~1;  // a single 2-byte scale is copied with its neighbour
-        it.sbp = sb_src + elem;
-    };
-    auto it_init = [&](Iter& it) {
-        it.b0 = rt_lo; it.kb = kb_lo + warp; it.rt = rt_lo;
-        it.valid = it.kb < kb_hi && rt_lo < rt_hi;
-        if (it.valid) it_setup(it);
-    };
-    auto it_next = [&](Iter& it) {
-        it.rt++;
-        it.p0 += 16 * row_bytes;
-        it.sbp += 16 * gpr;
-        if (it.rt >= it.rt_end) {
-            it.kb += kWarps;
-            it.rt = it.b0;
-            if (it.kb >= kb_hi) {
-                it.b0 += tb;
-                it.kb = kb_lo + warp;
-                it.rt = it.b0;
-                if (it.b0 >= rt_hi) it.valid = false;
-            }
-            if (it.valid) it_setup(it);
-        }
-    };
-    auto issue = [&](const Iter& it, uint32_t dst) {
-        const unsigned char* p0 = it.p0;
-        const unsigned char* p1 = p0 + 8 * row_bytes;
-        const __nv_bfloat16* sbp = it.sbp;
-        if (it.rt == tail_tile) {  // rows past N read row N-1 (their results are never stored)
-            const int n0 = it.rt * 16;
-            p0 = wbase + (size_t)min(n0 + g, p.N - 1) * row_bytes + it.kb * 128;
-            p1 = wbase + (size_t)min(n0 + g + 8, p.N - 1) * row_bytes + it.kb * 128;
-            int elem = min(n0 + (lane & 15), p.N - 1) * gpr + it.kb * gpk;
-            if (p.sb_bytes == 2) elem &= ~1;
-            sbp = sb_src + elem;
+    // The warp's tasks: for each batch of tb tiles, for each of its k-blocks, the tiles of the batch
+    // ("run").  One task is in flight while the previous one is computed (two ring stages).
+    const size_t half_tile = 8 * row_bytes;
+    auto issue = [&](int rt, int kb, uint32_t dst) {
+        const unsigned char* p0;
+        const unsigned char* p1;
+        int elem;
+        if (rt != tail_tile) {
+            p0 = wbase + (size_t)(rt * 16 + g) * row_bytes + kb * 128;
+            p1 = p0 + half_tile;
+            elem = (rt * 16 + (lane & 15)) * gpr + kb * gpk;
+        } else {  // rows past N read row N-1 (their results are never stored)
+            const int n0 = rt * 16;
+            p0 = wbase + (size_t)min(n0 + g, p.N - 1) * row_bytes + kb * 128;
+            p1 = wbase + (size_t)min(n0 + g + 8, p.N - 1) * row_bytes + kb * 128;
+            elem = min(n0 + (lane & 15), p.N - 1) * gpr + kb * gpk;
         }
         cp_async16(dst, p0);
         cp_async16(dst + 512, p0 + 64);
         cp_async16(dst + 1024, p1);
         cp_async16(dst + 1536, p1 + 64);
-        if (p.sb_bytes == 16) cp_async16(dst + 2048, sbp);
-        else if (p.sb_bytes == 8) cp_async8(dst + 2048, sbp);
-        else cp_async4(dst + 2048, sbp);
+        if (p.sb_bytes == 16) cp_async16(dst + 2048, sb_src + elem);
+        else if (p.sb_bytes == 8) cp_async8(dst + 2048, sb_src + elem);
+        else cp_async4(dst + 2048, sb_src + (p.sb_bytes == 2 ? (elem & ~1) : elem));  // a lone scale travels with its neighbour
     };
 
-    TRACE(0);
-    Iter it_i, it_c;
-    it_init(it_i);
-    it_init(it_c);
+    const bool has_work = kb_lo + warp < kb_hi && rt_lo < rt_hi;
+    const uint32_t ring_sum = 2 * ring_lo + kStageBytes;  // stage <-> other stage
+    uint32_t src_c = ring_lo;                             // stage of the task computed next (this lane's slot)
+    if (has_work) issue(rt_lo, kb_lo + warp, src_c);
+    cp_async_commit();
 
-    // prime the ring: kDepth-1 tasks in flight before anything else
-    uint32_t dst_i = ring_lo;
-#pragma unroll 1
-    for (int d = 0; d < kDepth - 1; d++) {
-        if (it_i.valid) {
-            issue(it_i, dst_i);
-            it_next(it_i);
-        }
-        cp_async_commit();
-        dst_i += kStageBytes;
-    }
+    // Everything above touched only the weights, which no kernel of the chain writes.  From here on the
+    // kernel reads x and uses the scratch, which the previous kernel may have written: wait for it, then
+    // let the next kernel of the chain start its own weight fetch.  (Both are no-ops in a plain launch.)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    // per-k-block state of the compute side
     uint4 xr[MT][XV];
-    uint32_t sboff[2][2];   // byte offsets of this lane's scales inside a stage, by row half r and piece h
-    int cur_kb = -1, cur_b0 = rt_lo;
-    uint32_t src_c = ring_lo;   // stage being computed (this lane's slot)
-    float4* dstp = part;
-    TRACE(1);
-    int trace_i = 2;
-    (void)trace_i;
+    uint32_t sboff[2][2];  // byte offsets of this lane's scales inside a stage, by row half r and piece h
 #pragma unroll 1
-    while (it_c.valid) {
-        if (it_i.valid) {
-            issue(it_i, dst_i);
-            it_next(it_i);
-        }
-        cp_async_commit();
-        dst_i += kStageBytes;
-        if (dst_i == ring_hi) dst_i = ring_lo;
-
-        if (it_c.b0 != cur_b0 || it_c.kb != cur_kb) {  // new k-block or new batch (rare)
-            while (cur_b0 < it_c.b0) {
-                batch_end<MT>(p, reinterpret_cast<const float*>(part), cur_b0, min(tb, rt_hi - cur_b0), kb_lo, nkl, s_flags, true);
-                cur_b0 += tb;
-            }
-            if (it_c.kb != cur_kb) {
-                cur_kb = it_c.kb;
-                load_x_raw<BITS, MT>(p, cur_kb, g, t, xr);
+    for (int b0 = rt_lo; b0 < rt_hi; b0 += tb) {
+        const int nt = min(tb, rt_hi - b0);
+        if (has_work) {
+#pragma unroll 1
+            for (int kb = kb_lo + warp; kb < kb_hi; kb += kWarps) {
+                // the run after this one: next k-block of the batch, else first k-block of the next batch
+                int kb_n = kb + kWarps, b0_n = b0;
+                if (kb_n >= kb_hi) {
+                    kb_n = kb_lo + warp;
+                    b0_n = b0 + tb;
+                }
+                const int rt_last = b0 + nt - 1;
+                if (nt > 1) issue(b0 + 1, kb, ring_sum - src_c);
+                else if (b0_n < rt_hi) issue(b0_n, kb_n, ring_sum - src_c);
+                cp_async_commit();
+                load_x_raw<BITS, MT>(p, kb, g, t, xr);
                 permute_x<BITS, MT>(xr);
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
                     const int slot = g + 8 * r;
-                    const int par = p.sb_bytes == 2 ? ((slot * gpr + cur_kb) & 1) : 0;
+                    const int par = p.sb_bytes == 2 ? ((slot * gpr + kb) & 1) : 0;
 #pragma unroll
                     for (int h = 0; h < 2; h++)
                         sboff[r][h] = 2048 - lane * 16 + slot * 16 + ((((h * (KB / 2) + t * (KB / 8)) >> p.gshift) + par) << 1);
                 }
+                float4* dstp = part + (kb - kb_lo) * E4 + lane;
+#pragma unroll 1
+                for (int rt = b0; rt <= rt_last; rt++) {
+                    if (rt != b0) {  // (the run's first prefetch was issued before the x loads)
+                        if (rt < rt_last) issue(rt + 1, kb, ring_sum - src_c);
+                        else if (b0_n < rt_hi) issue(b0_n, kb_n, ring_sum - src_c);
+                        cp_async_commit();
+                    }
+                    cp_async_wait<1>();
+                    __syncwarp();
+                    uint4 w[2][2];
+                    uint32_t s[2][2], b[2][2];
+#pragma unroll
+                    for (int r = 0; r < 2; r++)
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                         : "=r"(w[r][h].x), "=r"(w[r][h].y), "=r"(w[r][h].z), "=r"(w[r][h].w)
+                                         : "r"(src_c + (r * 2 + h) * 512));
+                            asm volatile("ld.shared.u16 %0, [%1];" : "=r"(s[r][h]) : "r"(src_c + sboff[r][h]));
+                            asm volatile("ld.shared.u16 %0, [%1+256];" : "=r"(b[r][h]) : "r"(src_c + sboff[r][h]));
+                        }
+                    const bool fast = scales_fast_ok4(s[0][0], s[0][1], s[1][0], s[1][1]);
+                    float acc[MT][2][4];  // two independent accumulation chains per 8-row block of x
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                        for (int c = 0; c < 2; c++) acc[mt][c][0] = acc[mt][c][1] = acc[mt][c][2] = acc[mt][c][3] = 0.0f;
+                    if (__all_sync(0xffffffffu, fast)) task_mma<BITS, MT, true>(w, s, b, xr, acc);
+                    else task_mma<BITS, MT, false>(w, s, b, xr, acc);
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++)
+                        dstp[mt * 32] = make_float4(acc[mt][0][0] + acc[mt][1][0], acc[mt][0][1] + acc[mt][1][1],
+                                                    acc[mt][0][2] + acc[mt][1][2], acc[mt][0][3] + acc[mt][1][3]);
+                    dstp += nkl * E4;
+                    __syncwarp();  // every lane is done with the stage before it is refilled
+                    src_c = ring_sum - src_c;
+                }
             }
-            dstp = part + ((it_c.rt - it_c.b0) * nkl + (cur_kb - kb_lo)) * E4 + lane;
         }
-        cp_async_wait<kDepth - 1>();
-        __syncwarp();
-        uint4 w[2][2];
-        uint32_t s[2][2], b[2][2];
-#pragma unroll
-        for (int r = 0; r < 2; r++)
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(w[r][h].x), "=r"(w[r][h].y), "=r"(w[r][h].z), "=r"(w[r][h].w)
-                             : "r"(src_c + (r * 2 + h) * 512));
-                uint16_t sv, bv;
-                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sv) : "r"(src_c + sboff[r][h]));
-                asm volatile("ld.shared.u16 %0, [%1+256];" : "=h"(bv) : "r"(src_c + sboff[r][h]));
-                s[r][h] = sv;
-                b[r][h] = bv;
-            }
-        const bool fast = scales_fast_ok4(s[0][0], s[0][1], s[1][0], s[1][1]);
-        float acc[MT][2][4];  // two independent accumulation chains per 8-row block of x
-#pragma unroll
-        for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-            for (int c = 0; c < 2; c++) acc[mt][c][0] = acc[mt][c][1] = acc[mt][c][2] = acc[mt][c][3] = 0.0f;
-#ifdef QMV_LOADONLY
-        acc[0][0][0] = __uint_as_float(w[0][0].x ^ w[0][1].y ^ w[1][0].z ^ w[1][1].w ^ s[0][0] ^ b[1][1] ^ xr[0][0].x ^ (fast ? 1u : 0u));
-#else
-        if (__all_sync(0xffffffffu, fast)) task_mma<BITS, MT, true>(w, s, b, xr, acc);
-        else task_mma<BITS, MT, false>(w, s, b, xr, acc);
-#endif
-#pragma unroll
-        for (int mt = 0; mt < MT; mt++)
-            dstp[mt * 32] = make_float4(acc[mt][0][0] + acc[mt][1][0], acc[mt][0][1] + acc[mt][1][1],
-                                        acc[mt][0][2] + acc[mt][1][2], acc[mt][0][3] + acc[mt][1][3]);
-        dstp += nkl * E4;
-        __syncwarp();  // every lane is done with the stage before it is refilled
-        it_next(it_c);
-        src_c += kStageBytes;
-        if (src_c == ring_hi) src_c = ring_lo;
-        TRACE(trace_i);
-        trace_i++;
+        batch_end<MT>(p, reinterpret_cast<const float*>(part), b0, nt, kb_lo, nkl, s_flags, b0 + tb < rt_hi);
     }
     cp_async_wait<0>();
-    while (cur_b0 < rt_hi) {
-        batch_end<MT>(p, reinterpret_cast<const float*>(part), cur_b0, min(tb, rt_hi - cur_b0), kb_lo, nkl, s_flags,
-                      cur_b0 + tb < rt_hi);
-        cur_b0 += tb;
-    }
-    TRACE(15);
 }
 
 struct Plan {
@@ -518,7 +449,7 @@ bool make_plan(const QmmArgs& a, int sm_count, Plan* pl) {
 }
 
 template <int BITS, int MT>
-cudaError_t launch_t(const Params& p, const Plan& pl, cudaStream_t stream) {
+cudaError_t launch_t(const Params& p, const Plan& pl, cudaStream_t stream, bool overlap_prev) {
     auto kern = qmv_mma_kernel<BITS, MT>;
     // opt in to large dynamic shared memory (static + dynamic stay within the 227 KiB per-block limit)
     static std::atomic<size_t> attr_smem[64];
@@ -529,8 +460,19 @@ cudaError_t launch_t(const Params& p, const Plan& pl, cudaStream_t stream) {
         if (e != cudaSuccess) return e;
         attr_smem[dev & 63].store(pl.smem);
     }
-    kern<<<pl.chunks * pl.ks, kThreads, pl.smem, stream>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(pl.chunks * pl.ks);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = pl.smem;
+    cfg.stream = stream;
+    // As a programmatic dependent the grid may start (and fetch weights) while the previous kernel of the
+    // stream drains; everything else in the kernel sits behind its griddepcontrol.wait.
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap_prev ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 }  // namespace
@@ -550,7 +492,8 @@ size_t qmv_mma_workspace_bytes(const QmmArgs& a, int sm_count) {
 
 // workspace layout: [counters: n_rt x u32, padded to 256 B][partials]; the counters must
 // be zero before the first launch and are left zero by every launch.
-cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name) {
+cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name,
+                           bool overlap_prev) {
     Plan pl;
     if (!make_plan(a, sm_count, &pl)) return cudaErrorInvalidValue;
     Params p;
@@ -568,10 +511,10 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
     p.chunks = pl.chunks; p.ks = pl.ks; p.tb = pl.tb; p.sb_bytes = pl.sb_bytes;
     if (a.bits == 4) {
         if (name) *name = pl.mt == 1 ? "qmv_mma<4,m8>" : "qmv_mma<4,m16>";
-        return pl.mt == 1 ? launch_t<4, 1>(p, pl, stream) : launch_t<4, 2>(p, pl, stream);
+        return pl.mt == 1 ? launch_t<4, 1>(p, pl, stream, overlap_prev) : launch_t<4, 2>(p, pl, stream, overlap_prev);
     }
     if (name) *name = pl.mt == 1 ? "qmv_mma<8,m8>" : "qmv_mma<8,m16>";
-    return pl.mt == 1 ? launch_t<8, 1>(p, pl, stream) : launch_t<8, 2>(p, pl, stream);
+    return pl.mt == 1 ? launch_t<8, 1>(p, pl, stream, overlap_prev) : launch_t<8, 2>(p, pl, stream, overlap_prev);
 }
 
 
@@ -640,10 +583,11 @@ extern "C" LUX_GPU_BACKEND_EXPORT LuxBackendError lux_gpu_cuda_qmatmul_decode_no
     cudaError_t e = static_scratch_ptr(c->dev->device(), &scratch);
     if (e != cudaSuccess) return map_cuda_error(e, "cudaGetSymbolAddress(static scratch)");
     const char* name = "";
-    e = launch_qmv_mma(a, scratch, c->dev->sm_count, c->stream, &name);
+    e = launch_qmv_mma(a, scratch, c->dev->sm_count, c->stream, &name, decode_may_overlap(c, a));
     if (e != cudaSuccess) return map_cuda_error(e, name);
     c->last_kernel = name;
     c->launches++;
+    note_decode_launch(c, a);
     bx->last_stream = bw->last_stream = bs->last_stream = bb->last_stream = by->last_stream = c->stream;
     return LUX_BACKEND_OK;
 }

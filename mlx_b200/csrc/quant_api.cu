@@ -37,6 +37,29 @@ LuxBackendError check_format(int K, int bits, int group) {
     return LUX_BACKEND_OK;
 }
 
+}  // namespace
+
+static bool ranges_overlap(const char* a_lo, size_t a_bytes, const char* b_lo, const char* b_hi) {
+    return a_lo < b_hi && b_lo < a_lo + a_bytes;
+}
+bool decode_may_overlap(const Context* c, const QmmArgs& a) {
+    static const bool disabled = getenv("LUXCUDA_NO_PDL") != nullptr;
+    if (disabled || c->stream_exposed) return false;
+    if (c->chain_launches != c->launches.load() || c->chain_copies != c->copies.load()) return false;
+    const size_t sb = (size_t)a.N * (a.K / a.group) * 2;
+    return !ranges_overlap((const char*)a.wq, (size_t)a.N * a.K * a.bits / 8, c->chain_out_lo, c->chain_out_hi) &&
+           !ranges_overlap((const char*)a.scales, sb, c->chain_out_lo, c->chain_out_hi) &&
+           !ranges_overlap((const char*)a.biases, sb, c->chain_out_lo, c->chain_out_hi);
+}
+void note_decode_launch(Context* c, const QmmArgs& a) {
+    c->chain_launches = c->launches.load();
+    c->chain_copies = c->copies.load();
+    c->chain_out_lo = (const char*)a.y;
+    c->chain_out_hi = (const char*)a.y + (size_t)a.M * a.N * (a.y_dtype == LUX_DTYPE_BFLOAT16 ? 2 : 4);
+}
+
+namespace {
+
 LuxBackendError ensure_qmv_workspace(Context* c, size_t bytes) {
     if (bytes <= c->qmv_ws_bytes) return LUX_BACKEND_OK;
     cudaError_t e = cudaSuccess;
@@ -44,6 +67,7 @@ LuxBackendError ensure_qmv_workspace(Context* c, size_t bytes) {
     if (!nb) return map_cuda_error(e, "qmv workspace");
     // arrival counters start at zero; every launch leaves them at zero
     e = cudaMemsetAsync(nb->ptr, 0, bytes, c->stream);
+    c->copies++;
     if (e != cudaSuccess) {
         c->dev->release(nb, c->stream);
         return map_cuda_error(e, "qmv workspace memset");
@@ -78,8 +102,11 @@ LuxBackendError qmatmul_on_stream(Context* c, const QmmArgs& a) {
                     chunk.M = a.M - m0 < 16 ? a.M - m0 : 16;
                     chunk.x = (const char*)a.x + (size_t)m0 * a.K * 2;
                     chunk.y = (char*)a.y + (size_t)m0 * a.N * ysz;
-                    e = launch_qmv_mma(chunk, c->qmv_ws->ptr, c->dev->sm_count, c->stream, &name);
-                    launches++;
+                    e = launch_qmv_mma(chunk, c->qmv_ws->ptr, c->dev->sm_count, c->stream, &name, decode_may_overlap(c, chunk));
+                    if (e == cudaSuccess) {
+                        c->launches++;
+                        note_decode_launch(c, chunk);
+                    }
                 }
             } else {
                 e = launch_qmv_simt(a, c->stream, &name);
@@ -236,6 +263,7 @@ LuxBackendError buffer_copy_from_host_async(LuxBackendContext* ctx, LuxBackendBu
     const size_t n = bytes < b->bytes ? bytes : b->bytes;
     if (!n) return LUX_BACKEND_OK;
     DeviceGuard g(c->dev->device());
+    c->copies++;
     LUX_CUDA_TRY(cudaMemcpyAsync(b->ptr, src, n, cudaMemcpyHostToDevice, c->stream));
     b->last_stream = c->stream;
     return LUX_BACKEND_OK;
@@ -253,7 +281,9 @@ void host_free_pinned(void* p) {
 }
 void* context_stream(LuxBackendContext* ctx) {
     Context* c = as_ctx(ctx);
-    return c ? (void*)c->stream : nullptr;
+    if (!c) return nullptr;
+    c->stream_exposed = true;  // from now on the host may enqueue work of its own on it
+    return (void*)c->stream;
 }
 LuxBackendError allocator_stats(LuxBackendContext* ctx, uint64_t* reserved, uint64_t* in_use, uint64_t* driver_allocs) {
     Context* c = as_ctx(ctx);

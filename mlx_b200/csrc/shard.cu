@@ -219,6 +219,7 @@ LuxBackendError qmatmul_sharded(LuxCudaShardComm* sc, LuxBackendBuffer* x, LuxBa
     if (e != LUX_BACKEND_OK) return e;
     {
         DeviceGuard g(c->dev->device());
+        c->copies++;  // a library kernel the context does not count as its own: ends a chain of decode launches
         LUX_NCCL_TRY(nccl().AllGather(view.ptr, bst->ptr, slice, ncclUint8, sc->comm, c->stream));
     }
     Deferred d{c, bst->ptr, by->ptr, sc->world, M, Nl, (int)ys};
