@@ -85,6 +85,7 @@ struct Params {
     int M, K, N, gshift, y_bf16;
     int nkb, n_rt;
     int chunks, ks;          // grid = chunks (tile ranges) x ks (k-block ranges)
+    int chained;             // launched as a programmatic dependent of the previous kernel
     int tb;                  // tiles per reduction batch
     int sb_bytes;            // bytes of scales per row per k-block: 2, 4, 8 or 16
 };
@@ -324,6 +325,14 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
     const bool has_work = kb_lo + warp < kb_hi && rt_lo < rt_hi;
     const uint32_t ring_sum = 2 * ring_lo + kStageBytes;  // stage <-> other stage
     uint32_t src_c = ring_lo;                             // stage of the task computed next (this lane's slot)
+    // The x fragments of the first k-block are on the critical path of the first task, and a load queues
+    // behind whatever the SM has already requested.  With up to 8 rows of x (32 registers) they are
+    // therefore requested ahead of the weights: first of all in a plain launch; in a dependent launch,
+    // where x may still be being written, right after the wait and ahead of the second task.  (With 16
+    // rows the fragments would have to be held across the issue code and spill; they stay behind it.)
+    constexpr bool kXFirst = MT == 1;
+    uint4 xr[MT][XV];
+    if (kXFirst && !p.chained && has_work) load_x_raw<BITS, MT>(p, kb_lo + warp, g, t, xr);
     if (has_work) issue(rt_lo, kb_lo + warp, src_c);
     cp_async_commit();
 
@@ -332,8 +341,9 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
     // let the next kernel of the chain start its own weight fetch.  (Both are no-ops in a plain launch.)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (kXFirst && p.chained && has_work) load_x_raw<BITS, MT>(p, kb_lo + warp, g, t, xr);
+    bool x_loaded = kXFirst;  // (of the first run)
 
-    uint4 xr[MT][XV];
     uint32_t sboff[2][2];  // byte offsets of this lane's scales inside a stage, by row half r and piece h
 #pragma unroll 1
     for (int b0 = rt_lo; b0 < rt_hi; b0 += tb) {
@@ -351,7 +361,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
                 if (nt > 1) issue(b0 + 1, kb, ring_sum - src_c);
                 else if (b0_n < rt_hi) issue(b0_n, kb_n, ring_sum - src_c);
                 cp_async_commit();
-                load_x_raw<BITS, MT>(p, kb, g, t, xr);
+                if (!x_loaded) load_x_raw<BITS, MT>(p, kb, g, t, xr);
+                x_loaded = false;
                 permute_x<BITS, MT>(xr);
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
@@ -509,6 +520,7 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
     p.y_bf16 = a.y_dtype == LUX_DTYPE_BFLOAT16;
     p.nkb = pl.nkb; p.n_rt = pl.n_rt;
     p.chunks = pl.chunks; p.ks = pl.ks; p.tb = pl.tb; p.sb_bytes = pl.sb_bytes;
+    p.chained = overlap_prev ? 1 : 0;
     if (a.bits == 4) {
         if (name) *name = pl.mt == 1 ? "qmv_mma<4,m8>" : "qmv_mma<4,m16>";
         return pl.mt == 1 ? launch_t<4, 1>(p, pl, stream, overlap_prev) : launch_t<4, 2>(p, pl, stream, overlap_prev);

@@ -219,6 +219,15 @@ class Buffer:
                 "buffer_copy_to_host")
         return out
 
+    def to_host_into(self, host_ptr, nbytes):
+        """Blocking copy into caller-owned host memory (e.g. a pinned array): no allocation, no extra copy."""
+        p = self.ctx.plugin
+        p.check(p.vtbl.buffer_copy_to_host(self.ctx.handle, self.handle, host_ptr, nbytes), "buffer_copy_to_host")
+
+    def from_host_ptr(self, host_ptr, nbytes):
+        p = self.ctx.plugin
+        p.check(p.vtbl.buffer_copy_from_host(self.ctx.handle, self.handle, host_ptr, nbytes), "buffer_copy_from_host")
+
     def from_host(self, a):
         a = np.ascontiguousarray(a)
         p = self.ctx.plugin
@@ -380,6 +389,24 @@ class Context:
 
     def graph_destroy(self, g):
         self.plugin.quant.graph_destroy(g)
+
+    def pinned_array(self, shape, dtype):
+        """numpy array over page-locked host memory (host_alloc_pinned); freed with free_pinned_array."""
+        dtype = np.dtype(dtype)
+        nbytes = int(np.prod(shape)) * dtype.itemsize
+        ptr = self.plugin.quant.host_alloc_pinned(max(nbytes, 1))
+        if not ptr:
+            raise MemoryError("host_alloc_pinned failed")
+        buf = (C.c_char * max(nbytes, 1)).from_address(ptr)
+        arr = np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
+        self._pinned = getattr(self, "_pinned", {})
+        self._pinned[arr.ctypes.data] = ptr
+        return arr
+
+    def free_pinned_array(self, arr):
+        ptr = getattr(self, "_pinned", {}).pop(arr.ctypes.data, None)
+        if ptr:
+            self.plugin.quant.host_free_pinned(ptr)
 
     def upload_async(self, buf, pinned_ptr, nbytes):
         self.plugin.check(self.plugin.quant.buffer_copy_from_host_async(self.handle, buf.handle, pinned_ptr, nbytes),
