@@ -33,6 +33,10 @@ import time
 
 import numpy as np
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one qmv_mma launch (M=1) of this workload, from the ncu
+# capture summarised in profiles/qmv_mma_decode_gemv_4bit_K4096_N11008.md
+NCU_TRAFFIC_BYTES = 25438464.0
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
@@ -391,7 +395,8 @@ def run_ours(args, rank, world):
                      "peak_source": which, "frac_of_nominal_8TBps": achieved / NOMINAL_HBM_GBS,
                      "kernel": "qmv_mma<4,m8|m16>", "avg_us_per_launch": avg_us,
                      "alg_bytes_per_launch": {str(M): alg_bytes(M) for M in M_SWEEP},
-                     "traffic": args.traffic_bytes},
+                     "traffic": args.traffic_bytes, "traffic_unit": "bytes per launch (ncu dram read+write, M=1 launch)",
+                     "traffic_over_algorithmic": args.traffic_bytes / alg_bytes(1) if args.traffic_bytes else None},
         "per_M": {str(M): per_m[M] for M in M_SWEEP},
         "prefill": prefill,
         "cpu_baseline": cpu,
@@ -416,7 +421,7 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the e2e and CPU-baseline legs (for short runs under a profiler)")
     ap.add_argument("--prefill-only", action="store_true", help="run only the tensor-bound legs (short, for profiling)")
-    ap.add_argument("--traffic-bytes", type=float, default=None,
+    ap.add_argument("--traffic-bytes", type=float, default=NCU_TRAFFIC_BYTES,
                     help="dram bytes per launch from the committed ncu summary (profiles/), echoed into roofline.traffic")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
