@@ -226,9 +226,22 @@ def run_ours(args, rank, world):
     x_host = {M: O.make_x(M, K_DEC, O.BF16, config_id=2, tag=M) for M in M_SWEEP}
     x_dev = {M: ctx.upload(x_host[M]) for M in M_SWEEP}
     n_total = N_DEC * world
-    y_dev = {M: ctx.empty((M, n_total), np.uint16) for M in M_SWEEP}
-    comm, staging = None, {}
-    if world > 1:
+    comm, staging, symm = None, {}, {}
+    use_push = world > 1 and not args.nccl_allgather
+    if use_push:
+        # the all-gather is done by the decode kernel itself: every rank's y_full is a buffer its peers store into
+        import torch
+        for M in M_SWEEP:
+            symm[M] = mlx_b200.plugin.SymmBuffer(ctx, rank, world, (M, n_total), np.uint16)
+            mine = torch.tensor(list(symm[M].export()), dtype=torch.uint8, device="cuda")
+            every = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(every, mine)
+            symm[M].attach([bytes(t.cpu().tolist()) for t in every])
+        y_dev = {M: symm[M].buffer for M in M_SWEEP}
+        dist.barrier()
+    else:
+        y_dev = {M: ctx.empty((M, n_total), np.uint16) for M in M_SWEEP}
+    if world > 1 and not use_push:
         import torch
         uid = (C.c_ubyte * 128)()
         if rank == 0:
@@ -244,6 +257,8 @@ def run_ours(args, rank, world):
         w, s, b = layers[r]
         if world == 1:
             ctx.qmatmul(x_dev[M], w, s, b, y_dev[M], M, K_DEC, N_DEC, BITS, GROUP, BF16, BF16, BF16)
+        elif use_push:
+            symm[M].qmatmul(x_dev[M], w, s, b, M, K_DEC, N_DEC, BITS, GROUP, BF16)
         else:
             plugin.check(q.qmatmul_sharded(comm, x_dev[M].handle, w.handle, s.handle, b.handle, y_dev[M].handle,
                                            staging[M].handle, M, K_DEC, N_DEC, BITS, GROUP, BF16, BF16, BF16),
@@ -258,12 +273,32 @@ def run_ours(args, rank, world):
         wq0, s0, b0 = O.make_layer(N_DEC, K_DEC, BITS, GROUP, O.BF16, config_id=2, layer=0, proj=0)
         err, _ = O.rel_err(y, O.qmatmul_truth(x_host[4], wq0, s0, b0, BITS, GROUP))
         assert err <= O.TOL[O.BF16], f"parity check failed before timing: {err}"
+    verified = None
+    if world > 1:
+        # every rank's columns, as they arrived on rank 0, against the same slice computed here on one GPU
+        if dist is not None:
+            ctx.sync()
+            dist.barrier()
+        if rank == 0:
+            for M in (4, 16):
+                got = y_dev[M].to_host((M, n_total), np.uint16)
+                for r in range(world):
+                    wq_r, s_r, b_r = O.make_layer(N_DEC, K_DEC, BITS, GROUP, O.BF16, config_id=2, layer=0, proj=r)
+                    bw, bs, bb = ctx.upload(wq_r), ctx.upload(s_r), ctx.upload(b_r)
+                    ref = ctx.empty((M, N_DEC), np.uint16)
+                    ctx.qmatmul(x_dev[M], bw, bs, bb, ref, M, K_DEC, N_DEC, BITS, GROUP, BF16, BF16, BF16)
+                    want = ref.to_host()
+                    assert np.array_equal(got[:, r * N_DEC:(r + 1) * N_DEC], want), f"columns of rank {r} differ (M={M})"
+                    for h in (bw, bs, bb, ref):
+                        h.free()
+            verified = "all ranks' columns on rank 0 bit-identical to the single-GPU kernel (M=4, 16)"
+        dist.barrier()
 
     # one sweep = len(M_SWEEP) * R launches, recorded once as a CUDA graph per M
     l0 = ctx.launch_count()
     graphs = {}
     # one process per GPU: the NCCL all-gathers are launched eagerly (a capture of them hung a 2-rank run)
-    use_graph = world == 1 and not args.no_graph
+    use_graph = (world == 1 or use_push) and not args.no_graph
     if use_graph:
         for M in M_SWEEP:
             ctx.graph_begin()
@@ -373,6 +408,8 @@ def run_ours(args, rank, world):
         dist.barrier()
         if comm:
             q.shard_comm_destroy(comm)
+        for sb in symm.values():
+            sb.free()
         dist.destroy_process_group()
     if rank != 0:
         return
@@ -389,6 +426,9 @@ def run_ours(args, rank, world):
         "config": {"workload": "decode_gemv_sweep" if world == 1 else "decode_gemv_sweep_column_sharded_allgather",
                    "M": list(M_SWEEP), "K": K_DEC, "N": N_DEC, "N_total": n_total, "bits": BITS, "group": GROUP,
                    "weight_sets": R_SETS, "sweeps_per_step": args.reps, "cuda_graph": use_graph,
+                   "allgather": None if world == 1 else ("peer stores from the decode kernel (one launch per call)" if use_push
+                                                         else "NCCL all-gather + interleave pass"),
+                   "verified": verified,
                    "l2": f"inputs larger than L2: {R_SETS} rotating weight sets = {R_SETS * alg_bytes(1) / 1e6:.0f} MB, "
                          "each launch reads a set last touched 11 launches earlier"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -420,6 +460,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the e2e and CPU-baseline legs (for short runs under a profiler)")
+    ap.add_argument("--nccl-allgather", action="store_true",
+                    help="N>1: gather the column slices with NCCL + an interleave pass instead of peer stores from the kernel")
     ap.add_argument("--prefill-only", action="store_true", help="run only the tensor-bound legs (short, for profiling)")
     ap.add_argument("--traffic-bytes", type=float, default=NCU_TRAFFIC_BYTES,
                     help="dram bytes per launch from the committed ncu summary (profiles/), echoed into roofline.traffic")

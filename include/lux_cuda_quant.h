@@ -48,7 +48,7 @@ extern "C" {
 #endif
 
 #define LUX_CUDA_QUANT_MAGIC 0x4C515854u /* "LQXT" */
-#define LUX_CUDA_QUANT_VERSION 1u
+#define LUX_CUDA_QUANT_VERSION 2u /* 2: symm_* and qmatmul_sharded_push appended */
 #define LUX_CUDA_QMM_KERNEL_NAME "lux.qmm.affine"
 #define LUX_CUDA_NCCL_UID_BYTES 128
 
@@ -59,6 +59,9 @@ typedef struct lux_qmm_params {
 
 /* One rank of a column-sharded layer (see shard_* below). */
 typedef struct LuxCudaShardComm LuxCudaShardComm;
+/* One rank's copy of a buffer that its peers can store into (see symm_*). */
+typedef struct LuxCudaSymmBuffer LuxCudaSymmBuffer;
+#define LUX_CUDA_SYMM_HANDLE_BYTES 96
 /* A recorded sequence of calls on one context (see graph_*). */
 typedef struct LuxCudaGraph LuxCudaGraph;
 
@@ -170,6 +173,28 @@ typedef struct lux_gpu_quant_vtbl {
                                        LuxBackendDtype x_dtype, LuxBackendDtype sb_dtype, LuxBackendDtype y_dtype);
     LuxBackendError (*shard_group_begin)(void);
     LuxBackendError (*shard_group_end)(void);
+
+    /* --- column-sharded decode with the all-gather inside the matmul kernel (version >= 2) ---
+     * Every rank holds the whole y[M, world*Nl] in a "symmetric" buffer that its peers can store into
+     * over NVLink.  Set-up, once: symm_alloc on every rank; symm_export gives LUX_CUDA_SYMM_HANDLE_BYTES
+     * to pass to the other ranks by any host channel; symm_attach takes all ranks' handles in rank order
+     * (own entry ignored; other processes are reached by CUDA IPC, the same process directly).
+     * symm_buffer is the local copy as an ordinary buffer (borrowed: valid until symm_free).  Before
+     * symm_free every rank must be past its last call that stores into the buffer. */
+    LuxBackendError (*symm_alloc)(LuxBackendContext* ctx, int rank, int world, size_t bytes, LuxCudaSymmBuffer** out);
+    LuxBackendError (*symm_export)(LuxCudaSymmBuffer* buf, void* handle_out /* LUX_CUDA_SYMM_HANDLE_BYTES */);
+    LuxBackendError (*symm_attach)(LuxCudaSymmBuffer* buf, const void* handles /* world x LUX_CUDA_SYMM_HANDLE_BYTES */);
+    LuxBackendBuffer* (*symm_buffer)(LuxCudaSymmBuffer* buf);
+    void (*symm_free)(LuxCudaSymmBuffer* buf);
+    /* y_full[:, rank*Nl : (rank+1)*Nl] = x . dequant(wq_local)^T, written by ONE decode launch into every
+     * rank's copy of y_full; the launch ends when the peers' columns of the same call have arrived, so
+     * whatever is enqueued after it sees the whole y_full.  All ranks must make the same calls on the
+     * same buffer in the same order (a rank waits up to 2 s for its peers, then the next sync returns
+     * INTERNAL).  bf16 x / scales / biases, 1 <= M <= 16, Nl a multiple of 16, world <= 8; anything else is
+     * NOT_SUPPORTED (use qmatmul_sharded).  May be recorded with graph_begin/graph_end. */
+    LuxBackendError (*qmatmul_sharded_push)(LuxCudaSymmBuffer* y_full, LuxBackendBuffer* x, LuxBackendBuffer* wq_local,
+                                            LuxBackendBuffer* scales_local, LuxBackendBuffer* biases_local,
+                                            int M, int K, int N_local, int bits, int group, LuxBackendDtype y_dtype);
 } lux_gpu_quant_vtbl;
 
 /* Entry points exported with default visibility. */

@@ -162,12 +162,23 @@ struct QmmArgs {
     int x_dtype, sb_dtype, y_dtype;  // LuxBackendDtype values
 };
 
+// Column-sharded decode launch: where the finished output tiles go besides this rank's own copy of y.
+// world == 1 (the default) means "not sharded".
+constexpr int kMaxShardWorld = 8;
+struct ShardPush {
+    int world = 1, me = 0;
+    int ld = 0, col0 = 0;                   // row stride of the full y and this rank's first column (elements)
+    size_t inbox_off = 0;                   // byte offset from a rank's y to its inbox (words sent by the peers)
+    void* y[kMaxShardWorld] = {};           // every rank's copy of y (own copy at [me])
+    uint32_t* flags[kMaxShardWorld] = {};   // every rank's flag words (see qmv_mma.cu)
+};
+
 // decode GEMV, bf16 activations: mma.sync m16n8k16 with in-register dequant
 bool qmv_mma_supported(const QmmArgs& a);
 size_t qmv_mma_workspace_bytes(const QmmArgs& a, int sm_count);
 // overlap_prev: launch as a programmatic dependent of the previous kernel in the stream (see Context)
 cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name,
-                           bool overlap_prev = false);
+                           bool overlap_prev = false, const ShardPush* push = nullptr);
 bool decode_may_overlap(const Context* c, const QmmArgs& a);
 void note_decode_launch(Context* c, const QmmArgs& a);  // call right after a decode launch, before counting it
 // decode / small-M, any supported dtype combination: CUDA cores + warp shuffles
@@ -177,6 +188,7 @@ bool qmm_tc_supported(const QmmArgs& a);
 cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, const char** name);
 // non-zero once a kernel gave up on one of its bounded waits since the last call (clears it)
 int take_device_error();
+int* device_error_word();  // where kernels raise it (null if the mapped word could not be set up)
 
 cudaError_t launch_dequantize(const uint32_t* wq, const void* scales, const void* biases, void* out, int N, int K,
                               int bits, int group, int sb_dtype, int out_dtype, cudaStream_t stream);
@@ -198,5 +210,7 @@ cudaError_t ntt_device(uint64_t* host_data, size_t n, uint64_t modulus, bool inv
 const lux_gpu_quant_vtbl* quant_vtbl();
 LuxBackendError qmatmul_on_stream(Context* c, const QmmArgs& a);
 void fill_shard_entries(lux_gpu_quant_vtbl* t);
+void fill_symm_entries(lux_gpu_quant_vtbl* t);
+LuxBackendError ensure_qmv_workspace(Context* c, size_t bytes);  // scratch of the decode kernel, grown on demand
 
 }  // namespace luxcuda

@@ -629,6 +629,17 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, c
     return launch_gemm_t<8>(tmap, tmap_w, p, pl, sm_count, stream);
 }
 
+// Device-side address of the host-visible error word (the same on every GPU: portable mapped memory).
+int* device_error_word() {
+    int* err = error_word();
+    int* derr = nullptr;
+    if (!err || cudaHostGetDevicePointer((void**)&derr, err, 0) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return derr;
+}
+
 // Non-zero once a kernel has given up on a bounded wait; reading clears it.
 int take_device_error() {
     if (!g_error_host || !*g_error_host) return 0;

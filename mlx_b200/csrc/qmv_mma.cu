@@ -80,6 +80,7 @@ struct Params {
     const __nv_bfloat16* scales;
     const __nv_bfloat16* biases;
     void* y;
+    int* error;              // host-visible error word (bounded waits of the sharded path)
     float* scratch;          // [n_rt][nkb][128*MT] partials of k-split tiles
     unsigned int* counters;  // [n_rt] arrival counters (zero between launches)
     int M, K, N, gshift, y_bf16;
@@ -88,7 +89,109 @@ struct Params {
     int chained;             // launched as a programmatic dependent of the previous kernel
     int tb;                  // tiles per reduction batch
     int sb_bytes;            // bytes of scales per row per k-block: 2, 4, 8 or 16
+    int ld, col0;            // y row stride and first column (elements): N and 0 unless the layer is column-sharded
+    ShardPush sp;            // sp.world > 1: the finished tiles are also stored into the peers' copies of y
 };
+
+// ---- column-sharded layers: all-gather by peer stores -----------------------------------
+// Every rank holds the full y[M, ld]; this rank computes columns [col0, col0 + N), stores them into its own
+// copy and sends them over NVLink to every peer.  What travels is 8-byte words, 4 bytes of y plus the
+// number of the call ("epoch"), written with single 64-bit stores into the receiver's inbox
+// (inbox[sender][row][word], behind y in the same buffer): a word is either absent or complete, so the
+// receiver needs no fence and no acknowledgement -- it polls the words, which costs one NVLink traversal
+// instead of three (data, ack, flag).  Each CTA, once its own tiles are sent, unpacks its share of the
+// inbox into the local y; when the launch ends the local y is whole, so stream order is all a consumer
+// needs.  One hand-shake guards the inbox: a rank announces ready[q] = epoch on every peer when its kernel
+// of that call has started -- everything it enqueued before has then finished with its y and inbox -- and a
+// sender waits for it before its first remote store.  Waits are bounded (kPeerWaitNs): on a time-out the
+// kernel raises the host-visible error word, stops waiting (in every later launch too) and returns.
+constexpr int kFlagEpoch = 0, kFlagCtaDone = 1, kFlagReady = 8;
+constexpr long long kPeerWaitNs = 2000000000ll;
+
+__device__ __forceinline__ long long now_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_sys64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+// Set by the first wait that runs out and never cleared: from then on no launch of this process waits
+// for a peer again (a lost peer must cost one time-out, not one per launch); the host sees the error word.
+__device__ int g_peer_lost;
+__device__ __forceinline__ bool peer_lost() { return *reinterpret_cast<volatile int*>(&g_peer_lost) != 0; }
+// true once *flag has reached epoch e (wrap-around safe)
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t e) {
+    if (peer_lost()) return false;
+    const long long t0 = now_ns();
+    for (;;) {
+        if ((int32_t)(ld_relaxed_sys(flag) - e) >= 0) return true;
+        if (now_ns() - t0 > kPeerWaitNs) {
+            g_peer_lost = 1;
+            return false;
+        }
+        __nanosleep(100);
+    }
+}
+// Send the finished tile (16 columns of every row of y) to the peers' inboxes.
+__device__ __forceinline__ void push_tile(const Params& p, uint32_t epoch, int rt, int tid_in_group, int group_threads) {
+    const int esz = p.y_bf16 ? 2 : 4, wpt = 4 * esz;  // words (4 bytes of y each) per tile row: 8 | 16
+    const int wpr = p.N * esz / 4;                    // words per row of this rank's columns
+    const int items = p.M * wpt * (p.sp.world - 1);
+    const char* ylocal = static_cast<const char*>(p.sp.y[p.sp.me]);
+    for (int i = tid_in_group; i < items; i += group_threads) {
+        const int k = i % wpt, m = (i / wpt) % p.M;
+        int q = i / (wpt * p.M);
+        q += q >= p.sp.me;
+        const uint32_t v = __ldcg(reinterpret_cast<const uint32_t*>(ylocal + ((size_t)m * p.ld + p.col0 + rt * 16) * esz) + k);
+        unsigned long long* inbox = reinterpret_cast<unsigned long long*>(static_cast<char*>(p.sp.y[q]) + p.sp.inbox_off);
+        st_relaxed_sys64(inbox + ((size_t)p.sp.me * p.M + m) * wpr + rt * wpt + k, ((unsigned long long)epoch << 32) | v);
+    }
+}
+// This CTA's share of the inbox -> local y.  Returns false if a word did not arrive in time.
+__device__ __forceinline__ bool unpack_inbox(const Params& p, uint32_t epoch) {
+    const int esz = p.y_bf16 ? 2 : 4;
+    const int wpr = p.N * esz / 4;
+    const int total = (p.sp.world - 1) * p.M * wpr;
+    const int per_cta = (total + gridDim.x - 1) / gridDim.x;
+    const int lo = blockIdx.x * per_cta, hi = min(total, lo + per_cta);
+    char* ylocal = static_cast<char*>(p.sp.y[p.sp.me]);
+    const unsigned long long* inbox = reinterpret_cast<const unsigned long long*>(ylocal + p.sp.inbox_off);
+    bool ok = true;
+    for (int i = lo + (int)threadIdx.x; i < hi; i += kThreads) {
+        const int w = i % wpr, m = (i / wpr) % p.M;
+        int src = i / (wpr * p.M);
+        src += src >= p.sp.me;
+        const unsigned long long* slot = inbox + ((size_t)src * p.M + m) * wpr + w;
+        unsigned long long v = ld_relaxed_sys64(slot);
+        if ((uint32_t)(v >> 32) != epoch) {
+            const long long t0 = now_ns();
+            while (ok) {
+                v = ld_relaxed_sys64(slot);
+                if ((uint32_t)(v >> 32) == epoch) break;
+                if (peer_lost() || now_ns() - t0 > kPeerWaitNs) {
+                    g_peer_lost = 1;
+                    ok = false;
+                }
+            }
+        }
+        if (ok) *reinterpret_cast<uint32_t*>(ylocal + ((size_t)m * p.ld + (size_t)src * p.N) * esz + (size_t)w * 4) = (uint32_t)v;
+    }
+    return ok;
+}
 
 template <int MT>
 __device__ __forceinline__ void store_tile(const Params& p, int rt, int e, float sum) {
@@ -96,7 +199,7 @@ __device__ __forceinline__ void store_tile(const Params& p, int rt, int e, float
     const int row = rt * 16 + (ln >> 2) + 8 * (ci >> 1);
     const int m = mt * 8 + 2 * (ln & 3) + (ci & 1);
     if (row < p.N && m < p.M) {
-        const size_t idx = (size_t)m * p.N + row;
+        const size_t idx = (size_t)m * p.ld + p.col0 + row;
         if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(sum);
         else reinterpret_cast<float*>(p.y)[idx] = sum;
     }
@@ -124,7 +227,7 @@ __device__ __forceinline__ float ordered_sum(const float* src, int n, int stride
 // is finished by whichever CTA arrives last.
 template <int MT>
 __device__ __noinline__ void batch_end(const Params& p, const float* part, int first_tile, int ntiles, int kb_lo, int nkl,
-                                       int* flags, bool more) {
+                                       int* flags, bool more, bool peers_ready, uint32_t epoch) {
     constexpr int E = 128 * MT;  // fp32 elements per partial
     const int tid = threadIdx.x;
     __syncthreads();
@@ -153,6 +256,15 @@ __device__ __noinline__ void batch_end(const Params& p, const float* part, int f
             if (flags[ti])
                 store_tile<MT>(p, first_tile + ti, tid % E,
                                ordered_sum<true>(p.scratch + (size_t)(first_tile + ti) * p.nkb * E + tid % E, p.nkb, E, 0.0f));
+    }
+    if (p.sp.world > 1) {
+        // the tiles this CTA has just finished go to the peers (unless the hand-shake failed)
+        __syncthreads();
+        if (peers_ready) {
+            constexpr int kGroup = 128;
+            for (int ti = tid / kGroup; ti < ntiles; ti += kThreads / kGroup)
+                if (p.ks == 1 || flags[ti]) push_tile(p, epoch, first_tile + ti, tid % kGroup, kGroup);
+        }
     }
     if (more) __syncthreads();  // the partial buffer and the flags are reused by the next batch
 }
@@ -341,6 +453,14 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
     // let the next kernel of the chain start its own weight fetch.  (Both are no-ops in a plain launch.)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // column-sharded: this call's number, and the word to the peers that our copy of y may be overwritten
+    uint32_t epoch = 0;
+    bool peers_ready = true, ready_checked = p.sp.world <= 1;
+    if (p.sp.world > 1) {
+        epoch = *reinterpret_cast<volatile uint32_t*>(p.sp.flags[p.sp.me] + kFlagEpoch) + 1;
+        // (a relaxed store: it publishes no data of this kernel, only that the kernel has started)
+        if (blockIdx.x == 0 && tid < p.sp.world && tid != p.sp.me) st_relaxed_sys(p.sp.flags[tid] + kFlagReady + p.sp.me, epoch);
+    }
     if (kXFirst && p.chained && has_work) load_x_raw<BITS, MT>(p, kb_lo + warp, g, t, xr);
     bool x_loaded = kXFirst;  // (of the first run)
 
@@ -412,9 +532,29 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
                 }
             }
         }
-        batch_end<MT>(p, reinterpret_cast<const float*>(part), b0, nt, kb_lo, nkl, s_flags, b0 + tb < rt_hi);
+        if (!ready_checked) {  // before the first remote store: has every peer started this call?
+            ready_checked = true;
+            int ok = 1;
+            if (tid < p.sp.world && tid != p.sp.me) ok = wait_flag(p.sp.flags[p.sp.me] + kFlagReady + tid, epoch);
+            peers_ready = __syncthreads_and(ok);
+        }
+        batch_end<MT>(p, reinterpret_cast<const float*>(part), b0, nt, kb_lo, nkl, s_flags, b0 + tb < rt_hi, peers_ready, epoch);
     }
     cp_async_wait<0>();
+    if (p.sp.world > 1) {
+        // the peers' columns: this CTA's share of the inbox goes into the local y; the launch ends when all
+        // shares are in.  The last CTA to finish moves the call number on.
+        const bool ok = peers_ready && unpack_inbox(p, epoch);
+        if (!__syncthreads_and(ok) && tid == 0 && p.error) *p.error = 2;
+        if (tid == 0) {
+            uint32_t* lf = p.sp.flags[p.sp.me];
+            __threadfence();
+            if (atomicAdd(lf + kFlagCtaDone, 1u) == gridDim.x - 1) {
+                lf[kFlagCtaDone] = 0;
+                *reinterpret_cast<volatile uint32_t*>(lf + kFlagEpoch) = epoch;
+            }
+        }
+    }
 }
 
 struct Plan {
@@ -504,7 +644,7 @@ size_t qmv_mma_workspace_bytes(const QmmArgs& a, int sm_count) {
 // workspace layout: [counters: n_rt x u32, padded to 256 B][partials]; the counters must
 // be zero before the first launch and are left zero by every launch.
 cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name,
-                           bool overlap_prev) {
+                           bool overlap_prev, const ShardPush* push) {
     Plan pl;
     if (!make_plan(a, sm_count, &pl)) return cudaErrorInvalidValue;
     Params p;
@@ -521,6 +661,15 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
     p.nkb = pl.nkb; p.n_rt = pl.n_rt;
     p.chunks = pl.chunks; p.ks = pl.ks; p.tb = pl.tb; p.sb_bytes = pl.sb_bytes;
     p.chained = overlap_prev ? 1 : 0;
+    p.ld = a.N; p.col0 = 0;
+    p.error = nullptr;
+    if (push && push->world > 1) {
+        if (push->world > kMaxShardWorld || (a.N & 15)) return cudaErrorInvalidValue;  // whole 16-column tiles only
+        p.sp = *push;
+        p.ld = push->ld; p.col0 = push->col0;
+        p.error = device_error_word();
+        if (!p.error) return cudaErrorMemoryAllocation;
+    }
     if (a.bits == 4) {
         if (name) *name = pl.mt == 1 ? "qmv_mma<4,m8>" : "qmv_mma<4,m16>";
         return pl.mt == 1 ? launch_t<4, 1>(p, pl, stream, overlap_prev) : launch_t<4, 2>(p, pl, stream, overlap_prev);

@@ -58,8 +58,6 @@ void note_decode_launch(Context* c, const QmmArgs& a) {
     c->chain_out_hi = (const char*)a.y + (size_t)a.M * a.N * (a.y_dtype == LUX_DTYPE_BFLOAT16 ? 2 : 4);
 }
 
-namespace {
-
 LuxBackendError ensure_qmv_workspace(Context* c, size_t bytes) {
     if (bytes <= c->qmv_ws_bytes) return LUX_BACKEND_OK;
     cudaError_t e = cudaSuccess;
@@ -77,8 +75,6 @@ LuxBackendError ensure_qmv_workspace(Context* c, size_t bytes) {
     c->qmv_ws_bytes = bytes;
     return LUX_BACKEND_OK;
 }
-
-}  // namespace
 
 LuxBackendError qmatmul_on_stream(Context* c, const QmmArgs& a) {
     if (a.M == 0 || a.N == 0) return LUX_BACKEND_OK;
@@ -429,6 +425,7 @@ void fill_quant() {
     g_quant.graph_launch = graph_launch;
     g_quant.graph_destroy = graph_destroy;
     fill_shard_entries(&g_quant);
+    fill_symm_entries(&g_quant);
 }
 
 }  // namespace

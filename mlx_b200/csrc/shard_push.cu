@@ -1,0 +1,201 @@
+// Column-sharded decode matmul whose all-gather is done by the matmul kernel itself: every rank keeps a
+// full copy of y in a buffer its peers can store into ("symmetric buffer"), the decode kernel writes its
+// columns into all copies over NVLink (peer pointers, plain stores) and ends when the peers' columns have
+// arrived (flag words at the head of each buffer; qmv_mma.cu has the protocol).  One launch per call, no
+// collective library on the data path, no interleave pass, and the launch can be recorded in a CUDA graph.
+//
+// Peers in other processes are reached through CUDA IPC handles, peers in the same process directly.
+// The reference has no multi-device path beyond create_context(device_index)
+// (include/lux/gpu/backend_plugin.h:84).
+#include <unistd.h>
+
+#include <cstring>
+#include <new>
+
+#include "internal.h"
+
+struct LuxCudaSymmBuffer {
+    luxcuda::Context* ctx = nullptr;
+    int rank = 0, world = 1;
+    void* base = nullptr;   // cudaMalloc: [flag words, kHeader bytes][data][inbox: 2 x data]
+    size_t bytes = 0;       // of the data part
+    luxcuda::Buffer view;   // the data part as an ordinary (non-owning) buffer
+    void* peer_base[luxcuda::kMaxShardWorld] = {};
+    bool ipc_opened[luxcuda::kMaxShardWorld] = {};
+    bool attached = false;
+};
+
+namespace luxcuda {
+
+namespace {
+
+constexpr size_t kHeader = 256;
+
+struct Handle {  // what travels between ranks; LUX_CUDA_SYMM_HANDLE_BYTES
+    uint64_t pid;
+    int32_t device;
+    int32_t rank;
+    uint64_t ptr;
+    cudaIpcMemHandle_t ipc;
+    uint8_t pad[LUX_CUDA_SYMM_HANDLE_BYTES - 24 - sizeof(cudaIpcMemHandle_t)];
+};
+static_assert(sizeof(Handle) == LUX_CUDA_SYMM_HANDLE_BYTES, "handle size");
+
+LuxBackendError symm_alloc(LuxBackendContext* ctx, int rank, int world, size_t bytes, LuxCudaSymmBuffer** out) {
+    Context* c = as_ctx(ctx);
+    if (!c || !out || world < 1 || world > kMaxShardWorld || rank < 0 || rank >= world || bytes == 0)
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    auto* sb = new (std::nothrow) LuxCudaSymmBuffer();
+    if (!sb) return LUX_BACKEND_ERROR_OUT_OF_MEMORY;
+    DeviceGuard g(c->dev->device());
+    // a whole driver allocation of its own: that is what an IPC handle names
+    const size_t data = (bytes + 255) & ~size_t(255);  // the inbox (8 bytes per 4 bytes of a peer's columns) follows
+    cudaError_t e = cudaMalloc(&sb->base, kHeader + 3 * data);
+    if (e == cudaSuccess) e = cudaMemset(sb->base, 0, kHeader + 3 * data);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        if (sb->base) cudaFree(sb->base);
+        delete sb;
+        return map_cuda_error(e, "symm_alloc");
+    }
+    sb->ctx = c;
+    sb->rank = rank;
+    sb->world = world;
+    sb->bytes = bytes;
+    sb->view.dev = c->dev;
+    sb->view.block = nullptr;
+    sb->view.ptr = static_cast<char*>(sb->base) + kHeader;
+    sb->view.bytes = bytes;
+    sb->view.last_stream = c->stream;
+    sb->peer_base[rank] = sb->base;
+    sb->attached = world == 1;
+    *out = sb;
+    return LUX_BACKEND_OK;
+}
+
+LuxBackendError symm_export(LuxCudaSymmBuffer* sb, void* handle_out) {
+    if (!sb || !handle_out) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    Handle h;
+    memset(&h, 0, sizeof(h));
+    h.pid = (uint64_t)getpid();
+    h.device = sb->ctx->dev->device();
+    h.rank = sb->rank;
+    h.ptr = (uint64_t)(uintptr_t)sb->base;
+    DeviceGuard g(sb->ctx->dev->device());
+    LUX_CUDA_TRY(cudaIpcGetMemHandle(&h.ipc, sb->base));
+    memcpy(handle_out, &h, sizeof(h));
+    return LUX_BACKEND_OK;
+}
+
+LuxBackendError symm_attach(LuxCudaSymmBuffer* sb, const void* handles) {
+    if (!sb || !handles) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (sb->attached) return LUX_BACKEND_OK;
+    const int dev = sb->ctx->dev->device();
+    DeviceGuard g(dev);
+    for (int r = 0; r < sb->world; r++) {
+        if (r == sb->rank) continue;
+        Handle h;
+        memcpy(&h, static_cast<const char*>(handles) + (size_t)r * sizeof(Handle), sizeof(h));
+        if (h.rank != r) {
+            set_last_error("symm_attach: handle %d belongs to rank %d (handles must be in rank order)", r, h.rank);
+            return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+        }
+        if (h.pid == (uint64_t)getpid()) {  // same process: the pointer itself, once the GPUs may reach each other
+            if (h.device != dev) {
+                cudaError_t e = cudaDeviceEnablePeerAccess(h.device, 0);
+                if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+                else if (e != cudaSuccess) return map_cuda_error(e, "cudaDeviceEnablePeerAccess");
+            }
+            sb->peer_base[r] = (void*)(uintptr_t)h.ptr;
+        } else {
+            LUX_CUDA_TRY(cudaIpcOpenMemHandle(&sb->peer_base[r], h.ipc, cudaIpcMemLazyEnablePeerAccess));
+            sb->ipc_opened[r] = true;
+        }
+    }
+    sb->attached = true;
+    return LUX_BACKEND_OK;
+}
+
+LuxBackendBuffer* symm_buffer(LuxCudaSymmBuffer* sb) {
+    return sb ? reinterpret_cast<LuxBackendBuffer*>(&sb->view) : nullptr;
+}
+
+// The caller makes sure no peer still stores into the buffer (all ranks past their last call).
+void symm_free(LuxCudaSymmBuffer* sb) {
+    if (!sb) return;
+    DeviceGuard g(sb->ctx->dev->device());
+    cudaStreamSynchronize(sb->ctx->stream);
+    for (int r = 0; r < sb->world; r++)
+        if (sb->ipc_opened[r]) cudaIpcCloseMemHandle(sb->peer_base[r]);
+    cudaFree(sb->base);
+    delete sb;
+}
+
+LuxBackendError qmatmul_sharded_push(LuxCudaSymmBuffer* sb, LuxBackendBuffer* x, LuxBackendBuffer* wq, LuxBackendBuffer* scales,
+                                     LuxBackendBuffer* biases, int M, int K, int Nl, int bits, int group,
+                                     LuxBackendDtype y_dtype) {
+    if (!sb) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    Context* c = sb->ctx;
+    Buffer *bx = as_buf(x), *bw = as_buf(wq), *bs = as_buf(scales), *bb = as_buf(biases);
+    if (!bx || !bw || !bs || !bb) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (y_dtype != LUX_DTYPE_BFLOAT16 && y_dtype != LUX_DTYPE_FLOAT32) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (!sb->attached) {
+        set_last_error("qmatmul_sharded_push: symm_attach has not been called");
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    }
+    if (M < 1 || M > 16 || Nl < 1 || (Nl & 15) || K < 1 || (bits != 4 && bits != 8) ||
+        (group != 32 && group != 64 && group != 128) || K % group) {
+        set_last_error("qmatmul_sharded_push: needs 1 <= M <= 16, N_local a multiple of 16, bits 4|8, group 32|64|128");
+        return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    }
+    const size_t ys = y_dtype == LUX_DTYPE_BFLOAT16 ? 2 : 4;
+    const size_t ld = (size_t)Nl * sb->world;
+    if ((size_t)M * K * 2 > bx->bytes || (size_t)Nl * K * bits / 8 > bw->bytes || (size_t)Nl * (K / group) * 2 > bs->bytes ||
+        (size_t)Nl * (K / group) * 2 > bb->bytes || (size_t)M * ld * ys > sb->bytes) {
+        set_last_error("qmatmul_sharded_push: a buffer is smaller than its shape needs");
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    }
+    QmmArgs a{bx->ptr, (const uint32_t*)bw->ptr, bs->ptr, bb->ptr, sb->view.ptr, M, K, Nl, bits, group,
+              LUX_DTYPE_BFLOAT16, LUX_DTYPE_BFLOAT16, (int)y_dtype};
+    std::lock_guard<std::mutex> lk(c->mu);
+    DeviceGuard g(c->dev->device());
+    if (!qmv_mma_supported(a)) {
+        set_last_error("qmatmul_sharded_push: shape not taken by the decode kernel (K must be a multiple of %d)", 1024 / bits);
+        return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    }
+    LuxBackendError le = ensure_qmv_workspace(c, qmv_mma_workspace_bytes(a, c->dev->sm_count));
+    if (le != LUX_BACKEND_OK) return le;
+    ShardPush sp;
+    sp.world = sb->world;
+    sp.me = sb->rank;
+    sp.ld = (int)ld;
+    sp.col0 = sb->rank * Nl;
+    sp.inbox_off = (sb->bytes + 255) & ~size_t(255);
+    for (int r = 0; r < sb->world; r++) {
+        sp.flags[r] = static_cast<uint32_t*>(sb->peer_base[r]);
+        sp.y[r] = static_cast<char*>(sb->peer_base[r]) + kHeader;
+    }
+    QmmArgs whole = a;  // what the launch writes, for the chain bookkeeping: every column of the local copy
+    whole.N = (int)ld;
+    const char* name = "";
+    cudaError_t e = launch_qmv_mma(a, c->qmv_ws->ptr, c->dev->sm_count, c->stream, &name, decode_may_overlap(c, a), &sp);
+    if (e != cudaSuccess) return map_cuda_error(e, name);
+    c->last_kernel = name;
+    c->launches++;
+    note_decode_launch(c, whole);
+    bx->last_stream = bw->last_stream = bs->last_stream = bb->last_stream = sb->view.last_stream = c->stream;
+    return LUX_BACKEND_OK;
+}
+
+}  // namespace
+
+void fill_symm_entries(lux_gpu_quant_vtbl* t) {
+    t->symm_alloc = symm_alloc;
+    t->symm_export = symm_export;
+    t->symm_attach = symm_attach;
+    t->symm_buffer = symm_buffer;
+    t->symm_free = symm_free;
+    t->qmatmul_sharded_push = qmatmul_sharded_push;
+}
+
+}  // namespace luxcuda

@@ -127,7 +127,17 @@ class QuantVtbl(C.Structure):  # include/lux_cuda_quant.h: lux_gpu_quant_vtbl
         ("qmatmul_sharded", _fn(_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i)),
         ("shard_group_begin", _fn(_i)),
         ("shard_group_end", _fn(_i)),
+        # version >= 2
+        ("symm_alloc", _fn(_i, _vp, _i, _i, _sz, C.POINTER(_vp))),
+        ("symm_export", _fn(_i, _vp, _vp)),
+        ("symm_attach", _fn(_i, _vp, _vp)),
+        ("symm_buffer", _fn(_vp, _vp)),
+        ("symm_free", _fn(None, _vp)),
+        ("qmatmul_sharded_push", _fn(_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i)),
     ]
+
+
+SYMM_HANDLE_BYTES = 96  # LUX_CUDA_SYMM_HANDLE_BYTES
 
 
 EXPORTED_SYMBOLS = ("lux_gpu_backend_init", "lux_gpu_cuda_quant_vtbl", "lux_gpu_cuda_abi_layout",
@@ -239,9 +249,9 @@ class Buffer:
         return self.ctx.plugin.quant.buffer_device_ptr(self.ctx.handle, self.handle)
 
     def free(self):
-        if self.handle:
+        if self.handle and not getattr(self, "borrowed", False):
             self.ctx.plugin.vtbl.buffer_free(self.ctx.handle, self.handle)
-            self.handle = None
+        self.handle = None
 
 
 class Context:
@@ -411,6 +421,45 @@ class Context:
     def upload_async(self, buf, pinned_ptr, nbytes):
         self.plugin.check(self.plugin.quant.buffer_copy_from_host_async(self.handle, buf.handle, pinned_ptr, nbytes),
                           "buffer_copy_from_host_async")
+
+
+class SymmBuffer:
+    """One rank's copy of y_full[M, world*N_local] that the peers store into (symm_* entry points)."""
+
+    def __init__(self, ctx, rank, world, shape, dtype):
+        self.ctx, self.rank, self.world = ctx, rank, world
+        self.shape, self.dtype = tuple(shape), np.dtype(dtype)
+        nbytes = int(np.prod(shape)) * self.dtype.itemsize
+        h = _vp()
+        ctx.plugin.check(ctx.plugin.quant.symm_alloc(ctx.handle, rank, world, nbytes, C.byref(h)), "symm_alloc")
+        self.handle = h
+        self.buffer = Buffer(ctx, ctx.plugin.quant.symm_buffer(h), nbytes, self.shape, self.dtype, owned=False)
+        self.buffer.borrowed = True  # lives inside the symmetric buffer: never handed to buffer_free
+
+    def export(self):
+        out = (C.c_ubyte * SYMM_HANDLE_BYTES)()
+        self.ctx.plugin.check(self.ctx.plugin.quant.symm_export(self.handle, out), "symm_export")
+        return bytes(out)
+
+    def attach(self, handles):
+        """handles: the export() of every rank, in rank order."""
+        blob = b"".join(handles)
+        assert len(blob) == SYMM_HANDLE_BYTES * self.world
+        buf = (C.c_ubyte * len(blob)).from_buffer_copy(blob)
+        self.ctx.plugin.check(self.ctx.plugin.quant.symm_attach(self.handle, buf), "symm_attach")
+
+    def qmatmul(self, x, wq, scales, biases, M, K, N_local, bits, group, y_dtype):
+        self.ctx.plugin.check(
+            self.ctx.plugin.quant.qmatmul_sharded_push(self.handle, x.handle, wq.handle, scales.handle, biases.handle,
+                                                       M, K, N_local, bits, group, y_dtype), "qmatmul_sharded_push")
+
+    def to_host(self):
+        return self.buffer.to_host(self.shape, self.dtype)
+
+    def free(self):
+        if self.handle:
+            self.ctx.plugin.quant.symm_free(self.handle)
+            self.handle = None
 
 
 class QuantizedLinear:

@@ -1,0 +1,59 @@
+"""Symmetric buffers and the decode matmul that does its own all-gather (symm_*, qmatmul_sharded_push).
+
+With one GPU only world = 1 can run as a kernel: ranks that wait for one another must not share a GPU.
+The multi-rank path is checked (bit for bit, every rank's columns) by bench.py on 2, 4 and 8 GPUs, and
+this file runs that check itself when the box has at least two GPUs.
+"""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from mlx_b200 import BF16, BackendError
+from mlx_b200 import plugin as P
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_world_of_one_equals_plain_qmatmul(ctx, oracle):
+    M, K, N = 8, 1024, 256
+    wq, s, b = oracle.make_layer(N, K, 4, 64, oracle.BF16, config_id=8, layer=3)
+    x = oracle.make_x(M, K, oracle.BF16, config_id=8, tag=3)
+    bx, bw, bs, bb = ctx.upload(x), ctx.upload(wq), ctx.upload(s), ctx.upload(b)
+    y = ctx.empty((M, N), np.uint16)
+    ctx.qmatmul(bx, bw, bs, bb, y, M, K, N, 4, 64, BF16, BF16, BF16)
+    sb = P.SymmBuffer(ctx, 0, 1, (M, N), np.uint16)
+    assert len(sb.export()) == P.SYMM_HANDLE_BYTES
+    sb.qmatmul(bx, bw, bs, bb, M, K, N, 4, 64, BF16)
+    assert np.array_equal(sb.to_host(), y.to_host())
+    with pytest.raises(BackendError):  # N_local must be whole 16-column tiles
+        sb.qmatmul(bx, bw, bs, bb, M, K, N - 8, 4, 64, BF16)
+    sb.free()
+    for h in (bx, bw, bs, bb, y):
+        h.free()
+
+
+def test_attach_is_required_and_checks_rank_order(ctx):
+    sb = P.SymmBuffer(ctx, 0, 2, (4, 64), np.uint16)
+    dummy = ctx.empty((4, 64), np.uint16)
+    with pytest.raises(BackendError):
+        sb.qmatmul(dummy, dummy, dummy, dummy, 4, 64, 32, 4, 64, BF16)  # not attached
+    h = sb.export()
+    with pytest.raises(BackendError):
+        sb.attach([h, h])  # second handle says rank 0, not 1
+    sb.free()
+    dummy.free()
+
+
+def test_two_ranks_bit_exact(plugin):
+    if plugin.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29533", os.path.join(ROOT, "bench.py"), "--gpus", "2", "--steps", "1", "--warmup", "3", "--reps", "2",
+           "--kernel-only"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert '"verified": "all ranks' in r.stdout
