@@ -150,19 +150,24 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t e) {
 __device__ __forceinline__ void push_tile(const Params& p, uint32_t epoch, int rt, int tid_in_group, int group_threads) {
     const int esz = p.y_bf16 ? 2 : 4, wpt = 4 * esz;  // words (4 bytes of y each) per tile row: 8 | 16
     const int wpr = p.N * esz / 4;                    // words per row of this rank's columns
-    const int items = p.M * wpt * (p.sp.world - 1);
+    const int per_peer = p.M * wpt;
     const char* ylocal = static_cast<const char*>(p.sp.y[p.sp.me]);
-    for (int i = tid_in_group; i < items; i += group_threads) {
-        const int k = i % wpt, m = (i / wpt) % p.M;
-        int q = i / (wpt * p.M);
-        q += q >= p.sp.me;
+    // the tile's words of this rank's own y, read once, stored to every peer
+    for (int i = tid_in_group; i < per_peer; i += group_threads) {
+        const int k = i & (wpt - 1), m = i / wpt;
         const uint32_t v = __ldcg(reinterpret_cast<const uint32_t*>(ylocal + ((size_t)m * p.ld + p.col0 + rt * 16) * esz) + k);
-        unsigned long long* inbox = reinterpret_cast<unsigned long long*>(static_cast<char*>(p.sp.y[q]) + p.sp.inbox_off);
-        st_relaxed_sys64(inbox + ((size_t)p.sp.me * p.M + m) * wpr + rt * wpt + k, ((unsigned long long)epoch << 32) | v);
+        const unsigned long long word = ((unsigned long long)epoch << 32) | v;
+        const size_t off = ((size_t)p.sp.me * p.M + m) * wpr + rt * wpt + k;
+        for (int q = 0; q < p.sp.world; q++)
+            if (q != p.sp.me)
+                st_relaxed_sys64(reinterpret_cast<unsigned long long*>(static_cast<char*>(p.sp.y[q]) + p.sp.inbox_off) + off, word);
     }
 }
 // This CTA's share of the inbox -> local y.  Returns false if a word did not arrive in time.
+// Four words per thread are requested at once (a poll is an L2 round trip: one after the other they
+// would add up to microseconds), then whatever has not arrived yet is polled again.
 __device__ __forceinline__ bool unpack_inbox(const Params& p, uint32_t epoch) {
+    constexpr int U = 4;
     const int esz = p.y_bf16 ? 2 : 4;
     const int wpr = p.N * esz / 4;
     const int total = (p.sp.world - 1) * p.M * wpr;
@@ -170,25 +175,53 @@ __device__ __forceinline__ bool unpack_inbox(const Params& p, uint32_t epoch) {
     const int lo = blockIdx.x * per_cta, hi = min(total, lo + per_cta);
     char* ylocal = static_cast<char*>(p.sp.y[p.sp.me]);
     const unsigned long long* inbox = reinterpret_cast<const unsigned long long*>(ylocal + p.sp.inbox_off);
+    int i = lo + (int)threadIdx.x;
+    if (i >= hi) return true;
+    // position of word i: sender (skipping this rank), row, word in the row; advanced without divisions
+    int w = i % wpr, m = (i / wpr) % p.M, s = i / (wpr * p.M);
     bool ok = true;
-    for (int i = lo + (int)threadIdx.x; i < hi; i += kThreads) {
-        const int w = i % wpr, m = (i / wpr) % p.M;
-        int src = i / (wpr * p.M);
-        src += src >= p.sp.me;
-        const unsigned long long* slot = inbox + ((size_t)src * p.M + m) * wpr + w;
-        unsigned long long v = ld_relaxed_sys64(slot);
-        if ((uint32_t)(v >> 32) != epoch) {
-            const long long t0 = now_ns();
-            while (ok) {
-                v = ld_relaxed_sys64(slot);
-                if ((uint32_t)(v >> 32) == epoch) break;
-                if (peer_lost() || now_ns() - t0 > kPeerWaitNs) {
-                    g_peer_lost = 1;
-                    ok = false;
+    while (i < hi && ok) {
+        const unsigned long long* slot[U];
+        uint32_t* dst[U];
+        unsigned long long v[U];
+        int n = 0;
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            if (i < hi) {
+                const int src = s + (s >= p.sp.me);
+                slot[u] = inbox + ((size_t)src * p.M + m) * wpr + w;
+                dst[u] = reinterpret_cast<uint32_t*>(ylocal + ((size_t)m * p.ld + (size_t)src * p.N) * esz + (size_t)w * 4);
+                v[u] = ld_relaxed_sys64(slot[u]);
+                n = u + 1;
+                i += kThreads;
+                w += kThreads;
+                while (w >= wpr) {
+                    w -= wpr;
+                    if (++m == p.M) {
+                        m = 0;
+                        s++;
+                    }
                 }
             }
         }
-        if (ok) *reinterpret_cast<uint32_t*>(ylocal + ((size_t)m * p.ld + (size_t)src * p.N) * esz + (size_t)w * 4) = (uint32_t)v;
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            if (u < n) {
+                if ((uint32_t)(v[u] >> 32) != epoch) {
+                    const long long t0 = now_ns();
+                    for (;;) {
+                        v[u] = ld_relaxed_sys64(slot[u]);
+                        if ((uint32_t)(v[u] >> 32) == epoch) break;
+                        if (peer_lost() || now_ns() - t0 > kPeerWaitNs) {
+                            g_peer_lost = 1;
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+                if (ok) *dst[u] = (uint32_t)v[u];
+            }
+        }
     }
     return ok;
 }
