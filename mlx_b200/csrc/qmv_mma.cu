@@ -87,6 +87,7 @@ struct Params {
     int nkb, n_rt;
     int chunks, ks;          // grid = chunks (tile ranges) x ks (k-block ranges)
     int chained;             // launched as a programmatic dependent of the previous kernel
+    int xs_off;              // byte offset in shared memory of the x fragments kept there (16-row variant)
     int tb;                  // tiles per reduction batch
     int sb_bytes;            // bytes of scales per row per k-block: 2, 4, 8 or 16
     int ld, col0;            // y row stride and first column (elements): N and 0 unless the layer is column-sharded
@@ -302,12 +303,16 @@ __device__ __noinline__ void batch_end(const Params& p, const float* part, int f
     if (more) __syncthreads();  // the partial buffer and the flags are reused by the next batch
 }
 
+// With 16 rows of x the fragments of rows 8..15 live in shared memory (one conflict-free 16-byte read per
+// use) instead of 32 more registers per lane: at the 128-register limit the kernel otherwise spills.
+constexpr bool kX1Shared = true;
+
 // One task out of the warp's ring stage: 4 x 16 bytes of packed weights per
 // lane (rows g, g+8; pieces t, t+4), their scales/biases, times the x fragments.
 // stage layout: [piece = r*2+h][lane] 16 B  |  [row 0..15 scales][row 0..15 biases] 16 B each
 template <int BITS, int MT, bool FAST>
 __device__ __forceinline__ void task_mma(const uint4 (&w)[2][2], const uint32_t (&s)[2][2], const uint32_t (&b)[2][2],
-                                         const uint4 (&xr)[MT][BITS == 4 ? 8 : 4], float (&acc)[MT][2][4]) {
+                                         const uint4 (&xr)[MT][BITS == 4 ? 8 : 4], const uint4* xs, float (&acc)[MT][2][4]) {
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         uint32_t sa[2], sb[2], b2[2];
@@ -332,7 +337,7 @@ __device__ __forceinline__ void task_mma(const uint4 (&w)[2][2], const uint32_t 
                 }
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++) {
-                    const uint4 bx = xr[mt][h * 4 + i];
+                    const uint4 bx = (mt == 0 || !kX1Shared) ? xr[mt][h * 4 + i] : xs[(h * 4 + i) * 32];
                     mma_bf16(acc[mt][0], lo[0], hi[0], lo[1], hi[1], bx.x, bx.y);
                     mma_bf16(acc[mt][1], lo[2], hi[2], lo[3], hi[3], bx.z, bx.w);
                 }
@@ -354,7 +359,7 @@ __device__ __forceinline__ void task_mma(const uint4 (&w)[2][2], const uint32_t 
                 }
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++) {
-                    const uint4 bx = xr[mt][h * 2 + i];
+                    const uint4 bx = (mt == 0 || !kX1Shared) ? xr[mt][h * 2 + i] : xs[(h * 2 + i) * 32];
                     mma_bf16(acc[mt][0], lo0[0], hi0[0], lo0[1], hi0[1], bx.x, bx.y);
                     mma_bf16(acc[mt][1], lo1[0], hi1[0], lo1[1], hi1[1], bx.z, bx.w);
                 }
@@ -424,6 +429,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
     constexpr int E4 = MT * 32;            // float4 per partial
     extern __shared__ __align__(16) unsigned char smem[];
     float4* part = reinterpret_cast<float4*>(smem + kRingBytes);   // [tb][nkl][MT][32]; ring: [kWarps][kDepth][kStageBytes]
+    // after the partials (MT == 2): the x fragments of rows 8..15, [warp][fragment][lane]
+    uint4* xs = reinterpret_cast<uint4*>(smem + p.xs_off) + (threadIdx.x >> 5) * (XV * 32) + (threadIdx.x & 31);
     __shared__ int s_flags[kMaxTb];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -517,6 +524,12 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
                 if (!x_loaded) load_x_raw<BITS, MT>(p, kb, g, t, xr);
                 x_loaded = false;
                 permute_x<BITS, MT>(xr);
+                if (MT == 2 && kX1Shared) {
+                    __syncwarp();  // (the previous run's reads of xs)
+#pragma unroll
+                    for (int j = 0; j < XV; j++) xs[j * 32] = xr[MT - 1][j];
+                    __syncwarp();
+                }
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
                     const int slot = g + 8 * r;
@@ -553,8 +566,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
                     for (int mt = 0; mt < MT; mt++)
 #pragma unroll
                         for (int c = 0; c < 2; c++) acc[mt][c][0] = acc[mt][c][1] = acc[mt][c][2] = acc[mt][c][3] = 0.0f;
-                    if (__all_sync(0xffffffffu, fast)) task_mma<BITS, MT, true>(w, s, b, xr, acc);
-                    else task_mma<BITS, MT, false>(w, s, b, xr, acc);
+                    if (__all_sync(0xffffffffu, fast)) task_mma<BITS, MT, true>(w, s, b, xr, xs, acc);
+                    else task_mma<BITS, MT, false>(w, s, b, xr, xs, acc);
 #pragma unroll
                     for (int mt = 0; mt < MT; mt++)
                         dstp[mt * 32] = make_float4(acc[mt][0][0] + acc[mt][1][0], acc[mt][0][1] + acc[mt][1][1],
@@ -591,7 +604,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
 }
 
 struct Plan {
-    int nkb, n_rt, mt, chunks, ks, tb, gshift, sb_bytes;
+    int nkb, n_rt, mt, chunks, ks, tb, gshift, sb_bytes, xs_off;
     size_t smem, ctr_bytes, scratch_bytes;
 };
 
@@ -622,10 +635,12 @@ bool make_plan(const QmmArgs& a, int sm_count, Plan* pl) {
     const int tiles_max = (pl->n_rt + pl->chunks - 1) / pl->chunks;
     const int nkl_max = (pl->nkb + ks - 1) / ks;
     const size_t per_tile = (size_t)nkl_max * pl->mt * 512;
-    const size_t avail = (size_t)kSmemLimit - kRingBytes;
+    const size_t xs_bytes = pl->mt == 2 ? (size_t)kWarps * (a.bits == 4 ? 8 : 4) * 512 : 0;  // x fragments of rows 8..15
+    const size_t avail = (size_t)kSmemLimit - kRingBytes - xs_bytes;
     if (per_tile > avail) return false;
     pl->tb = (int)std::min<size_t>(std::min<size_t>(tiles_max, avail / per_tile), kMaxTb);
-    pl->smem = kRingBytes + pl->tb * per_tile;
+    pl->xs_off = (int)(kRingBytes + pl->tb * per_tile);
+    pl->smem = kRingBytes + pl->tb * per_tile + xs_bytes;
     pl->ctr_bytes = ((size_t)pl->n_rt * sizeof(unsigned int) + 255) & ~size_t(255);
     pl->scratch_bytes = ks > 1 ? (size_t)pl->n_rt * pl->nkb * pl->mt * 128 * sizeof(float) : 0;
     if (((uintptr_t)a.wq & 15) || ((uintptr_t)a.x & 15) || ((uintptr_t)a.scales & 15) || ((uintptr_t)a.biases & 15)) return false;
@@ -694,6 +709,7 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
     p.nkb = pl.nkb; p.n_rt = pl.n_rt;
     p.chunks = pl.chunks; p.ks = pl.ks; p.tb = pl.tb; p.sb_bytes = pl.sb_bytes;
     p.chained = overlap_prev ? 1 : 0;
+    p.xs_off = pl.xs_off;
     p.ld = a.N; p.col0 = 0;
     p.error = nullptr;
     if (push && push->world > 1) {
