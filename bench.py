@@ -195,6 +195,70 @@ def prefill_legs(ctx, O, BF16, peaks):
     return out
 
 
+def chain_leg(ctx, O, BF16, peaks):
+    """BASELINE.json configs[4] at one GPU: one decode step (M = 8) through 32 layers of quantized projections
+    (q,k,v,o 4096x4096; gate,up 11008x4096; down 4096x11008; 4-bit g64) with the rms-norms between them.
+    q/k/v run as one N = 12288 launch and gate/up as one N = 22016 launch (the configuration allows it: same
+    results), so a layer is 4 matmul launches + 3 rms-norm launches, each ordered behind the one before.
+    Four distinct layers' weights (455 MB, more than L2) are cycled eight times: a layer's weights were last
+    read three layers earlier.  The bf16 adds / products between projections of the full dataflow (elementwise,
+    64-176 KB) are left out; their inputs are stand-in buffers of the right shape."""
+    M, D, FF, L, DISTINCT = 8, 4096, 11008, 32, 4
+    shapes = [("qkv", 3 * D, D), ("o", D, D), ("gateup", 2 * FF, D), ("down", D, FF)]
+    layers = []
+    for l in range(DISTINCT):
+        ws = {}
+        for pi, (name, N, K) in enumerate(shapes):
+            wq, s, b = O.make_layer(N, K, BITS, GROUP, O.BF16, config_id=5, layer=l, proj=pi)
+            ws[name] = (ctx.upload(wq), ctx.upload(s), ctx.upload(b), N, K)
+        layers.append(ws)
+    h = ctx.upload(O.make_x(M, D, O.BF16, config_id=5))
+    a = ctx.upload(O.make_x(M, D, O.BF16, config_id=5, tag=1))     # stands for bf16(q + k + v)
+    gu = ctx.upload(O.make_x(M, FF, O.BF16, config_id=5, tag=2))   # stands for bf16(gate * up)
+    t = {n: ctx.empty((M, N), np.uint16) for n, N in (("qkv", 3 * D), ("o", D), ("r", D), ("gateup", 2 * FF), ("m", FF), ("d", D))}
+
+    def mm(ws, name, src, dst):
+        bw, bs, bb, N, K = ws[name]
+        ctx.qmatmul(src, bw, bs, bb, dst, M, K, N, BITS, GROUP, BF16, BF16, BF16)
+
+    def step():
+        for l in range(L):
+            ws = layers[l % DISTINCT]
+            mm(ws, "qkv", h, t["qkv"])
+            mm(ws, "o", a, t["o"])
+            ctx.rms_norm(t["o"], t["r"], M, D, 1e-6, BF16, BF16)
+            mm(ws, "gateup", t["r"], t["gateup"])
+            ctx.rms_norm(gu, t["m"], M, FF, 1e-6, BF16, BF16)
+            mm(ws, "down", t["m"], t["d"])
+            ctx.rms_norm(t["d"], h, M, D, 1e-6, BF16, BF16)
+
+    step()
+    ctx.sync()
+    ctx.graph_begin()
+    step()
+    g = ctx.graph_end()
+    for _ in range(3):
+        ctx.graph_launch(g)
+    ctx.sync()
+    iters = 10
+    ctx.timer_record(8)
+    for _ in range(iters):
+        ctx.graph_launch(g)
+    ctx.timer_record(9)
+    ms = ctx.timer_elapsed_ms(8, 9) / iters
+    nbytes = L * sum(alg_bytes(M, K, N) for _, N, K in shapes)
+    gbs = nbytes / ms / 1e6
+    ctx.graph_destroy(g)
+    for ws in layers:
+        for (bw, bs, bb, _, _) in ws.values():
+            bw.free(); bs.free(); bb.free()
+    for b in list(t.values()) + [h, a, gu]:
+        b.free()
+    return {"workload": "32 layers x (qkv, o, gate/up, down) + 3 rms-norms, M=8, one GPU, one CUDA graph per step",
+            "ms_per_step": ms, "launches_per_step": L * 7, "algorithmic_GB": nbytes / 1e9, "GBps": gbs,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"]}}
+
+
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
@@ -216,6 +280,10 @@ def run_ours(args, rank, world):
     if args.prefill_only:
         peaks, _ = measured_peaks()
         print(json.dumps({"prefill": prefill_legs(ctx, O, BF16, peaks)}))
+        return
+    if args.chain_only:
+        peaks, _ = measured_peaks()
+        print(json.dumps({"chain": chain_leg(ctx, O, BF16, peaks)}))
         return
 
     # resident inputs: R weight sets (each rank: its own column slice), x per M
@@ -403,6 +471,7 @@ def run_ours(args, rank, world):
 
     peaks, which = measured_peaks()
     prefill = prefill_legs(ctx, O, BF16, peaks) if (world == 1 and not args.kernel_only) else None
+    chain = chain_leg(ctx, O, BF16, peaks) if (world == 1 and not args.kernel_only) else None
     if dist is not None:
         ctx.sync()
         dist.barrier()
@@ -439,6 +508,7 @@ def run_ours(args, rank, world):
                      "traffic_over_algorithmic": args.traffic_bytes / alg_bytes(1) if args.traffic_bytes else None},
         "per_M": {str(M): per_m[M] for M in M_SWEEP},
         "prefill": prefill,
+        "chain": chain,
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "calls": e2e_calls, "us_per_call": ms_e2e * 1e3 / max(1, e2e_calls),
@@ -462,6 +532,7 @@ def main():
                     help="skip the e2e and CPU-baseline legs (for short runs under a profiler)")
     ap.add_argument("--nccl-allgather", action="store_true",
                     help="N>1: gather the column slices with NCCL + an interleave pass instead of peer stores from the kernel")
+    ap.add_argument("--chain-only", action="store_true", help="run only the quantized-linear chain leg")
     ap.add_argument("--prefill-only", action="store_true", help="run only the tensor-bound legs (short, for profiling)")
     ap.add_argument("--traffic-bytes", type=float, default=NCU_TRAFFIC_BYTES,
                     help="dram bytes per launch from the committed ncu summary (profiles/), echoed into roofline.traffic")

@@ -180,6 +180,8 @@ size_t qmv_mma_workspace_bytes(const QmmArgs& a, int sm_count);
 cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name,
                            bool overlap_prev = false, const ShardPush* push = nullptr);
 bool decode_may_overlap(const Context* c, const QmmArgs& a);
+bool chain_is_open(const Context* c);  // the last thing the context enqueued is a chain kernel (decode matmul, rms-norm)
+void note_chain_launch(Context* c, const void* out, size_t out_bytes);  // right after such a launch, before counting it
 void note_decode_launch(Context* c, const QmmArgs& a);  // call right after a decode launch, before counting it
 // decode / small-M, any supported dtype combination: CUDA cores + warp shuffles
 cudaError_t launch_qmv_simt(const QmmArgs& a, cudaStream_t stream, const char** name);
@@ -196,7 +198,7 @@ cudaError_t launch_unpack(const uint32_t* wq, uint8_t* q, int N, int K, int bits
 cudaError_t launch_quantize(const float* w, uint32_t* wq, void* scales, void* biases, int N, int K, int bits,
                             int group, int sb_dtype, cudaStream_t stream);
 cudaError_t launch_rms_norm(const void* in, void* out, const float* weight, size_t rows, size_t dim, float eps,
-                            int in_dtype, int out_dtype, cudaStream_t stream);
+                            int in_dtype, int out_dtype, cudaStream_t stream, bool overlap_prev = false);
 cudaError_t launch_gather_columns(const void* staging, void* y_full, int world, int M, int n_local, int elem_size,
                                   cudaStream_t stream);
 cudaError_t launch_flush(void* buf, size_t bytes, cudaStream_t stream);

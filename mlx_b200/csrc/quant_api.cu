@@ -42,10 +42,19 @@ LuxBackendError check_format(int K, int bits, int group) {
 static bool ranges_overlap(const char* a_lo, size_t a_bytes, const char* b_lo, const char* b_hi) {
     return a_lo < b_hi && b_lo < a_lo + a_bytes;
 }
-bool decode_may_overlap(const Context* c, const QmmArgs& a) {
+bool chain_is_open(const Context* c) {
     static const bool disabled = getenv("LUXCUDA_NO_PDL") != nullptr;
     if (disabled || c->stream_exposed) return false;
-    if (c->chain_launches != c->launches.load() || c->chain_copies != c->copies.load()) return false;
+    return c->chain_launches == c->launches.load() && c->chain_copies == c->copies.load();
+}
+void note_chain_launch(Context* c, const void* out, size_t out_bytes) {
+    c->chain_launches = c->launches.load();
+    c->chain_copies = c->copies.load();
+    c->chain_out_lo = (const char*)out;
+    c->chain_out_hi = (const char*)out + out_bytes;
+}
+bool decode_may_overlap(const Context* c, const QmmArgs& a) {
+    if (!chain_is_open(c)) return false;
     const size_t sb = (size_t)a.N * (a.K / a.group) * 2;
     return !ranges_overlap((const char*)a.wq, (size_t)a.N * a.K * a.bits / 8, c->chain_out_lo, c->chain_out_hi) &&
            !ranges_overlap((const char*)a.scales, sb, c->chain_out_lo, c->chain_out_hi) &&
@@ -225,9 +234,11 @@ LuxBackendError rms_norm(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBacken
         return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     std::lock_guard<std::mutex> lk(c->mu);
     DeviceGuard g(c->dev->device());
+    // behind a chain kernel the whole kernel waits for it on the device (it reads nothing before that wait)
     LUX_CUDA_TRY(launch_rms_norm(bi->ptr, bo->ptr, bw ? (const float*)bw->ptr : nullptr, rows, dim, eps, (int)in_dtype,
-                                 (int)out_dtype, c->stream));
+                                 (int)out_dtype, c->stream, chain_is_open(c)));
     c->launches++;
+    note_chain_launch(c, bo->ptr, rows * dim * os);
     bi->last_stream = bo->last_stream = c->stream;
     return LUX_BACKEND_OK;
 }

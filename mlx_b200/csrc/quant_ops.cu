@@ -166,38 +166,72 @@ cudaError_t launch_quantize(const float* w, uint32_t* wq, void* scales, void* bi
     return cudaGetLastError();
 }
 
-// y = x * rsqrt(mean(x^2) + eps) * w, fp32 math (kernels/cpu/tensor_ops.c:546-566)
-__global__ void rms_norm_kernel(const void* __restrict__ in, void* __restrict__ out, const float* __restrict__ weight,
-                                size_t dim, float eps, int in_dtype, int out_dtype) {
+// y = x * rsqrt(mean(x^2) + eps) * w, fp32 math (kernels/cpu/tensor_ops.c:546-566).
+// One 1024-thread block per row; a thread keeps its (up to kRmsCache) elements in registers between the
+// sum of squares and the scaling, so a row is read once.  In a decode chain the kernel is launched as a
+// programmatic dependent of the kernel before it: everything it does sits behind griddepcontrol.wait.
+constexpr int kRmsThreads = 1024, kRmsCache = 16;
+__global__ void __launch_bounds__(kRmsThreads) rms_norm_kernel(const void* __restrict__ in, void* __restrict__ out,
+                                                               const float* __restrict__ weight, size_t dim, float eps,
+                                                               int in_dtype, int out_dtype) {
     __shared__ float red[32];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const size_t r = blockIdx.x;
+    const bool cached = dim <= (size_t)kRmsThreads * kRmsCache;
+    float v[kRmsCache];
     float ss = 0.0f;
-    for (size_t i = threadIdx.x; i < dim; i += blockDim.x) {
-        const float v = load_sb(in, r * dim + i, in_dtype);
-        ss = fmaf(v, v, ss);
+    if (cached) {
+#pragma unroll
+        for (int j = 0; j < kRmsCache; j++) {
+            const size_t i = threadIdx.x + (size_t)j * kRmsThreads;
+            v[j] = i < dim ? load_sb(in, r * dim + i, in_dtype) : 0.0f;
+            ss = fmaf(v[j], v[j], ss);
+        }
+    } else {
+        for (size_t i = threadIdx.x; i < dim; i += kRmsThreads) {
+            const float x = load_sb(in, r * dim + i, in_dtype);
+            ss = fmaf(x, x, ss);
+        }
     }
     for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
     __syncthreads();
     if (threadIdx.x < 32) {
-        float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.0f;
+        float t = red[threadIdx.x];
         for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
         if (threadIdx.x == 0) red[0] = t;
     }
     __syncthreads();
     const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(red[0], (float)dim), eps)));
-    for (size_t i = threadIdx.x; i < dim; i += blockDim.x) {
-        const float v = load_sb(in, r * dim + i, in_dtype);
-        const float o = __fmul_rn(__fmul_rn(v, inv), weight ? weight[i] : 1.0f);
+    auto put = [&](size_t i, float x) {
+        const float o = __fmul_rn(__fmul_rn(x, inv), weight ? weight[i] : 1.0f);
         if (out_dtype == LUX_DTYPE_BFLOAT16) ((__nv_bfloat16*)out)[r * dim + i] = __float2bfloat16_rn(o);
         else ((float*)out)[r * dim + i] = o;
+    };
+    if (cached) {
+#pragma unroll
+        for (int j = 0; j < kRmsCache; j++) {
+            const size_t i = threadIdx.x + (size_t)j * kRmsThreads;
+            if (i < dim) put(i, v[j]);
+        }
+    } else {
+        for (size_t i = threadIdx.x; i < dim; i += kRmsThreads) put(i, load_sb(in, r * dim + i, in_dtype));
     }
 }
 cudaError_t launch_rms_norm(const void* in, void* out, const float* weight, size_t rows, size_t dim, float eps,
-                            int in_dtype, int out_dtype, cudaStream_t stream) {
+                            int in_dtype, int out_dtype, cudaStream_t stream, bool overlap_prev) {
     if (!rows || !dim) return cudaSuccess;
-    rms_norm_kernel<<<(unsigned)rows, 256, 0, stream>>>(in, out, weight, dim, eps, in_dtype, out_dtype);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)rows);
+    cfg.blockDim = dim3(kRmsThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap_prev ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, rms_norm_kernel, in, out, weight, dim, eps, in_dtype, out_dtype);
 }
 
 }  // namespace luxcuda
