@@ -3,7 +3,7 @@
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
 
-Workload at N = 1 (BASELINE.json configs[1], the one the metric is quoted on):
+Workload at N = 1 (the decode configuration the metric is quoted on):
 the decode GEMV sweep  x bf16 [M in {1,4,8,16}, K=4096] . W^T,  W [N=11008,
 K=4096] 4-bit affine, group 64, bf16 scales/biases, fp32 accumulate, bf16 out.
 A "step" is REPS passes over the sweep; every launch reads a different one of
@@ -159,7 +159,7 @@ def run_reference(args, rank):
 
 
 def prefill_legs(ctx, O, BF16, peaks):
-    """Tensor-bound legs (BASELINE.json configs[2] and [3] at one GPU): TFLOP/s = 2*M*N*K / device time.
+    """Tensor-bound legs (the prefill and the 8-bit large-GEMM configurations at one GPU): TFLOP/s = 2*M*N*K / device time.
     Rotating input sets keep every launch's operands colder than L2 capacity in total."""
     out = {}
     for name, (M, K, N, bits, group, R, iters) in {
@@ -196,7 +196,7 @@ def prefill_legs(ctx, O, BF16, peaks):
 
 
 def chain_leg(ctx, O, BF16, peaks):
-    """BASELINE.json configs[4] at one GPU: one decode step (M = 8) through 32 layers of quantized projections
+    """The quantized-linear chain configuration at one GPU: one decode step (M = 8) through 32 layers of quantized projections
     (q,k,v,o 4096x4096; gate,up 11008x4096; down 4096x11008; 4-bit g64) with the rms-norms between them.
     q/k/v run as one N = 12288 launch and gate/up as one N = 22016 launch (the configuration allows it: same
     results), so a layer is 4 matmul launches + 3 rms-norm launches, each ordered behind the one before.

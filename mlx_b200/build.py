@@ -2,7 +2,7 @@
 
 The plugin is compiled against the reference's UNCHANGED ABI header
 (include/lux/gpu/backend_plugin.h), taken where it lies in the reference tree
-(``LUX_REFERENCE_INCLUDE`` or /root/reference/include); the header is not
+(``LUX_REFERENCE_INCLUDE``, else the default location below); the header is not
 copied into this repository.  On a machine without the reference tree the
 prebuilt library is used as is.
 """
