@@ -259,6 +259,111 @@ def chain_leg(ctx, O, BF16, peaks):
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"]}}
 
 
+def chain_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks):
+    """The quantized-linear chain with every projection column-sharded over the ranks (strong scaling: the
+    model is fixed, each rank keeps 1/world of every weight matrix) and the decode kernel delivering its
+    columns to all ranks.  Same launches as chain_leg; x of every launch is the whole (gathered) activation.
+    Before timing, rank 0 recomputes each of the four projections of one layer unsharded and compares the
+    gathered outputs bit for bit."""
+    import torch
+    from mlx_b200.plugin import SymmBuffer
+    M, D, FF, L, DISTINCT = 8, 4096, 11008, 32, 4
+    shapes = [("qkv", 3 * D, D), ("o", D, D), ("gateup", 2 * FF, D), ("down", D, FF)]
+    layers, full0 = [], {}
+    for l in range(DISTINCT):
+        ws = {}
+        for pi, (name, N, K) in enumerate(shapes):
+            wq, s, b = O.make_layer(N, K, BITS, GROUP, O.BF16, config_id=5, layer=l, proj=pi)
+            nl = N // world
+            sl = slice(rank * nl, (rank + 1) * nl)
+            ws[name] = (ctx.upload(wq[sl]), ctx.upload(s[sl]), ctx.upload(b[sl]), nl, K)
+            if l == 0 and rank == 0:
+                full0[name] = (wq, s, b)
+        layers.append(ws)
+    symm = {}
+    for name, N, _ in shapes:
+        symm[name] = SymmBuffer(ctx, rank, world, (M, N), np.uint16)
+        mine = torch.tensor(list(symm[name].export()), dtype=torch.uint8, device="cuda")
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        symm[name].attach([bytes(t.cpu().tolist()) for t in every])
+    dist.barrier()
+    h0 = O.make_x(M, D, O.BF16, config_id=5)
+    h = ctx.upload(h0)
+    a = ctx.upload(O.make_x(M, D, O.BF16, config_id=5, tag=1))
+    gu = ctx.upload(O.make_x(M, FF, O.BF16, config_id=5, tag=2))
+    r_buf, m_buf = ctx.empty((M, D), np.uint16), ctx.empty((M, FF), np.uint16)
+
+    def mm(ws, name, src):
+        bw, bs, bb, nl, K = ws[name]
+        symm[name].qmatmul(src, bw, bs, bb, M, K, nl, BITS, GROUP, BF16)
+
+    def layer(ws):
+        mm(ws, "qkv", h)
+        mm(ws, "o", a)
+        ctx.rms_norm(symm["o"].buffer, r_buf, M, D, 1e-6, BF16, BF16)
+        mm(ws, "gateup", r_buf)
+        ctx.rms_norm(gu, m_buf, M, FF, 1e-6, BF16, BF16)
+        mm(ws, "down", m_buf)
+        ctx.rms_norm(symm["down"].buffer, h, M, D, 1e-6, BF16, BF16)
+
+    # check: one layer, gathered outputs against the unsharded matmuls on rank 0
+    layer(layers[0])
+    ctx.sync()
+    dist.barrier()
+    verified = None
+    if rank == 0:
+        inputs = {"qkv": h0, "o": a.to_host(), "gateup": r_buf.to_host(), "down": m_buf.to_host()}
+        for name, N, K in shapes:
+            wq, s, b = full0[name]
+            bw, bs, bb, bx = ctx.upload(wq), ctx.upload(s), ctx.upload(b), ctx.upload(inputs[name])
+            ref = ctx.empty((M, N), np.uint16)
+            ctx.qmatmul(bx, bw, bs, bb, ref, M, K, N, BITS, GROUP, BF16, BF16, BF16)
+            assert np.array_equal(symm[name].to_host(), ref.to_host()), f"sharded {name} differs from the unsharded matmul"
+            for t in (bw, bs, bb, bx, ref):
+                t.free()
+        verified = "gathered qkv / o / gate-up / down outputs of one layer bit-identical to the unsharded matmuls"
+    dist.barrier()
+
+    def step():
+        for l in range(L):
+            layer(layers[l % DISTINCT])
+
+    step()
+    ctx.sync()
+    dist.barrier()
+    ctx.graph_begin()
+    step()
+    g = ctx.graph_end()
+    for _ in range(3):
+        ctx.graph_launch(g)
+    ctx.sync()
+    dist.barrier()
+    iters = 10
+    ctx.timer_record(8)
+    for _ in range(iters):
+        ctx.graph_launch(g)
+    ctx.timer_record(9)
+    ms = ctx.timer_elapsed_ms(8, 9) / iters
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    ctx.sync()
+    dist.barrier()
+    nbytes = L * sum(alg_bytes(M, K, N) for _, N, K in shapes)
+    ctx.graph_destroy(g)
+    for sb in symm.values():
+        sb.free()
+    for ws in layers:
+        for (bw, bs, bb, _, _) in ws.values():
+            bw.free(); bs.free(); bb.free()
+    for b in (h, a, gu, r_buf, m_buf):
+        b.free()
+    return {"workload": f"32 layers x (qkv, o, gate/up, down) + 3 rms-norms, M=8, every projection column-sharded over {world} GPUs",
+            "scaling": "strong", "ms_per_step": ms, "launches_per_step": L * 7, "algorithmic_GB": nbytes / 1e9,
+            "GBps_aggregate": nbytes / ms / 1e6, "verified": verified}
+
+
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
@@ -472,6 +577,8 @@ def run_ours(args, rank, world):
     peaks, which = measured_peaks()
     prefill = prefill_legs(ctx, O, BF16, peaks) if (world == 1 and not args.kernel_only) else None
     chain = chain_leg(ctx, O, BF16, peaks) if (world == 1 and not args.kernel_only) else None
+    chain_sharded = (chain_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks)
+                     if (world > 1 and use_push and args.chain_sharded) else None)
     if dist is not None:
         ctx.sync()
         dist.barrier()
@@ -509,6 +616,7 @@ def run_ours(args, rank, world):
         "per_M": {str(M): per_m[M] for M in M_SWEEP},
         "prefill": prefill,
         "chain": chain,
+        "chain_sharded": chain_sharded,
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "calls": e2e_calls, "us_per_call": ms_e2e * 1e3 / max(1, e2e_calls),
@@ -532,6 +640,8 @@ def main():
                     help="skip the e2e and CPU-baseline legs (for short runs under a profiler)")
     ap.add_argument("--nccl-allgather", action="store_true",
                     help="N>1: gather the column slices with NCCL + an interleave pass instead of peer stores from the kernel")
+    ap.add_argument("--chain-sharded", action="store_true",
+                    help="N>1: also run the column-sharded quantized-linear chain (strong scaling) after the sweep")
     ap.add_argument("--chain-only", action="store_true", help="run only the quantized-linear chain leg")
     ap.add_argument("--prefill-only", action="store_true", help="run only the tensor-bound legs (short, for profiling)")
     ap.add_argument("--traffic-bytes", type=float, default=NCU_TRAFFIC_BYTES,
