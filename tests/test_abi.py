@@ -68,6 +68,17 @@ def test_quant_table():
         assert C.cast(getattr(q, name), C.c_void_p).value, name
 
 
+def test_python_mirror_follows_the_header_field_by_field():
+    """The ctypes mirror is written by hand: its entries must be the header's, in the header's order."""
+    text = open(os.path.join(ROOT, "include", "lux_cuda_quant.h")).read()
+    body = text[text.index("typedef struct lux_gpu_quant_vtbl {"):text.index("} lux_gpu_quant_vtbl;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    in_header = re.findall(r"\(\*(\w+)\)\s*\(", body)
+    in_mirror = [name for name, _ in P.QuantVtbl._fields_[4:]]
+    assert in_header == in_mirror
+    assert int(re.search(r"#define LUX_CUDA_SYMM_HANDLE_BYTES (\d+)", text).group(1)) == P.SYMM_HANDLE_BYTES
+
+
 def test_null_arguments_are_errors_not_crashes():
     p = mlx_b200.Plugin(require_gpu=False)
     v, q = p.vtbl, p.quant
@@ -79,6 +90,12 @@ def test_null_arguments_are_errors_not_crashes():
     assert v.op_matmul_f32(None, None, None, None, 1, 1, 1) == P.ERR_INVALID
     assert q.qmatmul(None, None, None, None, None, None, 1, 64, 1, 4, 64, 0, 0, 0) == P.ERR_INVALID
     assert q.dequantize(None, None, None, None, None, 1, 64, 4, 64, 0, 0) == P.ERR_INVALID
+    assert q.symm_alloc(None, 0, 1, 64, None) == P.ERR_INVALID
+    assert q.symm_export(None, None) == P.ERR_INVALID
+    assert q.symm_attach(None, None) == P.ERR_INVALID
+    assert q.symm_buffer(None) is None
+    assert q.qmatmul_sharded_push(None, None, None, None, None, 1, 64, 16, 4, 64, 2) == P.ERR_INVALID
+    q.symm_free(None)
     v.buffer_free(None, None)
     v.destroy_context(None)
 
