@@ -412,6 +412,9 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
                         const uint4 v = *reinterpret_cast<const uint4*>(wrow + ((c ^ wsw) << 4));
                         w[4 * c] = v.x; w[4 * c + 1] = v.y; w[4 * c + 2] = v.z; w[4 * c + 3] = v.w;
                     }
+                    // The reads above are generic-proxy accesses, the refill is an async-proxy write: the proxy
+                    // fence orders the two (without it a read still in the load pipe could see the next unit).
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     // every thread of the group has its bytes: the slot may be refilled.  The same barrier makes
                     // a failed wait a decision of the whole group, so nobody is left waiting at it.
                     ok = group_all(bar_id, got);

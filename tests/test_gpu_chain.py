@@ -110,3 +110,24 @@ def test_weights_written_just_before_use(ctx, oracle):
     assert np.any(results[0] != 0)
     for h in [bw_f, bzero, bx, y0, y1, wq, s, b] + bwarm:
         h.free()
+
+
+@pytest.mark.parametrize("M,K,N,bits,group", [(1, 4096, 1024, 4, 64), (16, 2048, 528, 4, 32), (8, 8192, 96, 8, 128)])
+def test_decode_is_repeatable(ctx, oracle, M, K, N, bits, group):
+    """Back-to-back decode launches overlap (the next one fetches weights while the previous drains) and hand
+    partial sums between warps and CTAs: repeated launches must give the same bits every time."""
+    wq, s, b = oracle.make_layer(N, K, bits, group, oracle.BF16, config_id=6, layer=K, proj=N)
+    x = oracle.make_x(M, K, oracle.BF16, config_id=6, layer=K, tag=M)
+    bx, bw, bs, bb = ctx.upload(x), ctx.upload(wq), ctx.upload(s), ctx.upload(b)
+    ys = [ctx.empty((M, N), np.uint16) for _ in range(8)]
+    ctx.qmatmul(bx, bw, bs, bb, ys[0], M, K, N, bits, group, BF16, BF16, BF16)
+    first = ys[0].to_host()
+    bad = 0
+    for rep in range(40):
+        for y in ys:
+            ctx.qmatmul(bx, bw, bs, bb, y, M, K, N, bits, group, BF16, BF16, BF16)
+        for y in ys:
+            bad += not np.array_equal(y.to_host(), first)
+    for h in (bx, bw, bs, bb, *ys):
+        h.free()
+    assert bad == 0, f"{bad} of 320 launches differed from the first"

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 from mlx_b200 import BF16, F32
-from test_gpu_parity import run_qmatmul
+from test_gpu_parity import check, run_qmatmul
 
 pytestmark = pytest.mark.gpu
 
@@ -72,3 +72,26 @@ def test_prefill_full_size_sampled(ctx, oracle):
     t = oracle.qmatmul_truth(x[rows], wq, s, b, 4, 64)
     err, _ = oracle.rel_err(y[rows], t)
     assert err <= oracle.TOL[oracle.BF16], err
+
+
+@pytest.mark.parametrize("M,K,N,bits,group", [(256, 2048, 1024, 8, 32), (256, 2048, 1024, 4, 64), (130, 1024, 300, 8, 128)])
+def test_prefill_is_repeatable(ctx, oracle, M, K, N, bits, group):
+    """The kernel hands tiles between warps, the copy engine and the tensor core through barriers only: the same
+    launch repeated many times must give the same bits every time (a missed hand-over shows up here long
+    before it shows up in a tolerance check)."""
+    wq, s, b = oracle.make_layer(N, K, bits, group, oracle.BF16, config_id=3, layer=K, proj=N)
+    x = oracle.make_x(M, K, oracle.BF16, config_id=3, layer=K, tag=M)
+    bx, bw, bs, bb = ctx.upload(x), ctx.upload(wq), ctx.upload(s), ctx.upload(b)
+    ys = [ctx.empty((M, N), np.uint16) for _ in range(4)]
+    ctx.qmatmul(bx, bw, bs, bb, ys[0], M, K, N, bits, group, BF16, BF16, BF16)
+    first = ys[0].to_host()
+    check(oracle, first, x, wq, s, b, bits, group, oracle.BF16)
+    bad = 0
+    for rep in range(60):
+        for y in ys:
+            ctx.qmatmul(bx, bw, bs, bb, y, M, K, N, bits, group, BF16, BF16, BF16)
+        for y in ys:
+            bad += not np.array_equal(y.to_host(), first)
+    for h in (bx, bw, bs, bb, *ys):
+        h.free()
+    assert bad == 0, f"{bad} of 240 launches differed from the first"
