@@ -36,6 +36,7 @@ import numpy as np
 # dram__bytes_read.sum + dram__bytes_write.sum of one qmv_mma launch (M=1) of this workload, from the ncu
 # capture summarised in profiles/qmv_mma_decode_gemv_4bit_K4096_N11008.md
 NCU_TRAFFIC_BYTES = 25438464.0
+SWEEPS_PER_GRAPH = 5  # sweeps (of 4 x 12 launches) recorded in the CUDA graph the timed step replays
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -478,6 +479,14 @@ def run_ours(args, rank, world):
             for r in range(R_SETS):
                 launch(M, r)
             graphs[M] = ctx.graph_end()
+        # the timed step replays whole sweeps: SWEEPS_PER_GRAPH of them per graph (graph boundaries serialise
+        # fully, so longer graphs mean fewer of them per launch)
+        ctx.graph_begin()
+        for _ in range(SWEEPS_PER_GRAPH):
+            for M in M_SWEEP:
+                for r in range(R_SETS):
+                    launch(M, r)
+        graph_sweeps = ctx.graph_end()
 
     def sweep():
         for M in M_SWEEP:
@@ -508,7 +517,11 @@ def run_ours(args, rank, world):
         return ms
 
     def step():
-        for _ in range(args.reps):
+        done = 0
+        while use_graph and done + SWEEPS_PER_GRAPH <= args.reps:
+            ctx.graph_launch(graph_sweeps)
+            done += SWEEPS_PER_GRAPH
+        for _ in range(args.reps - done):
             sweep()
 
     for _ in range(args.warmup):
@@ -602,6 +615,7 @@ def run_ours(args, rank, world):
         "config": {"workload": "decode_gemv_sweep" if world == 1 else "decode_gemv_sweep_column_sharded_allgather",
                    "M": list(M_SWEEP), "K": K_DEC, "N": N_DEC, "N_total": n_total, "bits": BITS, "group": GROUP,
                    "weight_sets": R_SETS, "sweeps_per_step": args.reps, "cuda_graph": use_graph,
+                   "launches_per_graph": SWEEPS_PER_GRAPH * len(M_SWEEP) * R_SETS if use_graph else None,
                    "allgather": None if world == 1 else ("peer stores from the decode kernel (one launch per call)" if use_push
                                                          else "NCCL all-gather + interleave pass"),
                    "verified": verified,
