@@ -35,7 +35,7 @@ import numpy as np
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one qmv_mma launch (M=1) of this workload, from the ncu
 # capture summarised in profiles/qmv_mma_decode_gemv_4bit_K4096_N11008.md
-NCU_TRAFFIC_BYTES = 25438464.0
+NCU_TRAFFIC_BYTES = 25449472.0
 SWEEPS_PER_GRAPH = 5  # sweeps (of 4 x 12 launches) recorded in the CUDA graph the timed step replays
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
