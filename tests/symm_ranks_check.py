@@ -1,0 +1,77 @@
+"""Helper of test_gpu_symm.py (not collected by pytest): run under torchrun with one rank per GPU.
+
+Every rank keeps a column slice of a few layers, runs the decode matmul that delivers its columns to all ranks
+(qmatmul_sharded_push), and rank 0 compares the gathered result with the unsharded matmul, bit for bit.  The
+shapes include few rows of W with a long K, where the decode kernel splits K over CTAs and the tiles are
+finished -- and sent to the peers -- by whichever CTA arrives last.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import mlx_b200  # noqa: E402
+import oracle as O  # noqa: E402
+from mlx_b200 import BF16  # noqa: E402
+from mlx_b200.plugin import SymmBuffer  # noqa: E402
+
+SHAPES = [  # (M, K, N_local, bits, group)
+    (8, 11008, 512, 4, 64),    # split-K
+    (16, 8192, 48, 4, 32),     # split-K, 16 rows of x
+    (1, 4096, 1024, 4, 64),
+    (5, 2048, 2752, 8, 128),
+    (16, 4096, 11008, 4, 64),
+]
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    plugin = mlx_b200.Plugin(require_gpu=True)
+    ctx = plugin.context(local)
+    for case, (M, K, nl, bits, group) in enumerate(SHAPES):
+        N = nl * world
+        wq, s, b = O.make_layer(N, K, bits, group, O.BF16, config_id=8, layer=case)
+        x = O.make_x(M, K, O.BF16, config_id=8, tag=case)
+        sl = slice(rank * nl, (rank + 1) * nl)
+        bx, bw, bs, bb = ctx.upload(x), ctx.upload(wq[sl]), ctx.upload(s[sl]), ctx.upload(b[sl])
+        sb = SymmBuffer(ctx, rank, world, (M, N), np.uint16)
+        mine = torch.tensor(list(sb.export()), dtype=torch.uint8, device="cuda")
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        sb.attach([bytes(t.cpu().tolist()) for t in every])
+        dist.barrier()
+        for rep in range(20):  # the same buffer again and again: the inbox hand-shake is part of the test
+            sb.qmatmul(bx, bw, bs, bb, M, K, nl, bits, group, BF16)
+        ctx.sync()
+        got = sb.to_host()
+        dist.barrier()
+        if rank == 0:
+            fw, fs, fb = ctx.upload(wq), ctx.upload(s), ctx.upload(b)
+            ref = ctx.empty((M, N), np.uint16)
+            ctx.qmatmul(bx, fw, fs, fb, ref, M, K, N, bits, group, BF16, BF16, BF16)
+            want = ref.to_host()
+            if not np.array_equal(got, want):
+                bad = np.argwhere(got != want)
+                print(f"MISMATCH case {case} {(M, K, nl, bits, group)}: {len(bad)} elements, first {bad[:4].tolist()}", flush=True)
+                os._exit(3)
+            for h in (fw, fs, fb, ref):
+                h.free()
+        dist.barrier()
+        sb.free()
+        for h in (bx, bw, bs, bb):
+            h.free()
+    ctx.sync()
+    dist.barrier()
+    if rank == 0:
+        print(f"SYMM_RANKS_OK world={world} cases={len(SHAPES)}", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

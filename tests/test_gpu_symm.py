@@ -57,3 +57,16 @@ def test_two_ranks_bit_exact(plugin):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT)
     assert r.returncode == 0, r.stderr[-2000:]
     assert '"verified": "all ranks' in r.stdout
+
+
+def test_ranks_bit_exact_including_split_k(plugin):
+    """Several shapes (among them few rows of W with a long K, which the decode kernel splits over CTAs) pushed
+    twenty times each into the same buffer by every rank: tests/symm_ranks_check.py compares on rank 0."""
+    n = plugin.device_count()
+    if n < 2:
+        pytest.skip("needs two GPUs")
+    n = 2 if n < 4 else 4
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(n), "--master-addr", "127.0.0.1",
+           "--master-port", "29537", os.path.join(ROOT, "tests", "symm_ranks_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert r.returncode == 0 and "SYMM_RANKS_OK" in r.stdout, (r.stdout[-1500:], r.stderr[-1500:])
