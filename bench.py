@@ -260,6 +260,96 @@ def chain_leg(ctx, O, BF16, peaks):
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"]}}
 
 
+def gemm_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks, use_push):
+    """The 8-bit large-GEMM configuration (M=512, K=8192, N=28672, g128) with N column-sharded over the ranks
+    (strong scaling): every rank runs the tcgen05 GEMM on its 28672/world columns.  use_push: the GEMM's epilogue
+    stores every tile into all ranks' copies of y (peer stores, two device-side rank barriers around the launch);
+    else the slices are all-gathered with NCCL and interleaved.  Launched eagerly.  Rank 0 checks sampled
+    outputs of the gathered y against the oracle."""
+    import torch
+    M, K, N, bits, group = 512, 8192, 28672, 8, 128
+    nl = N // world
+    q = plugin.quant
+    comm, symm_y = None, None
+    if use_push:
+        from mlx_b200.plugin import SymmBuffer
+        symm_y = SymmBuffer(ctx, rank, world, (M, N), np.uint16)
+        mine = torch.tensor(list(symm_y.export()), dtype=torch.uint8, device="cuda")
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        symm_y.attach([bytes(t.cpu().tolist()) for t in every])
+        dist.barrier()
+    else:
+        uid = (C.c_ubyte * 128)()
+        if rank == 0:
+            plugin.check(q.shard_unique_id(uid), "shard_unique_id")
+        t = torch.tensor(list(uid), dtype=torch.uint8, device="cuda")
+        dist.broadcast(t, 0)
+        uid = (C.c_ubyte * 128)(*t.cpu().tolist())
+        comm = C.c_void_p(None)
+        plugin.check(q.shard_comm_create(ctx.handle, rank, world, uid, C.byref(comm)), "shard_comm_create")
+    wq, s, b = O.make_layer(N, K, bits, group, O.BF16, config_id=4, layer=0)
+    x = O.make_x(M, K, O.BF16, config_id=4, layer=0)
+    sl = slice(rank * nl, (rank + 1) * nl)
+    R = 2  # two copies of the slice, alternated: 2 x 235/world MB of weights
+    sets = [(ctx.upload(wq[sl]), ctx.upload(s[sl]), ctx.upload(b[sl])) for _ in range(R)]
+    bx = ctx.upload(x)
+    y = symm_y.buffer if use_push else ctx.empty((M, N), np.uint16)
+    staging = None if use_push else ctx.empty((world, M, nl), np.uint16)
+
+    def go():
+        for (bw, bs, bb) in sets:
+            if use_push:
+                symm_y.qmatmul(bx, bw, bs, bb, M, K, nl, bits, group, BF16)
+            else:
+                plugin.check(q.qmatmul_sharded(comm, bx.handle, bw.handle, bs.handle, bb.handle, y.handle, staging.handle,
+                                               M, K, nl, bits, group, BF16, BF16, BF16), "qmatmul_sharded")
+    go()
+    ctx.sync()
+    dist.barrier()
+    verified = None
+    if rank == 0:
+        got = y.to_host()
+        rows = [0, 257, 511]
+        cols = np.arange(0, N, 97)
+        truth = O.qmatmul_truth(x[rows], wq[cols], s[cols], b[cols], bits, group)
+        err, _ = O.rel_err(got[np.ix_(rows, cols)], truth)
+        assert err <= O.TOL[O.BF16], f"sharded GEMM: sampled outputs off by {err}"
+        verified = f"sampled outputs of the gathered y within {O.TOL[O.BF16]} of the oracle (max rel err {err:.2e})"
+    dist.barrier()
+    for _ in range(2):
+        go()
+    ctx.sync()
+    dist.barrier()
+    iters = 5
+    ctx.timer_record(10)
+    for _ in range(iters):
+        go()
+    ctx.timer_record(11)
+    ms = ctx.timer_elapsed_ms(10, 11) / (iters * R)
+    tt = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    ms = float(tt.item())
+    ctx.sync()
+    dist.barrier()
+    if comm:
+        q.shard_comm_destroy(comm)
+    for tpl in sets:
+        for h in tpl:
+            h.free()
+    bx.free()
+    if use_push:
+        symm_y.free()
+    else:
+        y.free()
+        staging.free()
+    tf = 2.0 * M * N * K / ms / 1e9
+    how = "tiles stored into every rank's y from the GEMM epilogue" if use_push else "NCCL all-gather + interleave"
+    return {"workload": f"M=512 K=8192 N=28672 8-bit g128, N column-sharded over {world} GPUs, {how}",
+            "scaling": "strong", "us_per_call": ms * 1e3, "TFLOPS_aggregate": tf,
+            "allgather_bytes_per_rank": M * N * 2, "verified": verified}
+
+
 def chain_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks):
     """The quantized-linear chain with every projection column-sharded over the ranks (strong scaling: the
     model is fixed, each rank keeps 1/world of every weight matrix) and the decode kernel delivering its
@@ -590,6 +680,8 @@ def run_ours(args, rank, world):
     peaks, which = measured_peaks()
     prefill = prefill_legs(ctx, O, BF16, peaks) if (world == 1 and not args.kernel_only) else None
     chain = chain_leg(ctx, O, BF16, peaks) if (world == 1 and not args.kernel_only) else None
+    gemm_sharded = (gemm_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks, use_push)
+                    if (world > 1 and args.gemm_sharded) else None)
     chain_sharded = (chain_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks)
                      if (world > 1 and use_push and args.chain_sharded) else None)
     if dist is not None:
@@ -631,6 +723,7 @@ def run_ours(args, rank, world):
         "prefill": prefill,
         "chain": chain,
         "chain_sharded": chain_sharded,
+        "gemm_sharded": gemm_sharded,
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "calls": e2e_calls, "us_per_call": ms_e2e * 1e3 / max(1, e2e_calls),
@@ -654,6 +747,8 @@ def main():
                     help="skip the e2e and CPU-baseline legs (for short runs under a profiler)")
     ap.add_argument("--nccl-allgather", action="store_true",
                     help="N>1: gather the column slices with NCCL + an interleave pass instead of peer stores from the kernel")
+    ap.add_argument("--gemm-sharded", action="store_true",
+                    help="N>1: also run the column-sharded 8-bit large GEMM (strong scaling, NCCL all-gather) after the sweep")
     ap.add_argument("--chain-sharded", action="store_true",
                     help="N>1: also run the column-sharded quantized-linear chain (strong scaling) after the sweep")
     ap.add_argument("--chain-only", action="store_true", help="run only the quantized-linear chain leg")

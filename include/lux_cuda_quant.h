@@ -186,12 +186,14 @@ typedef struct lux_gpu_quant_vtbl {
     LuxBackendError (*symm_attach)(LuxCudaSymmBuffer* buf, const void* handles /* world x LUX_CUDA_SYMM_HANDLE_BYTES */);
     LuxBackendBuffer* (*symm_buffer)(LuxCudaSymmBuffer* buf);
     void (*symm_free)(LuxCudaSymmBuffer* buf);
-    /* y_full[:, rank*Nl : (rank+1)*Nl] = x . dequant(wq_local)^T, written by ONE decode launch into every
-     * rank's copy of y_full; the launch ends when the peers' columns of the same call have arrived, so
-     * whatever is enqueued after it sees the whole y_full.  All ranks must make the same calls on the
-     * same buffer in the same order (a rank waits up to 2 s for its peers, then the next sync returns
-     * INTERNAL).  bf16 x / scales / biases, 1 <= M <= 16, Nl a multiple of 16, world <= 8; anything else is
-     * NOT_SUPPORTED (use qmatmul_sharded).  May be recorded with graph_begin/graph_end. */
+    /* y_full[:, rank*Nl : (rank+1)*Nl] = x . dequant(wq_local)^T, delivered into every rank's copy of y_full by
+     * the matmul kernel itself; when the call's work on the stream ends the peers' columns of the same call
+     * have arrived, so whatever is enqueued after it sees the whole y_full.  M <= 16: ONE decode launch (may be
+     * recorded with graph_begin/graph_end).  M > 16: the prefill GEMM stores its tiles into all copies from
+     * its epilogue, between two device-side barriers over the ranks.  All ranks must make the same calls on
+     * the same buffer in the same order (a rank waits up to 2 s for its peers, then the next sync returns
+     * INTERNAL).  bf16 x / scales / biases, Nl a multiple of 16, world <= 8, K as the kernels need it;
+     * anything else is NOT_SUPPORTED (use qmatmul_sharded). */
     LuxBackendError (*qmatmul_sharded_push)(LuxCudaSymmBuffer* y_full, LuxBackendBuffer* x, LuxBackendBuffer* wq_local,
                                             LuxBackendBuffer* scales_local, LuxBackendBuffer* biases_local,
                                             int M, int K, int N_local, int bits, int group, LuxBackendDtype y_dtype);

@@ -187,7 +187,8 @@ void note_decode_launch(Context* c, const QmmArgs& a);  // call right after a de
 cudaError_t launch_qmv_simt(const QmmArgs& a, cudaStream_t stream, const char** name);
 // prefill GEMM, bf16 activations: TMA + tcgen05 + TMEM
 bool qmm_tc_supported(const QmmArgs& a);
-cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, const char** name);
+cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, const char** name,
+                          const ShardPush* push = nullptr);
 // non-zero once a kernel gave up on one of its bounded waits since the last call (clears it)
 int take_device_error();
 int* device_error_word();  // where kernels raise it (null if the mapped word could not be set up)

@@ -182,6 +182,8 @@ struct GemmParams {
     void* y;
     int* error;              // host-visible error word (0 = ok)
     int M, K, N, gshift, y_bf16;
+    int world, ld, col0;     // copies of y to write (1 unless column-sharded), their row stride and this rank's first column
+    void* y_all[kMaxShardWorld];
     int bm;                  // rows of x per tile (multiple of 16, <= 256)
     int n_tiles, m_tiles;
 };
@@ -468,22 +470,25 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
                 __syncwarp();
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
                 if (n < p.N) {
-                    const size_t idx0 = (size_t)(m0 + c0) * p.N + n;
-                    if (p.y_bf16) {
-                        __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(p.y) + idx0;
-                        if (c0 + 32 <= m_end) {
+                    // column-sharded layers: the tile goes into every rank's copy of y (peer stores over NVLink)
+                    const size_t idx0 = (size_t)(m0 + c0) * p.ld + p.col0 + n;
+                    for (int dst = 0; dst < p.world; dst++) {
+                        if (p.y_bf16) {
+                            __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(p.y_all[dst]) + idx0;
+                            if (c0 + 32 <= m_end) {
 #pragma unroll
-                            for (int j = 0; j < 32; j++) yp[(size_t)j * p.N] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                                for (int j = 0; j < 32; j++) yp[(size_t)j * p.ld] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    if (c0 + j < m_end) yp[(size_t)j * p.ld] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                            }
                         } else {
+                            float* yp = reinterpret_cast<float*>(p.y_all[dst]) + idx0;
 #pragma unroll
                             for (int j = 0; j < 32; j++)
-                                if (c0 + j < m_end) yp[(size_t)j * p.N] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                                if (c0 + j < m_end) yp[(size_t)j * p.ld] = __uint_as_float(v[j]);
                         }
-                    } else {
-                        float* yp = reinterpret_cast<float*>(p.y) + idx0;
-#pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (c0 + j < m_end) yp[(size_t)j * p.N] = __uint_as_float(v[j]);
                     }
                 }
             }
@@ -580,7 +585,7 @@ bool qmm_tc_supported(const QmmArgs& a) {
     return make_gemm_plan(a, 148, &pl);
 }
 
-cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, const char** name) {
+cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, const char** name, const ShardPush* push) {
     GemmPlan pl;
     if (!make_gemm_plan(a, sm_count, &pl)) return cudaErrorInvalidValue;
     int* err = error_word();
@@ -624,6 +629,18 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, c
     p.M = a.M; p.K = a.K; p.N = a.N;
     p.gshift = a.group == 32 ? 5 : (a.group == 64 ? 6 : 7);
     p.y_bf16 = a.y_dtype == LUX_DTYPE_BFLOAT16;
+    p.world = 1; p.ld = a.N; p.col0 = 0;
+    for (int r = 0; r < kMaxShardWorld; r++) p.y_all[r] = nullptr;
+    p.y_all[0] = a.y;
+    if (push && push->world > 1) {
+        if (push->world > kMaxShardWorld) return cudaErrorInvalidValue;
+        p.world = push->world; p.ld = push->ld; p.col0 = push->col0;
+        // own copy first, then the peers
+        int k = 0;
+        p.y_all[k++] = push->y[push->me];
+        for (int r = 0; r < push->world; r++)
+            if (r != push->me) p.y_all[k++] = push->y[r];
+    }
     p.bm = pl.bm; p.n_tiles = pl.n_tiles; p.m_tiles = pl.m_tiles;
     if (a.bits == 4) {
         if (name) *name = "qmm_tc<4>";

@@ -41,6 +41,49 @@ struct Handle {  // what travels between ranks; LUX_CUDA_SYMM_HANDLE_BYTES
 };
 static_assert(sizeof(Handle) == LUX_CUDA_SYMM_HANDLE_BYTES, "handle size");
 
+// Barrier over the ranks of a symmetric buffer, on the device: every rank bumps its count of barriers, writes
+// it into its slot on every peer and waits until every peer's slot here has reached it.  One warp; the waits
+// are bounded (on a time-out the host-visible error word is raised and the kernel returns).
+// Flag words used: [kBarEpoch] this rank's count, [kBarSlot + q] the count announced by rank q.
+constexpr int kBarEpoch = 2, kBarSlot = 32;
+constexpr long long kBarWaitNs = 2000000000ll;
+struct BarrierArgs {
+    uint32_t* flags[kMaxShardWorld];
+    int world, me;
+    int* error;
+};
+__global__ void symm_barrier_kernel(const __grid_constant__ BarrierArgs a) {
+    const int q = threadIdx.x;
+    uint32_t* mine = a.flags[a.me];
+    const uint32_t e = *reinterpret_cast<volatile uint32_t*>(mine + kBarEpoch) + 1;
+    __syncwarp();
+    bool ok = true;
+    if (q < a.world && q != a.me) {
+        __threadfence_system();  // whatever this rank stored into the peers before is out before the count
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(a.flags[q] + kBarSlot + a.me), "r"(e) : "memory");
+        long long t0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+        for (;;) {
+            uint32_t v;
+            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine + kBarSlot + q) : "memory");
+            if ((int32_t)(v - e) >= 0) break;
+            long long t1;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+            if (t1 - t0 > kBarWaitNs) {
+                ok = false;
+                break;
+            }
+            __nanosleep(200);
+        }
+        __threadfence_system();
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (q == 0) {
+        *reinterpret_cast<volatile uint32_t*>(mine + kBarEpoch) = e;
+        if (!ok && a.error) *a.error = 3;
+    }
+}
+
 LuxBackendError symm_alloc(LuxBackendContext* ctx, int rank, int world, size_t bytes, LuxCudaSymmBuffer** out) {
     Context* c = as_ctx(ctx);
     if (!c || !out || world < 1 || world > kMaxShardWorld || rank < 0 || rank >= world || bytes == 0)
@@ -143,9 +186,9 @@ LuxBackendError qmatmul_sharded_push(LuxCudaSymmBuffer* sb, LuxBackendBuffer* x,
         set_last_error("qmatmul_sharded_push: symm_attach has not been called");
         return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     }
-    if (M < 1 || M > 16 || Nl < 1 || (Nl & 15) || K < 1 || (bits != 4 && bits != 8) ||
+    if (M < 1 || Nl < 1 || (Nl & 15) || K < 1 || (bits != 4 && bits != 8) ||
         (group != 32 && group != 64 && group != 128) || K % group) {
-        set_last_error("qmatmul_sharded_push: needs 1 <= M <= 16, N_local a multiple of 16, bits 4|8, group 32|64|128");
+        set_last_error("qmatmul_sharded_push: needs M >= 1, N_local a multiple of 16, bits 4|8, group 32|64|128");
         return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     }
     const size_t ys = y_dtype == LUX_DTYPE_BFLOAT16 ? 2 : 4;
@@ -159,6 +202,44 @@ LuxBackendError qmatmul_sharded_push(LuxCudaSymmBuffer* sb, LuxBackendBuffer* x,
               LUX_DTYPE_BFLOAT16, LUX_DTYPE_BFLOAT16, (int)y_dtype};
     std::lock_guard<std::mutex> lk(c->mu);
     DeviceGuard g(c->dev->device());
+    if (M > 16) {
+        // Prefill: the tcgen05 GEMM stores every tile into all ranks' copies of y from its epilogue, so the
+        // transfer runs under the remaining tiles.  A device-side barrier over the ranks before it (every rank
+        // is done reading its y of the previous call) and one after it (every rank's tiles have landed).
+        if (!qmm_tc_supported(a)) {
+            set_last_error("qmatmul_sharded_push: shape not taken by the prefill kernel (K must be a multiple of 64)");
+            return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+        }
+        ShardPush sp;
+        sp.world = sb->world;
+        sp.me = sb->rank;
+        sp.ld = (int)ld;
+        sp.col0 = sb->rank * Nl;
+        BarrierArgs ba;
+        ba.world = sb->world;
+        ba.me = sb->rank;
+        ba.error = device_error_word();
+        for (int r = 0; r < kMaxShardWorld; r++) ba.flags[r] = nullptr;
+        for (int r = 0; r < sb->world; r++) {
+            sp.y[r] = static_cast<char*>(sb->peer_base[r]) + kHeader;
+            ba.flags[r] = static_cast<uint32_t*>(sb->peer_base[r]);
+        }
+        const char* name = "";
+        if (sb->world > 1) {
+            symm_barrier_kernel<<<1, 32, 0, c->stream>>>(ba);
+            LUX_CUDA_TRY(cudaGetLastError());
+        }
+        cudaError_t e = launch_qmm_tc(a, c->dev->sm_count, c->stream, &name, &sp);
+        if (e != cudaSuccess) return map_cuda_error(e, name);
+        if (sb->world > 1) {
+            symm_barrier_kernel<<<1, 32, 0, c->stream>>>(ba);
+            LUX_CUDA_TRY(cudaGetLastError());
+        }
+        c->last_kernel = name;
+        c->launches += sb->world > 1 ? 3 : 1;
+        bx->last_stream = bw->last_stream = bs->last_stream = bb->last_stream = sb->view.last_stream = c->stream;
+        return LUX_BACKEND_OK;
+    }
     if (!qmv_mma_supported(a)) {
         set_last_error("qmatmul_sharded_push: shape not taken by the decode kernel (K must be a multiple of %d)", 1024 / bits);
         return LUX_BACKEND_ERROR_NOT_SUPPORTED;

@@ -24,6 +24,8 @@ SHAPES = [  # (M, K, N_local, bits, group)
     (1, 4096, 1024, 4, 64),
     (5, 2048, 2752, 8, 128),
     (16, 4096, 11008, 4, 64),
+    (300, 2048, 384, 8, 32),   # prefill GEMM: tiles stored into every rank's copy from the epilogue
+    (64, 1024, 144, 4, 64),
 ]
 
 
