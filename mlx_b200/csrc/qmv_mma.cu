@@ -88,6 +88,7 @@ struct Params {
     int chunks, ks;          // grid = chunks (tile ranges) x ks (k-block ranges)
     int chained;             // launched as a programmatic dependent of the previous kernel
     int xs_off;              // byte offset in shared memory of the x fragments kept there (16-row variant)
+    int yt_off;              // byte offset in shared memory of the tiles staged for the peers (0: not sharded)
     int tb;                  // tiles per reduction batch
     int sb_bytes;            // bytes of scales per row per k-block: 2, 4, 8 or 16
     int ld, col0;            // y row stride and first column (elements): N and 0 unless the layer is column-sharded
@@ -148,15 +149,15 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t e) {
     }
 }
 // Send the finished tile (16 columns of every row of y) to the peers' inboxes.
-__device__ __forceinline__ void push_tile(const Params& p, uint32_t epoch, int rt, int tid_in_group, int group_threads) {
+__device__ __forceinline__ void push_tile(const Params& p, uint32_t epoch, int rt, const unsigned char* ytile,
+                                          int tid_in_group, int group_threads) {
     const int esz = p.y_bf16 ? 2 : 4, wpt = 4 * esz;  // words (4 bytes of y each) per tile row: 8 | 16
     const int wpr = p.N * esz / 4;                    // words per row of this rank's columns
     const int per_peer = p.M * wpt;
-    const char* ylocal = static_cast<const char*>(p.sp.y[p.sp.me]);
-    // the tile's words of this rank's own y, read once, stored to every peer
+    // the tile's words (staged in shared memory by store_tile), read once, stored to every peer
     for (int i = tid_in_group; i < per_peer; i += group_threads) {
         const int k = i & (wpt - 1), m = i / wpt;
-        const uint32_t v = __ldcg(reinterpret_cast<const uint32_t*>(ylocal + ((size_t)m * p.ld + p.col0 + rt * 16) * esz) + k);
+        const uint32_t v = reinterpret_cast<const uint32_t*>(ytile + m * (16 * esz))[k];
         const unsigned long long word = ((unsigned long long)epoch << 32) | v;
         const size_t off = ((size_t)p.sp.me * p.M + m) * wpr + rt * wpt + k;
         for (int q = 0; q < p.sp.world; q++)
@@ -228,14 +229,24 @@ __device__ __forceinline__ bool unpack_inbox(const Params& p, uint32_t epoch) {
 }
 
 template <int MT>
-__device__ __forceinline__ void store_tile(const Params& p, int rt, int e, float sum) {
+// ytile (column-sharded launches only): the tile's values once more in shared memory, [row of x][16 columns]
+// (32 bytes per row of x for bf16, 64 for fp32; 16 rows per tile), from where they are sent to the peers
+// without a trip through L2.
+__device__ __forceinline__ void store_tile(const Params& p, int rt, int e, float sum, unsigned char* ytile) {
     const int mt = e >> 7, rem = e & 127, ln = rem >> 2, ci = rem & 3;
-    const int row = rt * 16 + (ln >> 2) + 8 * (ci >> 1);
+    const int r16 = (ln >> 2) + 8 * (ci >> 1);
+    const int row = rt * 16 + r16;
     const int m = mt * 8 + 2 * (ln & 3) + (ci & 1);
     if (row < p.N && m < p.M) {
         const size_t idx = (size_t)m * p.ld + p.col0 + row;
-        if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y)[idx] = __float2bfloat16_rn(sum);
-        else reinterpret_cast<float*>(p.y)[idx] = sum;
+        if (p.y_bf16) {
+            const __nv_bfloat16 v = __float2bfloat16_rn(sum);
+            reinterpret_cast<__nv_bfloat16*>(p.y)[idx] = v;
+            if (ytile) reinterpret_cast<__nv_bfloat16*>(ytile + m * 32)[r16] = v;
+        } else {
+            reinterpret_cast<float*>(p.y)[idx] = sum;
+            if (ytile) reinterpret_cast<float*>(ytile + m * 64)[r16] = sum;
+        }
     }
 }
 
@@ -261,13 +272,14 @@ __device__ __forceinline__ float ordered_sum(const float* src, int n, int stride
 // is finished by whichever CTA arrives last.
 template <int MT>
 __device__ __noinline__ void batch_end(const Params& p, const float* part, int first_tile, int ntiles, int kb_lo, int nkl,
-                                       int* flags, bool more, bool peers_ready, uint32_t epoch) {
+                                       int* flags, bool more, bool peers_ready, uint32_t epoch, unsigned char* ytiles) {
     constexpr int E = 128 * MT;  // fp32 elements per partial
     const int tid = threadIdx.x;
     __syncthreads();
     if (p.ks == 1) {
         for (int ti = tid / E; ti < ntiles; ti += kThreads / E)
-            store_tile<MT>(p, first_tile + ti, tid % E, ordered_sum<false>(part + ti * nkl * E + tid % E, nkl, E, 0.0f));
+            store_tile<MT>(p, first_tile + ti, tid % E, ordered_sum<false>(part + ti * nkl * E + tid % E, nkl, E, 0.0f),
+                           ytiles ? ytiles + ti * (p.y_bf16 ? 512 : 1024) : nullptr);
     } else {
         for (int ti = 0; ti < ntiles; ti++) {
             float* dst = p.scratch + ((size_t)(first_tile + ti) * p.nkb + kb_lo) * E;
@@ -289,7 +301,8 @@ __device__ __noinline__ void batch_end(const Params& p, const float* part, int f
         for (int ti = tid / E; ti < ntiles; ti += kThreads / E)
             if (flags[ti])
                 store_tile<MT>(p, first_tile + ti, tid % E,
-                               ordered_sum<true>(p.scratch + (size_t)(first_tile + ti) * p.nkb * E + tid % E, p.nkb, E, 0.0f));
+                               ordered_sum<true>(p.scratch + (size_t)(first_tile + ti) * p.nkb * E + tid % E, p.nkb, E, 0.0f),
+                               ytiles ? ytiles + ti * (p.y_bf16 ? 512 : 1024) : nullptr);
     }
     if (p.sp.world > 1) {
         // the tiles this CTA has just finished go to the peers (unless the hand-shake failed)
@@ -297,7 +310,7 @@ __device__ __noinline__ void batch_end(const Params& p, const float* part, int f
         if (peers_ready) {
             constexpr int kGroup = 128;
             for (int ti = tid / kGroup; ti < ntiles; ti += kThreads / kGroup)
-                if (p.ks == 1 || flags[ti]) push_tile(p, epoch, first_tile + ti, tid % kGroup, kGroup);
+                if (p.ks == 1 || flags[ti]) push_tile(p, epoch, first_tile + ti, ytiles + ti * (p.y_bf16 ? 512 : 1024), tid % kGroup, kGroup);
         }
     }
     if (more) __syncthreads();  // the partial buffer and the flags are reused by the next batch
@@ -496,6 +509,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
     // column-sharded: this call's number, and the word to the peers that our copy of y may be overwritten
     uint32_t epoch = 0;
     bool peers_ready = true, ready_checked = p.sp.world <= 1;
+    uint32_t ready_early = 0;  // a peer's ready word as read in mid-kernel (its latency hidden behind the tasks)
     if (p.sp.world > 1) {
         epoch = *reinterpret_cast<volatile uint32_t*>(p.sp.flags[p.sp.me] + kFlagEpoch) + 1;
         // (a relaxed store: it publishes no data of this kernel, only that the kernel has started)
@@ -538,6 +552,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
                     for (int h = 0; h < 2; h++)
                         sboff[r][h] = 2048 - lane * 16 + slot * 16 + ((((h * (KB / 2) + t * (KB / 8)) >> p.gshift) + par) << 1);
                 }
+                if (p.sp.world > 1 && tid < p.sp.world && tid != p.sp.me)
+                    ready_early = ld_relaxed_sys(p.sp.flags[p.sp.me] + kFlagReady + tid);  // used at the first push
                 float4* dstp = part + (kb - kb_lo) * E4 + lane;
 #pragma unroll 1
                 for (int rt = b0; rt <= rt_last; rt++) {
@@ -581,10 +597,12 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
         if (!ready_checked) {  // before the first remote store: has every peer started this call?
             ready_checked = true;
             int ok = 1;
-            if (tid < p.sp.world && tid != p.sp.me) ok = wait_flag(p.sp.flags[p.sp.me] + kFlagReady + tid, epoch);
+            if (tid < p.sp.world && tid != p.sp.me)
+                ok = (int32_t)(ready_early - epoch) >= 0 || wait_flag(p.sp.flags[p.sp.me] + kFlagReady + tid, epoch);
             peers_ready = __syncthreads_and(ok);
         }
-        batch_end<MT>(p, reinterpret_cast<const float*>(part), b0, nt, kb_lo, nkl, s_flags, b0 + tb < rt_hi, peers_ready, epoch);
+        batch_end<MT>(p, reinterpret_cast<const float*>(part), b0, nt, kb_lo, nkl, s_flags, b0 + tb < rt_hi, peers_ready, epoch,
+                      p.yt_off ? smem + p.yt_off : nullptr);
     }
     cp_async_wait<0>();
     if (p.sp.world > 1) {
@@ -604,11 +622,11 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
 }
 
 struct Plan {
-    int nkb, n_rt, mt, chunks, ks, tb, gshift, sb_bytes, xs_off;
+    int nkb, n_rt, mt, chunks, ks, tb, gshift, sb_bytes, xs_off, yt_off;
     size_t smem, ctr_bytes, scratch_bytes;
 };
 
-bool make_plan(const QmmArgs& a, int sm_count, Plan* pl) {
+bool make_plan(const QmmArgs& a, int sm_count, Plan* pl, bool sharded = false) {
     if (a.x_dtype != LUX_DTYPE_BFLOAT16 || a.sb_dtype != LUX_DTYPE_BFLOAT16) return false;
     if (a.bits != 4 && a.bits != 8) return false;
     if (a.M < 1 || a.M > 16 || a.N < 1 || sm_count < 1) return false;
@@ -637,10 +655,13 @@ bool make_plan(const QmmArgs& a, int sm_count, Plan* pl) {
     const size_t per_tile = (size_t)nkl_max * pl->mt * 512;
     const size_t xs_bytes = pl->mt == 2 ? (size_t)kWarps * (a.bits == 4 ? 8 : 4) * 512 : 0;  // x fragments of rows 8..15
     const size_t avail = (size_t)kSmemLimit - kRingBytes - xs_bytes;
-    if (per_tile > avail) return false;
-    pl->tb = (int)std::min<size_t>(std::min<size_t>(tiles_max, avail / per_tile), kMaxTb);
+    // column-sharded launches stage every finished tile once more (16 rows of x x 16 columns) for the peers
+    const size_t yt_tile = sharded ? (a.y_dtype == LUX_DTYPE_BFLOAT16 ? 512 : 1024) : 0;
+    if (per_tile + yt_tile > avail) return false;
+    pl->tb = (int)std::min<size_t>(std::min<size_t>(tiles_max, avail / (per_tile + yt_tile)), kMaxTb);
     pl->xs_off = (int)(kRingBytes + pl->tb * per_tile);
-    pl->smem = kRingBytes + pl->tb * per_tile + xs_bytes;
+    pl->yt_off = sharded ? (int)(pl->xs_off + xs_bytes) : 0;
+    pl->smem = kRingBytes + pl->tb * per_tile + xs_bytes + (sharded ? pl->tb * yt_tile : 0);
     pl->ctr_bytes = ((size_t)pl->n_rt * sizeof(unsigned int) + 255) & ~size_t(255);
     pl->scratch_bytes = ks > 1 ? (size_t)pl->n_rt * pl->nkb * pl->mt * 128 * sizeof(float) : 0;
     if (((uintptr_t)a.wq & 15) || ((uintptr_t)a.x & 15) || ((uintptr_t)a.scales & 15) || ((uintptr_t)a.biases & 15)) return false;
@@ -694,7 +715,7 @@ size_t qmv_mma_workspace_bytes(const QmmArgs& a, int sm_count) {
 cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name,
                            bool overlap_prev, const ShardPush* push) {
     Plan pl;
-    if (!make_plan(a, sm_count, &pl)) return cudaErrorInvalidValue;
+    if (!make_plan(a, sm_count, &pl, push && push->world > 1)) return cudaErrorInvalidValue;
     Params p;
     p.x = (const __nv_bfloat16*)a.x;
     p.wq = a.wq;
@@ -710,6 +731,7 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
     p.chunks = pl.chunks; p.ks = pl.ks; p.tb = pl.tb; p.sb_bytes = pl.sb_bytes;
     p.chained = overlap_prev ? 1 : 0;
     p.xs_off = pl.xs_off;
+    p.yt_off = pl.yt_off;
     p.ld = a.N; p.col0 = 0;
     p.error = nullptr;
     if (push && push->world > 1) {
