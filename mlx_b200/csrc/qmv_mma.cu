@@ -612,7 +612,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
         if (!__syncthreads_and(ok) && tid == 0 && p.error) *p.error = 2;
         if (tid == 0) {
             uint32_t* lf = p.sp.flags[p.sp.me];
-            __threadfence();
+            // (a plain count: the next launch reads the call number only after this one has completed)
             if (atomicAdd(lf + kFlagCtaDone, 1u) == gridDim.x - 1) {
                 lf[kFlagCtaDone] = 0;
                 *reinterpret_cast<volatile uint32_t*>(lf + kFlagEpoch) = epoch;
