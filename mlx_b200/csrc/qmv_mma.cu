@@ -98,7 +98,7 @@ struct Params {
 // ---- column-sharded layers: all-gather by peer stores -----------------------------------
 // Every rank holds the full y[M, ld]; this rank computes columns [col0, col0 + N), stores them into its own
 // copy and sends them over NVLink to every peer.  What travels is 8-byte words, 4 bytes of y plus the
-// number of the call ("epoch"), written with single 64-bit stores into the receiver's inbox
+// number of the call ("epoch"), written two at a time (each half is a whole word) into the receiver's inbox
 // (inbox[sender][row][word], behind y in the same buffer): a word is either absent or complete, so the
 // receiver needs no fence and no acknowledgement -- it polls the words, which costs one NVLink traversal
 // instead of three (data, ack, flag).  Each CTA, once its own tiles are sent, unpacks its share of the
@@ -118,17 +118,15 @@ __device__ __forceinline__ long long now_ns() {
 __device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ void st_relaxed_sys64(unsigned long long* p, unsigned long long v) {
-    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys64x2(unsigned long long* p, unsigned long long a, unsigned long long b) {
+    asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ void ld_relaxed_sys64x2(const unsigned long long* p, unsigned long long& a, unsigned long long& b) {
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
 __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ unsigned long long ld_relaxed_sys64(const unsigned long long* p) {
-    unsigned long long v;
-    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
 // Set by the first wait that runs out and never cleared: from then on no launch of this process waits
@@ -151,54 +149,56 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t e) {
 // Send the finished tile (16 columns of every row of y) to the peers' inboxes.
 __device__ __forceinline__ void push_tile(const Params& p, uint32_t epoch, int rt, const unsigned char* ytile,
                                           int tid_in_group, int group_threads) {
-    const int esz = p.y_bf16 ? 2 : 4, wpt = 4 * esz;  // words (4 bytes of y each) per tile row: 8 | 16
+    const int esz = p.y_bf16 ? 2 : 4, ppt = 2 * esz;  // pairs of words (8 bytes of y) per tile row: 4 | 8
     const int wpr = p.N * esz / 4;                    // words per row of this rank's columns
-    const int per_peer = p.M * wpt;
-    // the tile's words (staged in shared memory by store_tile), read once, stored to every peer
+    const int per_peer = p.M * ppt;
+    const unsigned long long stamp = (unsigned long long)epoch << 32;
+    // the tile's words (staged in shared memory by store_tile), read once, stored to every peer two at a time:
+    // each 8-byte half carries its own stamp, so the 16-byte store need not land as one
     for (int i = tid_in_group; i < per_peer; i += group_threads) {
-        const int k = i & (wpt - 1), m = i / wpt;
-        const uint32_t v = reinterpret_cast<const uint32_t*>(ytile + m * (16 * esz))[k];
-        const unsigned long long word = ((unsigned long long)epoch << 32) | v;
-        const size_t off = ((size_t)p.sp.me * p.M + m) * wpr + rt * wpt + k;
+        const int k2 = i & (ppt - 1), m = i / ppt;
+        const uint2 v = reinterpret_cast<const uint2*>(ytile + m * (16 * esz))[k2];
+        const size_t off = ((size_t)p.sp.me * p.M + m) * wpr + rt * (2 * ppt) + 2 * k2;
         for (int q = 0; q < p.sp.world; q++)
             if (q != p.sp.me)
-                st_relaxed_sys64(reinterpret_cast<unsigned long long*>(static_cast<char*>(p.sp.y[q]) + p.sp.inbox_off) + off, word);
+                st_relaxed_sys64x2(reinterpret_cast<unsigned long long*>(static_cast<char*>(p.sp.y[q]) + p.sp.inbox_off) + off,
+                                   stamp | v.x, stamp | v.y);
     }
 }
 // This CTA's share of the inbox -> local y.  Returns false if a word did not arrive in time.
-// Four words per thread are requested at once (a poll is an L2 round trip: one after the other they
-// would add up to microseconds), then whatever has not arrived yet is polled again.
+// A thread takes pairs of words, four pairs requested at once (a poll is an L2 round trip: one after the
+// other they would add up to microseconds); whatever has not arrived yet is polled again.
 __device__ __forceinline__ bool unpack_inbox(const Params& p, uint32_t epoch) {
     constexpr int U = 4;
     const int esz = p.y_bf16 ? 2 : 4;
-    const int wpr = p.N * esz / 4;
-    const int total = (p.sp.world - 1) * p.M * wpr;
+    const int ppr = p.N * esz / 8;  // pairs per row of a rank's columns
+    const int total = (p.sp.world - 1) * p.M * ppr;
     const int per_cta = (total + gridDim.x - 1) / gridDim.x;
     const int lo = blockIdx.x * per_cta, hi = min(total, lo + per_cta);
     char* ylocal = static_cast<char*>(p.sp.y[p.sp.me]);
     const unsigned long long* inbox = reinterpret_cast<const unsigned long long*>(ylocal + p.sp.inbox_off);
     int i = lo + (int)threadIdx.x;
     if (i >= hi) return true;
-    // position of word i: sender (skipping this rank), row, word in the row; advanced without divisions
-    int w = i % wpr, m = (i / wpr) % p.M, s = i / (wpr * p.M);
+    // position of pair i: sender (skipping this rank), row, pair in the row; advanced without divisions
+    int w = i % ppr, m = (i / ppr) % p.M, s = i / (ppr * p.M);
     bool ok = true;
     while (i < hi && ok) {
         const unsigned long long* slot[U];
-        uint32_t* dst[U];
-        unsigned long long v[U];
+        uint2* dst[U];
+        unsigned long long v0[U], v1[U];
         int n = 0;
 #pragma unroll
         for (int u = 0; u < U; u++) {
             if (i < hi) {
                 const int src = s + (s >= p.sp.me);
-                slot[u] = inbox + ((size_t)src * p.M + m) * wpr + w;
-                dst[u] = reinterpret_cast<uint32_t*>(ylocal + ((size_t)m * p.ld + (size_t)src * p.N) * esz + (size_t)w * 4);
-                v[u] = ld_relaxed_sys64(slot[u]);
+                slot[u] = inbox + (((size_t)src * p.M + m) * ppr + w) * 2;
+                dst[u] = reinterpret_cast<uint2*>(ylocal + ((size_t)m * p.ld + (size_t)src * p.N) * esz + (size_t)w * 8);
+                ld_relaxed_sys64x2(slot[u], v0[u], v1[u]);
                 n = u + 1;
                 i += kThreads;
                 w += kThreads;
-                while (w >= wpr) {
-                    w -= wpr;
+                while (w >= ppr) {
+                    w -= ppr;
                     if (++m == p.M) {
                         m = 0;
                         s++;
@@ -209,11 +209,11 @@ __device__ __forceinline__ bool unpack_inbox(const Params& p, uint32_t epoch) {
 #pragma unroll
         for (int u = 0; u < U; u++) {
             if (u < n) {
-                if ((uint32_t)(v[u] >> 32) != epoch) {
+                if ((uint32_t)(v0[u] >> 32) != epoch || (uint32_t)(v1[u] >> 32) != epoch) {
                     const long long t0 = now_ns();
                     for (;;) {
-                        v[u] = ld_relaxed_sys64(slot[u]);
-                        if ((uint32_t)(v[u] >> 32) == epoch) break;
+                        ld_relaxed_sys64x2(slot[u], v0[u], v1[u]);
+                        if ((uint32_t)(v0[u] >> 32) == epoch && (uint32_t)(v1[u] >> 32) == epoch) break;
                         if (peer_lost() || now_ns() - t0 > kPeerWaitNs) {
                             g_peer_lost = 1;
                             ok = false;
@@ -221,17 +221,17 @@ __device__ __forceinline__ bool unpack_inbox(const Params& p, uint32_t epoch) {
                         }
                     }
                 }
-                if (ok) *dst[u] = (uint32_t)v[u];
+                if (ok) *dst[u] = make_uint2((uint32_t)v0[u], (uint32_t)v1[u]);
             }
         }
     }
     return ok;
 }
 
-template <int MT>
 // ytile (column-sharded launches only): the tile's values once more in shared memory, [row of x][16 columns]
 // (32 bytes per row of x for bf16, 64 for fp32; 16 rows per tile), from where they are sent to the peers
 // without a trip through L2.
+template <int MT>
 __device__ __forceinline__ void store_tile(const Params& p, int rt, int e, float sum, unsigned char* ytile) {
     const int mt = e >> 7, rem = e & 127, ln = rem >> 2, ci = rem & 3;
     const int r16 = (ln >> 2) + 8 * (ci >> 1);
