@@ -314,8 +314,8 @@ def gemm_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks, use_push):
         cols = np.arange(0, N, 97)
         truth = O.qmatmul_truth(x[rows], wq[cols], s[cols], b[cols], bits, group)
         err, _ = O.rel_err(got[np.ix_(rows, cols)], truth)
-        assert err <= O.TOL[O.BF16], f"sharded GEMM: sampled outputs off by {err}"
-        verified = f"sampled outputs of the gathered y within {O.TOL[O.BF16]} of the oracle (max rel err {err:.2e})"
+        verified = (f"sampled outputs of the gathered y within {O.TOL[O.BF16]} of the oracle (max rel err {err:.2e})"
+                    if err <= O.TOL[O.BF16] else f"FAILED: sampled outputs off by {err:.3e}")
     dist.barrier()
     for _ in range(2):
         go()
@@ -410,10 +410,11 @@ def chain_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks):
             bw, bs, bb, bx = ctx.upload(wq), ctx.upload(s), ctx.upload(b), ctx.upload(inputs[name])
             ref = ctx.empty((M, N), np.uint16)
             ctx.qmatmul(bx, bw, bs, bb, ref, M, K, N, BITS, GROUP, BF16, BF16, BF16)
-            assert np.array_equal(symm[name].to_host(), ref.to_host()), f"sharded {name} differs from the unsharded matmul"
+            if not np.array_equal(symm[name].to_host(), ref.to_host()):
+                verified = f"FAILED: sharded {name} differs from the unsharded matmul"
             for t in (bw, bs, bb, bx, ref):
                 t.free()
-        verified = "gathered qkv / o / gate-up / down outputs of one layer bit-identical to the unsharded matmuls"
+        verified = verified or "gathered qkv / o / gate-up / down outputs of one layer bit-identical to the unsharded matmuls"
     dist.barrier()
 
     def step():
@@ -680,10 +681,18 @@ def run_ours(args, rank, world):
     peaks, which = measured_peaks()
     prefill = prefill_legs(ctx, O, BF16, peaks) if (world == 1 and not args.kernel_only) else None
     chain = chain_leg(ctx, O, BF16, peaks) if (world == 1 and not args.kernel_only) else None
-    gemm_sharded = (gemm_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks, use_push)
-                    if (world > 1 and args.gemm_sharded) else None)
-    chain_sharded = (chain_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks)
-                     if (world > 1 and use_push and args.chain_sharded) else None)
+    # the sharded configurations proper (strong scaling), after the sweep; a failure here must not lose the sweep
+    gemm_sharded = chain_sharded = None
+    if world > 1 and not args.kernel_only and not args.no_sharded_legs or world > 1 and args.gemm_sharded:
+        try:
+            gemm_sharded = gemm_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks, use_push)
+        except Exception as e:  # the same on every rank (shapes, memory): nobody is left in a collective
+            gemm_sharded = {"error": repr(e)[:300]}
+    if world > 1 and use_push and (args.chain_sharded or (not args.kernel_only and not args.no_sharded_legs)):
+        try:
+            chain_sharded = chain_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks)
+        except Exception as e:
+            chain_sharded = {"error": repr(e)[:300]}
     if dist is not None:
         ctx.sync()
         dist.barrier()
@@ -747,6 +756,8 @@ def main():
                     help="skip the e2e and CPU-baseline legs (for short runs under a profiler)")
     ap.add_argument("--nccl-allgather", action="store_true",
                     help="N>1: gather the column slices with NCCL + an interleave pass instead of peer stores from the kernel")
+    ap.add_argument("--no-sharded-legs", action="store_true",
+                    help="N>1: skip the column-sharded 8-bit GEMM and chain legs that follow the sweep by default")
     ap.add_argument("--gemm-sharded", action="store_true",
                     help="N>1: also run the column-sharded 8-bit large GEMM (strong scaling, NCCL all-gather) after the sweep")
     ap.add_argument("--chain-sharded", action="store_true",
