@@ -553,10 +553,12 @@ def run_ours(args, rank, world):
                     ref = ctx.empty((M, N_DEC), np.uint16)
                     ctx.qmatmul(x_dev[M], bw, bs, bb, ref, M, K_DEC, N_DEC, BITS, GROUP, BF16, BF16, BF16)
                     want = ref.to_host()
-                    assert np.array_equal(got[:, r * N_DEC:(r + 1) * N_DEC], want), f"columns of rank {r} differ (M={M})"
+                    if not np.array_equal(got[:, r * N_DEC:(r + 1) * N_DEC], want):  # recorded, not raised: the
+                        verified = f"FAILED: columns of rank {r} differ (M={M})"       # other ranks wait in a barrier
+                        print(verified, file=sys.stderr, flush=True)
                     for h in (bw, bs, bb, ref):
                         h.free()
-            verified = "all ranks' columns on rank 0 bit-identical to the single-GPU kernel (M=4, 16)"
+            verified = verified or "all ranks' columns on rank 0 bit-identical to the single-GPU kernel (M=4, 16)"
         dist.barrier()
 
     # one sweep = len(M_SWEEP) * R launches, recorded once as a CUDA graph per M
