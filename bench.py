@@ -13,11 +13,15 @@ launches / device time (CUDA events on the launching stream), GB/s.
 
 At N > 1 (torchrun, one process per GPU) the layer is column-sharded: every
 rank holds its own 11008-column slice (weak scaling: the logical layer has
-N * 11008 columns), computes it, and the slices are all-gathered over NVLink
-after every launch (qmatmul_sharded).  Time = max over ranks.
+N * 11008 columns), and the decode kernel delivers its columns to every rank
+over NVLink itself (qmatmul_sharded_push; --nccl-allgather: NCCL all-gather +
+interleave instead).  Time = max over ranks.  After the sweep the two sharded
+configurations proper run as strong-scaling legs (8-bit large GEMM, the
+quantized-linear chain; --no-sharded-legs skips them).
 
-`e2e` is the same metric through the reference-facing calls with HOST buffers:
-buffer_copy_from_host(x) -> qmatmul -> buffer_copy_to_host(y) per launch.
+`e2e` is the same metric through the reference-facing calls with HOST (page-
+locked) buffers: buffer_copy_from_host_async(x) -> qmatmul ->
+buffer_copy_to_host(y) per launch.
 `--impl reference` times the CPU implementation of the path (the oracle, in
 the reference CPU backend's loop style, all host threads) on a bounded sample.
 """
