@@ -100,6 +100,9 @@ struct Context {
     // split-K workspace of the decode GEMV (partials + arrival counters), grown on demand
     Block* qmv_ws = nullptr;
     size_t qmv_ws_bytes = 0;
+    // Outgrown workspaces stay allocated until the context goes: launches recorded in CUDA graphs keep
+    // using the block they were recorded with.
+    std::vector<Block*> qmv_ws_retired;
     const char* last_kernel = "";
     std::atomic<uint64_t> launches{0};
     std::atomic<uint64_t> copies{0};  // memcpy / memset enqueues
@@ -176,10 +179,12 @@ struct ShardPush {
 // decode GEMV, bf16 activations: mma.sync m16n8k16 with in-register dequant
 bool qmv_mma_supported(const QmmArgs& a);
 size_t qmv_mma_workspace_bytes(const QmmArgs& a, int sm_count);
-// overlap_prev: launch as a programmatic dependent of the previous kernel in the stream (see Context)
+// overlap_prev: launch as a programmatic dependent of the previous kernel in the stream (see Context);
+// x_stable: that previous kernel does not write x, which may then be read before the wait for it
 cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name,
-                           bool overlap_prev = false, const ShardPush* push = nullptr);
+                           bool overlap_prev = false, const ShardPush* push = nullptr, bool x_stable = false);
 bool decode_may_overlap(const Context* c, const QmmArgs& a);
+bool decode_x_stable(const Context* c, const QmmArgs& a);  // the last chain kernel's output does not overlap x
 bool chain_is_open(const Context* c);  // the last thing the context enqueued is a chain kernel (decode matmul, rms-norm)
 void note_chain_launch(Context* c, const void* out, size_t out_bytes);  // right after such a launch, before counting it
 void note_decode_launch(Context* c, const QmmArgs& a);  // call right after a decode launch, before counting it
@@ -192,6 +197,7 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, c
 // non-zero once a kernel gave up on one of its bounded waits since the last call (clears it)
 int take_device_error();
 int* device_error_word();  // where kernels raise it (null if the mapped word could not be set up)
+long long peer_wait_limit_ns();  // limit of a device-side wait for a peer rank (LUXCUDA_PEER_WAIT_MS, default 2000)
 
 cudaError_t launch_dequantize(const uint32_t* wq, const void* scales, const void* biases, void* out, int N, int K,
                               int bits, int group, int sb_dtype, int out_dtype, cudaStream_t stream);

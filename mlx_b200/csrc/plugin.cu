@@ -62,6 +62,7 @@ void destroy_context(LuxBackendContext* ctx) {
             if (ev) cudaEventDestroy(ev);
     }
     if (c->qmv_ws) c->dev->release(c->qmv_ws, c->stream);
+    for (Block* b : c->qmv_ws_retired) c->dev->release(b, c->stream);
     c->dev->release_stream(c->stream);
     c->magic = 0;
     delete c;

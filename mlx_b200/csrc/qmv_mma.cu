@@ -12,9 +12,9 @@
 //   * CTA (one per SM, 16 warps) owns a range of 16-row tiles and a range of
 //     k-blocks; warp w owns the k-blocks kb_lo + w + 16*s of that range and
 //     walks them over the CTA's tiles;
-//   * each warp keeps a private ring of kDepth task buffers in shared memory,
-//     filled with cp.async (16-byte pieces, L1 bypass): kDepth-1 tasks
-//     (2.5 KiB each) are in flight per warp -- 120 KiB per SM -- with no
+//   * each warp keeps a private ring of task buffers in shared memory (four, or two
+//     with 16 rows of x), filled with cp.async (16-byte pieces, L1 bypass): the
+//     tasks ahead of the one being computed (2.5 KiB each) are in flight, with no
 //     registers tied up and no block-wide barrier in the streaming loop;
 //   * lane (g = lane/4, t = lane%4) copies and later reads back exactly its own
 //     pieces: rows g and g+8, the 16-byte pieces t and t+4 of the 128-byte
@@ -46,9 +46,11 @@ namespace {
 
 constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
-constexpr int kDepth = 2;                  // ring stages per warp (measured best: deeper rings only delay the first data)
+// Ring stages per warp.  Up to 8 rows of x: four (three tasks = 7.5 KiB per warp, 120 KiB per SM in flight);
+// with 16 rows the partials and the x fragments kept in shared memory leave room for two.
+constexpr int ring_depth(int mt) { return mt == 1 ? 4 : 2; }
 constexpr int kStageBytes = 2048 + 512;    // 4 x 32 x 16 B of weights + 32 x 16 B of scales/biases
-constexpr int kRingBytes = kWarps * kDepth * kStageBytes;
+constexpr int ring_bytes(int mt) { return kWarps * ring_depth(mt) * kStageBytes; }
 constexpr int kSmemLimit = 227 * 1024 - 256;
 constexpr int kMaxTb = 32;                 // tiles per reduction batch (flags array)
 
@@ -80,7 +82,7 @@ struct Params {
     const __nv_bfloat16* scales;
     const __nv_bfloat16* biases;
     void* y;
-    int* error;              // host-visible error word (bounded waits of the sharded path)
+    int* error;              // host-visible error word (bounded waits of the sharded path); may be null
     float* scratch;          // [n_rt][nkb][128*MT] partials of k-split tiles
     unsigned int* counters;  // [n_rt] arrival counters (zero between launches)
     int M, K, N, gshift, y_bf16;
@@ -92,6 +94,8 @@ struct Params {
     int tb;                  // tiles per reduction batch
     int sb_bytes;            // bytes of scales per row per k-block: 2, 4, 8 or 16
     int ld, col0;            // y row stride and first column (elements): N and 0 unless the layer is column-sharded
+    int x_early;             // x is not written by the previous kernel of the stream: it may be read before the wait for it
+    long long peer_wait_ns;  // limit of a wait for a peer (column-sharded launches)
     ShardPush sp;            // sp.world > 1: the finished tiles are also stored into the peers' copies of y
 };
 
@@ -105,10 +109,9 @@ struct Params {
 // inbox into the local y; when the launch ends the local y is whole, so stream order is all a consumer
 // needs.  One hand-shake guards the inbox: a rank announces ready[q] = epoch on every peer when its kernel
 // of that call has started -- everything it enqueued before has then finished with its y and inbox -- and a
-// sender waits for it before its first remote store.  Waits are bounded (kPeerWaitNs): on a time-out the
+// sender waits for it before its first remote store.  Waits are bounded (Params::peer_wait_ns): on a time-out the
 // kernel raises the host-visible error word, stops waiting (in every later launch too) and returns.
 constexpr int kFlagEpoch = 0, kFlagCtaDone = 1, kFlagReady = 8;
-constexpr long long kPeerWaitNs = 2000000000ll;
 
 __device__ __forceinline__ long long now_ns() {
     long long t;
@@ -134,12 +137,12 @@ __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
 __device__ int g_peer_lost;
 __device__ __forceinline__ bool peer_lost() { return *reinterpret_cast<volatile int*>(&g_peer_lost) != 0; }
 // true once *flag has reached epoch e (wrap-around safe)
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t e) {
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t e, long long limit_ns) {
     if (peer_lost()) return false;
     const long long t0 = now_ns();
     for (;;) {
         if ((int32_t)(ld_relaxed_sys(flag) - e) >= 0) return true;
-        if (now_ns() - t0 > kPeerWaitNs) {
+        if (now_ns() - t0 > limit_ns) {
             g_peer_lost = 1;
             return false;
         }
@@ -214,7 +217,7 @@ __device__ __forceinline__ bool unpack_inbox(const Params& p, uint32_t epoch) {
                     for (;;) {
                         ld_relaxed_sys64x2(slot[u], v0[u], v1[u]);
                         if ((uint32_t)(v0[u] >> 32) == epoch && (uint32_t)(v1[u] >> 32) == epoch) break;
-                        if (peer_lost() || now_ns() - t0 > kPeerWaitNs) {
+                        if (peer_lost() || now_ns() - t0 > p.peer_wait_ns) {
                             g_peer_lost = 1;
                             ok = false;
                             break;
@@ -440,8 +443,9 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
     constexpr int XV = BITS == 4 ? 8 : 4;  // x fragments (uint4) per lane per k-block per 8-row block
     constexpr int KB = 1024 / BITS;        // weights per k-block (128 bytes per row)
     constexpr int E4 = MT * 32;            // float4 per partial
+    constexpr int D = ring_depth(MT);      // ring stages of a warp
     extern __shared__ __align__(16) unsigned char smem[];
-    float4* part = reinterpret_cast<float4*>(smem + kRingBytes);   // [tb][nkl][MT][32]; ring: [kWarps][kDepth][kStageBytes]
+    float4* part = reinterpret_cast<float4*>(smem + ring_bytes(MT));   // [tb][nkl][MT][32]; ring: [kWarps][D][kStageBytes]
     // after the partials (MT == 2): the x fragments of rows 8..15, [warp][fragment][lane]
     uint4* xs = reinterpret_cast<uint4*>(smem + p.xs_off) + (threadIdx.x >> 5) * (XV * 32) + (threadIdx.x & 31);
     __shared__ int s_flags[kMaxTb];
@@ -458,52 +462,68 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
     const int gpk = KB >> p.gshift;    // groups per k-block
     const unsigned char* wbase = reinterpret_cast<const unsigned char*>(p.wq) + t * 16;
     const __nv_bfloat16* sb_src = lane < 16 ? p.scales : p.biases;
-    const uint32_t ring_lo = smem_u32(smem) + warp * (kDepth * kStageBytes) + lane * 16;  // this lane's slot, stage 0
+    const uint32_t ring_lo = smem_u32(smem) + warp * (D * kStageBytes) + lane * 16;  // this lane's slot, stage 0
     const int tail_tile = (p.N & 15) ? p.n_rt - 1 : -1;  // the tile whose rows must be clamped to N-1
+    const bool has_work = kb_lo + warp < kb_hi && rt_lo < rt_hi;
 
-    // The warp's tasks: for each batch of tb tiles, for each of its k-blocks, the tiles of the batch
-    // ("run").  One task is in flight while the previous one is computed (two ring stages).
+    // The warp's tasks, in order: for each batch of tb tiles, for each of its k-blocks, the tiles of the
+    // batch ("run": they share the x fragments of that k-block).  D-1 tasks are in flight while one is
+    // computed; the fetch runs that far ahead of the computation, one commit group per task (empty past the end).
     const size_t half_tile = 8 * row_bytes;
-    auto issue = [&](int rt, int kb, uint32_t dst) {
-        const unsigned char* p0;
-        const unsigned char* p1;
-        int elem;
-        if (rt != tail_tile) {
-            p0 = wbase + (size_t)(rt * 16 + g) * row_bytes + kb * 128;
-            p1 = p0 + half_tile;
-            elem = (rt * 16 + (lane & 15)) * gpr + kb * gpk;
-        } else {  // rows past N read row N-1 (their results are never stored)
-            const int n0 = rt * 16;
-            p0 = wbase + (size_t)min(n0 + g, p.N - 1) * row_bytes + kb * 128;
-            p1 = wbase + (size_t)min(n0 + g + 8, p.N - 1) * row_bytes + kb * 128;
-            elem = min(n0 + (lane & 15), p.N - 1) * gpr + kb * gpk;
+    int f_b0 = rt_lo, f_kb = kb_lo + warp, f_rt = rt_lo;  // the task fetched next
+    uint32_t f_dst = ring_lo;                             // and the stage it goes to
+    auto fetch_next = [&]() {
+        if (has_work && f_b0 < rt_hi) {
+            const int rt = f_rt, kb = f_kb;
+            const unsigned char* p0;
+            const unsigned char* p1;
+            int elem;
+            if (rt != tail_tile) {
+                p0 = wbase + (size_t)(rt * 16 + g) * row_bytes + kb * 128;
+                p1 = p0 + half_tile;
+                elem = (rt * 16 + (lane & 15)) * gpr + kb * gpk;
+            } else {  // rows past N read row N-1 (their results are never stored)
+                const int n0 = rt * 16;
+                p0 = wbase + (size_t)min(n0 + g, p.N - 1) * row_bytes + kb * 128;
+                p1 = wbase + (size_t)min(n0 + g + 8, p.N - 1) * row_bytes + kb * 128;
+                elem = min(n0 + (lane & 15), p.N - 1) * gpr + kb * gpk;
+            }
+            cp_async16(f_dst, p0);
+            cp_async16(f_dst + 512, p0 + 64);
+            cp_async16(f_dst + 1024, p1);
+            cp_async16(f_dst + 1536, p1 + 64);
+            if (p.sb_bytes == 16) cp_async16(f_dst + 2048, sb_src + elem);
+            else if (p.sb_bytes == 8) cp_async8(f_dst + 2048, sb_src + elem);
+            else cp_async4(f_dst + 2048, sb_src + (p.sb_bytes == 2 ? (elem & ~1) : elem));  // a lone scale travels with its neighbour
+            // on to the task after it
+            f_dst = f_dst + kStageBytes == ring_lo + D * kStageBytes ? ring_lo : f_dst + kStageBytes;
+            if (++f_rt == min(f_b0 + tb, rt_hi)) {
+                f_kb += kWarps;
+                if (f_kb >= kb_hi) {
+                    f_kb = kb_lo + warp;
+                    f_b0 += tb;
+                }
+                f_rt = f_b0;
+            }
         }
-        cp_async16(dst, p0);
-        cp_async16(dst + 512, p0 + 64);
-        cp_async16(dst + 1024, p1);
-        cp_async16(dst + 1536, p1 + 64);
-        if (p.sb_bytes == 16) cp_async16(dst + 2048, sb_src + elem);
-        else if (p.sb_bytes == 8) cp_async8(dst + 2048, sb_src + elem);
-        else cp_async4(dst + 2048, sb_src + (p.sb_bytes == 2 ? (elem & ~1) : elem));  // a lone scale travels with its neighbour
+        cp_async_commit();
     };
 
-    const bool has_work = kb_lo + warp < kb_hi && rt_lo < rt_hi;
-    const uint32_t ring_sum = 2 * ring_lo + kStageBytes;  // stage <-> other stage
-    uint32_t src_c = ring_lo;                             // stage of the task computed next (this lane's slot)
     // The x fragments of the first k-block are on the critical path of the first task, and a load queues
-    // behind whatever the SM has already requested.  With up to 8 rows of x (32 registers) they are
-    // therefore requested ahead of the weights: first of all in a plain launch; in a dependent launch,
-    // where x may still be being written, right after the wait and ahead of the second task.  (With 16
-    // rows the fragments would have to be held across the issue code and spill; they stay behind it.)
+    // behind whatever the SM has already requested.  When the host knows that the previous kernel of the
+    // stream does not write x (or there is none to wait for), they are requested first of all, ahead of the
+    // weights; otherwise right after the wait.  (With 16 rows the fragments would have to be held across the
+    // fetch code and spill; they stay behind it.)
     constexpr bool kXFirst = MT == 1;
     uint4 xr[MT][XV];
-    if (kXFirst && !p.chained && has_work) load_x_raw<BITS, MT>(p, kb_lo + warp, g, t, xr);
-    if (has_work) issue(rt_lo, kb_lo + warp, src_c);
-    cp_async_commit();
+    if (kXFirst && p.x_early && has_work) load_x_raw<BITS, MT>(p, kb_lo + warp, g, t, xr);
+#pragma unroll
+    for (int i = 0; i < D - 1; i++) fetch_next();
 
-    // Everything above touched only the weights, which no kernel of the chain writes.  From here on the
-    // kernel reads x and uses the scratch, which the previous kernel may have written: wait for it, then
-    // let the next kernel of the chain start its own weight fetch.  (Both are no-ops in a plain launch.)
+    // Everything above touched only the weights (and, if the host allowed it, x), which no kernel of the chain
+    // writes.  From here on the kernel reads x and uses the scratch, which the previous kernel may have
+    // written: wait for it, then let the next kernel of the chain start its own weight fetch.  (Both are
+    // no-ops in a plain launch.)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // column-sharded: this call's number, and the word to the peers that our copy of y may be overwritten
@@ -515,26 +535,18 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
         // (a relaxed store: it publishes no data of this kernel, only that the kernel has started)
         if (blockIdx.x == 0 && tid < p.sp.world && tid != p.sp.me) st_relaxed_sys(p.sp.flags[tid] + kFlagReady + p.sp.me, epoch);
     }
-    if (kXFirst && p.chained && has_work) load_x_raw<BITS, MT>(p, kb_lo + warp, g, t, xr);
+    if (kXFirst && !p.x_early && has_work) load_x_raw<BITS, MT>(p, kb_lo + warp, g, t, xr);
     bool x_loaded = kXFirst;  // (of the first run)
 
-    uint32_t sboff[2][2];  // byte offsets of this lane's scales inside a stage, by row half r and piece h
+    uint32_t src_c = ring_lo;  // stage of the task computed next (this lane's slot)
+    uint32_t sboff[2][2];      // byte offsets of this lane's scales inside a stage, by row half r and piece h
 #pragma unroll 1
     for (int b0 = rt_lo; b0 < rt_hi; b0 += tb) {
         const int nt = min(tb, rt_hi - b0);
         if (has_work) {
 #pragma unroll 1
             for (int kb = kb_lo + warp; kb < kb_hi; kb += kWarps) {
-                // the run after this one: next k-block of the batch, else first k-block of the next batch
-                int kb_n = kb + kWarps, b0_n = b0;
-                if (kb_n >= kb_hi) {
-                    kb_n = kb_lo + warp;
-                    b0_n = b0 + tb;
-                }
-                const int rt_last = b0 + nt - 1;
-                if (nt > 1) issue(b0 + 1, kb, ring_sum - src_c);
-                else if (b0_n < rt_hi) issue(b0_n, kb_n, ring_sum - src_c);
-                cp_async_commit();
+                fetch_next();  // (the run's first fetch goes out ahead of the x loads)
                 if (!x_loaded) load_x_raw<BITS, MT>(p, kb, g, t, xr);
                 x_loaded = false;
                 permute_x<BITS, MT>(xr);
@@ -556,13 +568,9 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
                     ready_early = ld_relaxed_sys(p.sp.flags[p.sp.me] + kFlagReady + tid);  // used at the first push
                 float4* dstp = part + (kb - kb_lo) * E4 + lane;
 #pragma unroll 1
-                for (int rt = b0; rt <= rt_last; rt++) {
-                    if (rt != b0) {  // (the run's first prefetch was issued before the x loads)
-                        if (rt < rt_last) issue(rt + 1, kb, ring_sum - src_c);
-                        else if (b0_n < rt_hi) issue(b0_n, kb_n, ring_sum - src_c);
-                        cp_async_commit();
-                    }
-                    cp_async_wait<1>();
+                for (int rt = b0; rt < b0 + nt; rt++) {
+                    if (rt != b0) fetch_next();
+                    cp_async_wait<D - 1>();
                     __syncwarp();
                     uint4 w[2][2];
                     uint32_t s[2][2], b[2][2];
@@ -590,7 +598,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
                                                     acc[mt][0][2] + acc[mt][1][2], acc[mt][0][3] + acc[mt][1][3]);
                     dstp += nkl * E4;
                     __syncwarp();  // every lane is done with the stage before it is refilled
-                    src_c = ring_sum - src_c;
+                    src_c = src_c + kStageBytes == ring_lo + D * kStageBytes ? ring_lo : src_c + kStageBytes;
                 }
             }
         }
@@ -598,11 +606,22 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
             ready_checked = true;
             int ok = 1;
             if (tid < p.sp.world && tid != p.sp.me)
-                ok = (int32_t)(ready_early - epoch) >= 0 || wait_flag(p.sp.flags[p.sp.me] + kFlagReady + tid, epoch);
+                ok = (int32_t)(ready_early - epoch) >= 0 || wait_flag(p.sp.flags[p.sp.me] + kFlagReady + tid, epoch, p.peer_wait_ns);
             peers_ready = __syncthreads_and(ok);
         }
-        batch_end<MT>(p, reinterpret_cast<const float*>(part), b0, nt, kb_lo, nkl, s_flags, b0 + tb < rt_hi, peers_ready, epoch,
-                      p.yt_off ? smem + p.yt_off : nullptr);
+        // End of the batch: sum the per-k-block partials of every tile in k-block order and write y.  The
+        // common case stays in line (reads of the parameter block from a function out of line are slow).
+        if (p.ks == 1 && p.sp.world <= 1) {
+            constexpr int E = 128 * MT;
+            __syncthreads();
+            for (int ti = tid / E; ti < nt; ti += kThreads / E)
+                store_tile<MT>(p, b0 + ti, tid % E,
+                               ordered_sum<false>(reinterpret_cast<const float*>(part) + ti * nkl * E + tid % E, nkl, E, 0.0f), nullptr);
+            if (b0 + tb < rt_hi) __syncthreads();  // the partial buffer is reused by the next batch
+        } else {
+            batch_end<MT>(p, reinterpret_cast<const float*>(part), b0, nt, kb_lo, nkl, s_flags, b0 + tb < rt_hi, peers_ready, epoch,
+                          p.yt_off ? smem + p.yt_off : nullptr);
+        }
     }
     cp_async_wait<0>();
     if (p.sp.world > 1) {
@@ -623,8 +642,13 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
 
 struct Plan {
     int nkb, n_rt, mt, chunks, ks, tb, gshift, sb_bytes, xs_off, yt_off;
-    size_t smem, ctr_bytes, scratch_bytes;
+    size_t smem, scratch_bytes;
 };
+
+// Arrival counters of k-split tiles live at the head of the workspace in a region of fixed size, so that
+// launches of different shapes that share a workspace agree on where the counters end and the partials begin.
+constexpr size_t kCounterBytes = 4096;
+constexpr int kMaxSplitTiles = (int)(kCounterBytes / sizeof(unsigned int));
 
 bool make_plan(const QmmArgs& a, int sm_count, Plan* pl, bool sharded = false) {
     if (a.x_dtype != LUX_DTYPE_BFLOAT16 || a.sb_dtype != LUX_DTYPE_BFLOAT16) return false;
@@ -647,22 +671,24 @@ bool make_plan(const QmmArgs& a, int sm_count, Plan* pl, bool sharded = false) {
     // CTA's 16 warps would each still own more than one k-block
     int ks = 1;
     if (pl->n_rt * 2 <= sm_count) ks = std::max(1, std::min((pl->nkb + kWarps - 1) / kWarps, sm_count / pl->n_rt));
-    if (const char* env = getenv("LUXCUDA_QMV_KSPLIT")) ks = std::max(1, std::min(atoi(env), pl->nkb));
+    if (const char* env = getenv("LUXCUDA_QMV_KSPLIT"))
+        if (pl->n_rt <= kMaxSplitTiles) ks = std::max(1, std::min(atoi(env), pl->nkb));
+    if (pl->n_rt > kMaxSplitTiles) ks = 1;
     pl->ks = ks;
     pl->chunks = std::max(1, std::min(pl->n_rt, sm_count / ks));
     const int tiles_max = (pl->n_rt + pl->chunks - 1) / pl->chunks;
     const int nkl_max = (pl->nkb + ks - 1) / ks;
     const size_t per_tile = (size_t)nkl_max * pl->mt * 512;
     const size_t xs_bytes = pl->mt == 2 ? (size_t)kWarps * (a.bits == 4 ? 8 : 4) * 512 : 0;  // x fragments of rows 8..15
-    const size_t avail = (size_t)kSmemLimit - kRingBytes - xs_bytes;
+    const size_t ring = (size_t)ring_bytes(pl->mt);
+    const size_t avail = (size_t)kSmemLimit - ring - xs_bytes;
     // column-sharded launches stage every finished tile once more (16 rows of x x 16 columns) for the peers
     const size_t yt_tile = sharded ? (a.y_dtype == LUX_DTYPE_BFLOAT16 ? 512 : 1024) : 0;
     if (per_tile + yt_tile > avail) return false;
     pl->tb = (int)std::min<size_t>(std::min<size_t>(tiles_max, avail / (per_tile + yt_tile)), kMaxTb);
-    pl->xs_off = (int)(kRingBytes + pl->tb * per_tile);
+    pl->xs_off = (int)(ring + pl->tb * per_tile);
     pl->yt_off = sharded ? (int)(pl->xs_off + xs_bytes) : 0;
-    pl->smem = kRingBytes + pl->tb * per_tile + xs_bytes + (sharded ? pl->tb * yt_tile : 0);
-    pl->ctr_bytes = ((size_t)pl->n_rt * sizeof(unsigned int) + 255) & ~size_t(255);
+    pl->smem = ring + pl->tb * per_tile + xs_bytes + (sharded ? pl->tb * yt_tile : 0);
     pl->scratch_bytes = ks > 1 ? (size_t)pl->n_rt * pl->nkb * pl->mt * 128 * sizeof(float) : 0;
     if (((uintptr_t)a.wq & 15) || ((uintptr_t)a.x & 15) || ((uintptr_t)a.scales & 15) || ((uintptr_t)a.biases & 15)) return false;
     return true;
@@ -697,6 +723,16 @@ cudaError_t launch_t(const Params& p, const Plan& pl, cudaStream_t stream, bool 
 
 }  // namespace
 
+// Limit of a device-side wait for a peer rank, from LUXCUDA_PEER_WAIT_MS (default 2000 ms).
+long long peer_wait_limit_ns() {
+    static const long long ns = [] {
+        const char* env = getenv("LUXCUDA_PEER_WAIT_MS");
+        const long long ms = env ? atoll(env) : 2000;
+        return (ms < 1 ? 1 : ms) * 1000000ll;
+    }();
+    return ns;
+}
+
 bool qmv_mma_supported(const QmmArgs& a) {
     Plan pl;
     return make_plan(a, 148, &pl);
@@ -707,13 +743,13 @@ bool qmv_mma_supported(const QmmArgs& a) {
 size_t qmv_mma_workspace_bytes(const QmmArgs& a, int sm_count) {
     Plan pl;
     if (!make_plan(a, sm_count, &pl)) return 0;
-    return pl.ctr_bytes + pl.scratch_bytes;
+    return kCounterBytes + pl.scratch_bytes;
 }
 
-// workspace layout: [counters: n_rt x u32, padded to 256 B][partials]; the counters must
-// be zero before the first launch and are left zero by every launch.
+// workspace layout: [counters: kCounterBytes][partials]; the counters must be zero before the
+// first launch and are left zero by every launch.
 cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name,
-                           bool overlap_prev, const ShardPush* push) {
+                           bool overlap_prev, const ShardPush* push, bool x_stable) {
     Plan pl;
     if (!make_plan(a, sm_count, &pl, push && push->world > 1)) return cudaErrorInvalidValue;
     Params p;
@@ -723,7 +759,7 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
     p.biases = (const __nv_bfloat16*)a.biases;
     p.y = a.y;
     p.counters = (unsigned int*)workspace;
-    p.scratch = (float*)((unsigned char*)workspace + pl.ctr_bytes);
+    p.scratch = (float*)((unsigned char*)workspace + kCounterBytes);
     p.M = a.M; p.K = a.K; p.N = a.N;
     p.gshift = pl.gshift;
     p.y_bf16 = a.y_dtype == LUX_DTYPE_BFLOAT16;
@@ -733,7 +769,9 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
     p.xs_off = pl.xs_off;
     p.yt_off = pl.yt_off;
     p.ld = a.N; p.col0 = 0;
+    p.x_early = (!overlap_prev || x_stable) ? 1 : 0;
     p.error = nullptr;
+    p.peer_wait_ns = peer_wait_limit_ns();
     if (push && push->world > 1) {
         if (push->world > kMaxShardWorld || (a.N & 15)) return cudaErrorInvalidValue;  // whole 16-column tiles only
         p.sp = *push;
@@ -815,7 +853,7 @@ extern "C" LUX_GPU_BACKEND_EXPORT LuxBackendError lux_gpu_cuda_qmatmul_decode_no
     cudaError_t e = static_scratch_ptr(c->dev->device(), &scratch);
     if (e != cudaSuccess) return map_cuda_error(e, "cudaGetSymbolAddress(static scratch)");
     const char* name = "";
-    e = launch_qmv_mma(a, scratch, c->dev->sm_count, c->stream, &name, decode_may_overlap(c, a));
+    e = launch_qmv_mma(a, scratch, c->dev->sm_count, c->stream, &name, decode_may_overlap(c, a), nullptr, decode_x_stable(c, a));
     if (e != cudaSuccess) return map_cuda_error(e, name);
     c->last_kernel = name;
     c->launches++;

@@ -60,6 +60,9 @@ bool decode_may_overlap(const Context* c, const QmmArgs& a) {
            !ranges_overlap((const char*)a.scales, sb, c->chain_out_lo, c->chain_out_hi) &&
            !ranges_overlap((const char*)a.biases, sb, c->chain_out_lo, c->chain_out_hi);
 }
+bool decode_x_stable(const Context* c, const QmmArgs& a) {
+    return !ranges_overlap((const char*)a.x, (size_t)a.M * a.K * 2, c->chain_out_lo, c->chain_out_hi);
+}
 void note_decode_launch(Context* c, const QmmArgs& a) {
     c->chain_launches = c->launches.load();
     c->chain_copies = c->copies.load();
@@ -69,6 +72,12 @@ void note_decode_launch(Context* c, const QmmArgs& a) {
 
 LuxBackendError ensure_qmv_workspace(Context* c, size_t bytes) {
     if (bytes <= c->qmv_ws_bytes) return LUX_BACKEND_OK;
+    // Growing means an allocation and a memset: neither belongs into a stream capture.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(c->stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) {
+        set_last_error("qmatmul: this shape needs a larger decode workspace (%zu bytes); run it once outside the graph capture first", bytes);
+        return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    }
     cudaError_t e = cudaSuccess;
     Block* nb = c->dev->acquire(bytes, c->stream, &e);
     if (!nb) return map_cuda_error(e, "qmv workspace");
@@ -79,7 +88,7 @@ LuxBackendError ensure_qmv_workspace(Context* c, size_t bytes) {
         c->dev->release(nb, c->stream);
         return map_cuda_error(e, "qmv workspace memset");
     }
-    if (c->qmv_ws) c->dev->release(c->qmv_ws, c->stream);
+    if (c->qmv_ws) c->qmv_ws_retired.push_back(c->qmv_ws);  // graphs recorded earlier still point at it
     c->qmv_ws = nb;
     c->qmv_ws_bytes = bytes;
     return LUX_BACKEND_OK;
@@ -107,7 +116,8 @@ LuxBackendError qmatmul_on_stream(Context* c, const QmmArgs& a) {
                     chunk.M = a.M - m0 < 16 ? a.M - m0 : 16;
                     chunk.x = (const char*)a.x + (size_t)m0 * a.K * 2;
                     chunk.y = (char*)a.y + (size_t)m0 * a.N * ysz;
-                    e = launch_qmv_mma(chunk, c->qmv_ws->ptr, c->dev->sm_count, c->stream, &name, decode_may_overlap(c, chunk));
+                    e = launch_qmv_mma(chunk, c->qmv_ws->ptr, c->dev->sm_count, c->stream, &name, decode_may_overlap(c, chunk),
+                                       nullptr, decode_x_stable(c, chunk));
                     if (e == cudaSuccess) {
                         c->launches++;
                         note_decode_launch(c, chunk);

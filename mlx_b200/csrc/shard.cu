@@ -200,6 +200,19 @@ LuxBackendError qmatmul_sharded(LuxCudaShardComm* sc, LuxBackendBuffer* x, LuxBa
     const lux_gpu_quant_vtbl* q = quant_vtbl();
     auto* cctx = reinterpret_cast<LuxBackendContext*>(c);
     if (sc->world == 1) return q->qmatmul(cctx, x, wq, scales, biases, y_full, M, K, Nl, bits, group, x_dtype, sb_dtype, y_dtype);
+    // The library's all-gather is not recorded into CUDA graphs here: a capture of it together with the
+    // plugin's kernels once hung a two-GPU run on this class of machine (cause not established), and every
+    // rank would have to capture and replay the same collective sequence anyway.  Refuse instead.
+    {
+        DeviceGuard g(c->dev->device());
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(c->stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+            cudaGetLastError();
+            set_last_error("qmatmul_sharded: not available while the context's stream is being captured into a graph; "
+                           "use qmatmul_sharded_push (peer stores) inside graphs");
+            return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+        }
+    }
     Buffer *by = as_buf(y_full), *bst = as_buf(staging);
     const size_t ys = y_dtype == LUX_DTYPE_BFLOAT16 ? 2 : (y_dtype == LUX_DTYPE_FLOAT32 ? 4 : 0);
     if (!by || !bst || !ys || M < 0 || Nl < 0) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;

@@ -21,7 +21,7 @@ SHAPES = [
     (64, 256, 128, 8, 128),      # 8-bit
     (96, 1024, 300, 8, 64),
     (256, 2048, 1024, 8, 32),
-    (512, 4096, 2048, 4, 64),    # many tiles per CTA: accumulator double buffering, stage wrap-around
+    (512, 4096, 2048, 4, 64),    # many tiles per CTA: stage wrap-around
 ]
 
 
@@ -71,6 +71,29 @@ def test_prefill_full_size_sampled(ctx, oracle):
     rows = [0, 1, 255, 256, 1023, 1500, 2046]
     t = oracle.qmatmul_truth(x[rows], wq, s, b, 4, 64)
     err, _ = oracle.rel_err(y[rows], t)
+    assert err <= oracle.TOL[oracle.BF16], err
+
+
+def test_large_8bit_full_size_sampled(ctx, oracle):
+    """The 8-bit large-GEMM configuration on one GPU (M=512, K=8192, N=28672, group 128): one-hot rows of x
+    pick out dequantised weight columns exactly; random rows are checked against the oracle on a sample of
+    output columns (the oracle is run on the matching rows of W only)."""
+    M, K, N, bits, group = 512, 8192, 28672, 8, 128
+    wq, s, b = oracle.make_layer(N, K, bits, group, oracle.BF16, config_id=4)  # 8-bit default scale range: U(1e-4, 2e-3)
+    x = oracle.make_x(M, K, oracle.BF16, config_id=4)
+    hot = {3: 0, 200: 127, 317: 4097, 511: 8191}
+    for m, k in hot.items():
+        x[m] = 0
+        x[m, k] = 0x3F80
+    y, kern = run_qmatmul(ctx, x, wq, s, b, bits, group, BF16)
+    assert kern.startswith("qmm_tc"), kern
+    cols = np.r_[0:128, 3584 - 64:3584 + 64, 14336 - 64:14336 + 64, 20000:20128, N - 128:N]
+    w = oracle.dequantize(wq[cols], s[cols], b[cols], K, bits, group, oracle.BF16)
+    for m, k in hot.items():
+        assert np.array_equal(y[m, cols], w[:, k])
+    rows = [0, 1, 127, 128, 255, 256, 400, 510]
+    t = oracle.qmatmul_truth(x[rows], wq[cols], s[cols], b[cols], bits, group)
+    err, _ = oracle.rel_err(y[np.ix_(rows, cols)], t)
     assert err <= oracle.TOL[oracle.BF16], err
 
 

@@ -101,6 +101,28 @@ def test_decode_bf16(ctx, oracle, M, K, N, bits, group):
     check(oracle, y, x, wq, s, b, bits, group, oracle.BF16)
 
 
+@pytest.mark.parametrize("M", [1, 4, 8, 16])
+def test_decode_sweep_shape(ctx, oracle, M):
+    """The decode-sweep configuration itself (K=4096, N=11008, 4-bit, group 64) at each of its batch sizes."""
+    K, N = 4096, 11008
+    wq, s, b = oracle.make_layer(N, K, 4, 64, oracle.BF16, config_id=2)
+    x = oracle.make_x(M, K, oracle.BF16, config_id=2, tag=M)
+    y, kern = run_qmatmul(ctx, x, wq, s, b, 4, 64, BF16)
+    assert kern.startswith("qmv_mma"), kern
+    check(oracle, y, x, wq, s, b, 4, 64, oracle.BF16)
+
+
+def test_decode_workspace_shared_between_split_shapes(ctx, oracle):
+    """Two K-split shapes with different tile counts, one after the other on one context: the second must not
+    read the first one's partials as arrival counters (the counters sit in a region of fixed size)."""
+    for (M, K, N, bits, group) in ((8, 8192, 64, 4, 64), (1, 8192, 1120, 4, 64), (8, 16384, 1024, 4, 64), (1, 8192, 1120, 4, 64)):
+        wq, s, b = oracle.make_layer(N, K, bits, group, oracle.BF16, config_id=2, layer=K, proj=N)
+        x = oracle.make_x(M, K, oracle.BF16, config_id=2, layer=K, tag=M)
+        y, kern = run_qmatmul(ctx, x, wq, s, b, bits, group, BF16)
+        assert kern.startswith("qmv_mma"), kern
+        check(oracle, y, x, wq, s, b, bits, group, oracle.BF16)
+
+
 @pytest.mark.parametrize("M,K,N,bits,group", [(1, 4096, 4096, 4, 64), (4, 1024, 130, 4, 64), (2, 512, 64, 8, 128),
                                               (16, 256, 9, 4, 32), (1, 64, 5, 4, 64)])
 def test_fp32_compute(ctx, oracle, M, K, N, bits, group):
