@@ -201,13 +201,13 @@ def prefill_legs(ctx, O, BF16, peaks):
 
 
 def chain_leg(ctx, O, BF16, peaks):
-    """The quantized-linear chain configuration at one GPU: one decode step (M = 8) through 32 layers of quantized projections
-    (q,k,v,o 4096x4096; gate,up 11008x4096; down 4096x11008; 4-bit g64) with the rms-norms between them.
+    """The quantized-linear chain configuration at one GPU: one decode step (M = 8) through 32 layers of quantized
+    projections (q,k,v,o 4096x4096; gate,up 11008x4096; down 4096x11008; 4-bit g64) with the full dataflow between them:
+    a = bf16(q + k + v); o = Wo a; r = rms_norm(o); m = rms_norm(bf16(gate(r) * up(r))); d = Wd m; h' = rms_norm(d).
     q/k/v run as one N = 12288 launch and gate/up as one N = 22016 launch (the configuration allows it: same
-    results), so a layer is 4 matmul launches + 3 rms-norm launches, each ordered behind the one before.
-    Four distinct layers' weights (455 MB, more than L2) are cycled eight times: a layer's weights were last
-    read three layers earlier.  The bf16 adds / products between projections of the full dataflow (elementwise,
-    64-176 KB) are left out; their inputs are stand-in buffers of the right shape."""
+    results), so a layer is 4 matmul launches + 4 small row kernels (sum3, rms-norm, mul+rms-norm, rms-norm), each
+    ordered behind, and dependent on, the one before.  Four distinct layers' weights (455 MB, more than L2) are cycled
+    eight times: a layer's weights were last read three layers earlier."""
     M, D, FF, L, DISTINCT = 8, 4096, 11008, 32, 4
     shapes = [("qkv", 3 * D, D), ("o", D, D), ("gateup", 2 * FF, D), ("down", D, FF)]
     layers = []
@@ -218,9 +218,7 @@ def chain_leg(ctx, O, BF16, peaks):
             ws[name] = (ctx.upload(wq), ctx.upload(s), ctx.upload(b), N, K)
         layers.append(ws)
     h = ctx.upload(O.make_x(M, D, O.BF16, config_id=5))
-    a = ctx.upload(O.make_x(M, D, O.BF16, config_id=5, tag=1))     # stands for bf16(q + k + v)
-    gu = ctx.upload(O.make_x(M, FF, O.BF16, config_id=5, tag=2))   # stands for bf16(gate * up)
-    t = {n: ctx.empty((M, N), np.uint16) for n, N in (("qkv", 3 * D), ("o", D), ("r", D), ("gateup", 2 * FF), ("m", FF), ("d", D))}
+    t = {n: ctx.empty((M, N), np.uint16) for n, N in (("qkv", 3 * D), ("a", D), ("o", D), ("r", D), ("gateup", 2 * FF), ("m", FF), ("d", D))}
 
     def mm(ws, name, src, dst):
         bw, bs, bb, N, K = ws[name]
@@ -230,10 +228,11 @@ def chain_leg(ctx, O, BF16, peaks):
         for l in range(L):
             ws = layers[l % DISTINCT]
             mm(ws, "qkv", h, t["qkv"])
-            mm(ws, "o", a, t["o"])
+            ctx.sum3(t["qkv"], t["a"], M, D, 3 * D)
+            mm(ws, "o", t["a"], t["o"])
             ctx.rms_norm(t["o"], t["r"], M, D, 1e-6, BF16, BF16)
             mm(ws, "gateup", t["r"], t["gateup"])
-            ctx.rms_norm(gu, t["m"], M, FF, 1e-6, BF16, BF16)
+            ctx.mul_rms_norm(t["gateup"], t["m"], M, FF, 2 * FF, 1e-6)
             mm(ws, "down", t["m"], t["d"])
             ctx.rms_norm(t["d"], h, M, D, 1e-6, BF16, BF16)
 
@@ -257,10 +256,11 @@ def chain_leg(ctx, O, BF16, peaks):
     for ws in layers:
         for (bw, bs, bb, _, _) in ws.values():
             bw.free(); bs.free(); bb.free()
-    for b in list(t.values()) + [h, a, gu]:
+    for b in list(t.values()) + [h]:
         b.free()
-    return {"workload": "32 layers x (qkv, o, gate/up, down) + 3 rms-norms, M=8, one GPU, one CUDA graph per step",
-            "ms_per_step": ms, "launches_per_step": L * 7, "algorithmic_GB": nbytes / 1e9, "GBps": gbs,
+    return {"workload": "32 layers x (qkv, sum3, o, rms-norm, gate/up, mul+rms-norm, down, rms-norm), M=8, one GPU, "
+                        "every launch consumes the previous one's output, one CUDA graph per step",
+            "ms_per_step": ms, "launches_per_step": L * 8, "algorithmic_GB": nbytes / 1e9, "GBps": gbs,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"]}}
 
 

@@ -48,7 +48,7 @@ extern "C" {
 #endif
 
 #define LUX_CUDA_QUANT_MAGIC 0x4C515854u /* "LQXT" */
-#define LUX_CUDA_QUANT_VERSION 2u /* 2: symm_* and qmatmul_sharded_push appended */
+#define LUX_CUDA_QUANT_VERSION 3u /* 2: symm_* and qmatmul_sharded_push appended; 3: sum3, mul_rms_norm */
 #define LUX_CUDA_QMM_KERNEL_NAME "lux.qmm.affine"
 #define LUX_CUDA_NCCL_UID_BYTES 128
 
@@ -197,6 +197,18 @@ typedef struct lux_gpu_quant_vtbl {
     LuxBackendError (*qmatmul_sharded_push)(LuxCudaSymmBuffer* y_full, LuxBackendBuffer* x, LuxBackendBuffer* wq_local,
                                             LuxBackendBuffer* scales_local, LuxBackendBuffer* biases_local,
                                             int M, int K, int N_local, int bits, int group, LuxBackendDtype y_dtype);
+
+    /* --- the elementwise steps between the projections of a decode layer, bf16 (version >= 3) ---
+     * The inputs are column blocks of one row-major bf16 buffer with row stride `ld` elements, i.e. the
+     * output of a fused q|k|v or gate|up projection; fp32 math, one rounding to bf16 per result.
+     * sum3: out[r][c] = in[r][c] + in[r][cols+c] + in[r][2*cols+c]   (the add of op_add_f32,
+     * backend_plugin.h:120, applied twice).  mul_rms_norm: m = in[r][c] * in[r][cols+c] rounded to bf16
+     * (op_mul_f32, backend_plugin.h:122), then out = m * rsqrt(mean(m^2) + eps) per row (op_rms_norm_f32
+     * with unit weight, backend_plugin.h:178; kernels/cpu/tensor_ops.c:546-566). */
+    LuxBackendError (*sum3)(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t rows, size_t cols,
+                            size_t ld);
+    LuxBackendError (*mul_rms_norm)(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t rows,
+                                    size_t cols, size_t ld, float eps);
 } lux_gpu_quant_vtbl;
 
 /* Entry points exported with default visibility. */

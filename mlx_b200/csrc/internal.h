@@ -206,6 +206,10 @@ cudaError_t launch_quantize(const float* w, uint32_t* wq, void* scales, void* bi
                             int group, int sb_dtype, cudaStream_t stream);
 cudaError_t launch_rms_norm(const void* in, void* out, const float* weight, size_t rows, size_t dim, float eps,
                             int in_dtype, int out_dtype, cudaStream_t stream, bool overlap_prev = false);
+// decode-chain elementwise steps (bf16): sum of three column blocks; product of two column blocks + rms-norm
+cudaError_t launch_sum3(const void* in, void* out, size_t rows, size_t cols, size_t ld, cudaStream_t stream, bool overlap_prev = false);
+cudaError_t launch_mul_rms_norm(const void* in, void* out, size_t rows, size_t cols, size_t ld, float eps, cudaStream_t stream,
+                                bool overlap_prev = false);
 cudaError_t launch_gather_columns(const void* staging, void* y_full, int world, int M, int n_local, int elem_size,
                                   cudaStream_t stream);
 cudaError_t launch_flush(void* buf, size_t bytes, cudaStream_t stream);

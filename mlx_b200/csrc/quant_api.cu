@@ -253,6 +253,37 @@ LuxBackendError rms_norm(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBacken
     return LUX_BACKEND_OK;
 }
 
+LuxBackendError sum3(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t rows, size_t cols, size_t ld) {
+    Context* c = as_ctx(ctx);
+    Buffer *bi = as_buf(in), *bo = as_buf(out);
+    if (!c || !bi || !bo || ld < 3 * cols) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (rows && ((rows - 1) * ld + 3 * cols) * 2 > bi->bytes) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (rows * cols * 2 > bo->bytes) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lk(c->mu);
+    DeviceGuard g(c->dev->device());
+    LUX_CUDA_TRY(launch_sum3(bi->ptr, bo->ptr, rows, cols, ld, c->stream, chain_is_open(c)));
+    c->launches++;
+    note_chain_launch(c, bo->ptr, rows * cols * 2);
+    bi->last_stream = bo->last_stream = c->stream;
+    return LUX_BACKEND_OK;
+}
+
+LuxBackendError mul_rms_norm(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t rows, size_t cols,
+                             size_t ld, float eps) {
+    Context* c = as_ctx(ctx);
+    Buffer *bi = as_buf(in), *bo = as_buf(out);
+    if (!c || !bi || !bo || ld < 2 * cols) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (rows && ((rows - 1) * ld + 2 * cols) * 2 > bi->bytes) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (rows * cols * 2 > bo->bytes) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lk(c->mu);
+    DeviceGuard g(c->dev->device());
+    LUX_CUDA_TRY(launch_mul_rms_norm(bi->ptr, bo->ptr, rows, cols, ld, eps, c->stream, chain_is_open(c)));
+    c->launches++;
+    note_chain_launch(c, bo->ptr, rows * cols * 2);
+    bi->last_stream = bo->last_stream = c->stream;
+    return LUX_BACKEND_OK;
+}
+
 // --- buffer interop ---------------------------------------------------------
 void* buffer_device_ptr(LuxBackendContext*, LuxBackendBuffer* buf) {
     Buffer* b = as_buf(buf);
@@ -447,6 +478,8 @@ void fill_quant() {
     g_quant.graph_destroy = graph_destroy;
     fill_shard_entries(&g_quant);
     fill_symm_entries(&g_quant);
+    g_quant.sum3 = sum3;
+    g_quant.mul_rms_norm = mul_rms_norm;
 }
 
 }  // namespace

@@ -234,4 +234,92 @@ cudaError_t launch_rms_norm(const void* in, void* out, const float* weight, size
     return cudaLaunchKernelEx(&cfg, rms_norm_kernel, in, out, weight, dim, eps, in_dtype, out_dtype);
 }
 
+
+// ---- the two elementwise steps between the projections of a decode layer, bf16 in, bf16 out ------------
+// sum3:        out[r][c] = bf16( in[r][c] + in[r][cols + c] + in[r][2*cols + c] )          (fp32 adds, left to right)
+// mul_rms_norm: m[r][c]  = bf16( in[r][c] * in[r][cols + c] ),  out = rms_norm(m) as above (unit weight)
+// The inputs are column blocks of one row-major buffer with row stride ld (the output of a fused q|k|v or
+// gate|up projection).  One 1024-thread block per row; like rms_norm_kernel the kernels sit behind
+// griddepcontrol.wait, so they can be launched as programmatic dependents in a decode chain.
+__device__ __forceinline__ float bf16_at(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }
+
+__global__ void __launch_bounds__(kRmsThreads) sum3_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                                           size_t cols, size_t ld) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const __nv_bfloat16* row = in + (size_t)blockIdx.x * ld;
+    for (size_t c = threadIdx.x; c < cols; c += kRmsThreads) {
+        const float s = __fadd_rn(__fadd_rn(bf16_at(row, c), bf16_at(row, cols + c)), bf16_at(row, 2 * cols + c));
+        out[(size_t)blockIdx.x * cols + c] = __float2bfloat16_rn(s);
+    }
+}
+
+__global__ void __launch_bounds__(kRmsThreads) mul_rms_norm_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                                                   size_t cols, size_t ld, float eps) {
+    __shared__ float red[32];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const __nv_bfloat16* row = in + (size_t)blockIdx.x * ld;
+    const bool cached = cols <= (size_t)kRmsThreads * kRmsCache;
+    auto prod = [&](size_t c) { return __bfloat162float(__float2bfloat16_rn(__fmul_rn(bf16_at(row, c), bf16_at(row, cols + c)))); };
+    float v[kRmsCache];
+    float ss = 0.0f;
+    if (cached) {
+#pragma unroll
+        for (int j = 0; j < kRmsCache; j++) {
+            const size_t c = threadIdx.x + (size_t)j * kRmsThreads;
+            v[j] = c < cols ? prod(c) : 0.0f;
+            ss = fmaf(v[j], v[j], ss);
+        }
+    } else {
+        for (size_t c = threadIdx.x; c < cols; c += kRmsThreads) {
+            const float x = prod(c);
+            ss = fmaf(x, x, ss);
+        }
+    }
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = red[threadIdx.x];
+        for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (threadIdx.x == 0) red[0] = t;
+    }
+    __syncthreads();
+    const float inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(red[0], (float)cols), eps)));
+    if (cached) {
+#pragma unroll
+        for (int j = 0; j < kRmsCache; j++) {
+            const size_t c = threadIdx.x + (size_t)j * kRmsThreads;
+            if (c < cols) out[(size_t)blockIdx.x * cols + c] = __float2bfloat16_rn(__fmul_rn(v[j], inv));
+        }
+    } else {
+        for (size_t c = threadIdx.x; c < cols; c += kRmsThreads) out[(size_t)blockIdx.x * cols + c] = __float2bfloat16_rn(__fmul_rn(prod(c), inv));
+    }
+}
+
+static cudaError_t launch_row_kernel(const void* kern, void** args, size_t rows, cudaStream_t stream, bool overlap_prev) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)rows);
+    cfg.blockDim = dim3(kRmsThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap_prev ? 1 : 0;
+    return cudaLaunchKernelExC(&cfg, kern, args);
+}
+cudaError_t launch_sum3(const void* in, void* out, size_t rows, size_t cols, size_t ld, cudaStream_t stream, bool overlap_prev) {
+    if (!rows || !cols) return cudaSuccess;
+    void* args[] = {(void*)&in, (void*)&out, (void*)&cols, (void*)&ld};
+    return launch_row_kernel((const void*)sum3_kernel, args, rows, stream, overlap_prev);
+}
+cudaError_t launch_mul_rms_norm(const void* in, void* out, size_t rows, size_t cols, size_t ld, float eps, cudaStream_t stream,
+                                bool overlap_prev) {
+    if (!rows || !cols) return cudaSuccess;
+    void* args[] = {(void*)&in, (void*)&out, (void*)&cols, (void*)&ld, (void*)&eps};
+    return launch_row_kernel((const void*)mul_rms_norm_kernel, args, rows, stream, overlap_prev);
+}
+
 }  // namespace luxcuda

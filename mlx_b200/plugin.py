@@ -134,6 +134,9 @@ class QuantVtbl(C.Structure):  # include/lux_cuda_quant.h: lux_gpu_quant_vtbl
         ("symm_buffer", _fn(_vp, _vp)),
         ("symm_free", _fn(None, _vp)),
         ("qmatmul_sharded_push", _fn(_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i)),
+        # version >= 3
+        ("sum3", _fn(_i, _vp, _vp, _vp, _sz, _sz, _sz)),
+        ("mul_rms_norm", _fn(_i, _vp, _vp, _vp, _sz, _sz, _sz, C.c_float)),
     ]
 
 
@@ -359,6 +362,14 @@ class Context:
         self.plugin.check(self.plugin.quant.rms_norm(self.handle, src.handle, dst.handle,
                                                      weight.handle if weight else None, rows, dim, eps, in_dtype,
                                                      out_dtype), "rms_norm")
+
+    def sum3(self, src, dst, rows, cols, ld):
+        """dst[r][c] = src[r][c] + src[r][cols+c] + src[r][2*cols+c] (bf16, fp32 adds)."""
+        self.plugin.check(self.plugin.quant.sum3(self.handle, src.handle, dst.handle, rows, cols, ld), "sum3")
+
+    def mul_rms_norm(self, src, dst, rows, cols, ld, eps):
+        """dst = rms_norm(bf16(src[r][c] * src[r][cols+c])) per row (bf16, fp32 math)."""
+        self.plugin.check(self.plugin.quant.mul_rms_norm(self.handle, src.handle, dst.handle, rows, cols, ld, eps), "mul_rms_norm")
 
     def timer_record(self, slot):
         self.plugin.check(self.plugin.quant.timer_record(self.handle, slot), "timer_record")

@@ -19,7 +19,7 @@ _lib = None
 __all__ = [
     "F32", "BF16", "U32", "BASE_SEED", "build", "lib", "seed", "gen_q", "gen_uniform", "gen_normal",
     "to_bf16", "from_bf16", "unpack", "pack", "dequantize", "qmatmul_ref", "qmatmul_ref_rowcache",
-    "qmatmul_truth", "matmul_f32", "rms_norm", "quantize", "num_threads", "set_num_threads",
+    "qmatmul_truth", "matmul_f32", "rms_norm", "sum3", "mul_rms_norm", "quantize", "num_threads", "set_num_threads",
     "make_layer", "make_x", "rel_err", "REL_FLOOR", "alg_bytes", "TOL",
 ]
 
@@ -176,6 +176,22 @@ def rms_norm(x, eps=1e-6, weight=None, out_dtype=None):
     lib().orc_rms_norm(_p(x), _p(out), _p(w), C.c_int64(rows), C.c_int64(dim), C.c_float(eps),
                        C.c_int(_dt(x)), C.c_int(od))
     return out
+
+
+def sum3(qkv, cols):
+    """bf16(q + k + v) over the three column blocks of a bf16 [rows, >= 3*cols] array: fp32 adds, left to right,
+    one rounding (the elementwise add of the reference, src/cpu_backend.cpp:186-203, applied twice)."""
+    f = from_bf16(np.ascontiguousarray(qkv))
+    s = (f[:, :cols] + f[:, cols:2 * cols]).astype(np.float32) + f[:, 2 * cols:3 * cols]
+    return to_bf16(s.astype(np.float32))
+
+
+def mul_rms_norm(gu, cols, eps=1e-6):
+    """rms_norm(bf16(gate * up)) over the two column blocks of a bf16 [rows, >= 2*cols] array (elementwise
+    product of the reference, src/cpu_backend.cpp:224-241; rms-norm formula of kernels/cpu/tensor_ops.c:546-566)."""
+    f = from_bf16(np.ascontiguousarray(gu))
+    m = to_bf16((f[:, :cols] * f[:, cols:2 * cols]).astype(np.float32))
+    return rms_norm(m, eps=eps)
 
 
 def quantize(w, bits, group, sb_dtype):

@@ -61,7 +61,7 @@ def test_descriptor_and_layout():
 def test_quant_table():
     p = mlx_b200.Plugin(require_gpu=False)
     q = p.quant
-    assert q.magic == P.QUANT_MAGIC and q.version == 2 and q.size == C.sizeof(P.QuantVtbl)
+    assert q.magic == P.QUANT_MAGIC and q.version == 3 and q.size == C.sizeof(P.QuantVtbl)
     getter = p.lib.lux_gpu_cuda_quant_vtbl()
     assert C.addressof(getter.contents) == p.vtbl._reserved[0]
     for name, _ in P.QuantVtbl._fields_[4:]:

@@ -85,6 +85,76 @@ def test_back_to_back_launches_equal_synchronised_launches(ctx, oracle):
             h.free()
 
 
+def _bf16_ulps(a, b):
+    """Distance in bf16 steps between two bf16 arrays of equal sign pattern (raw uint16)."""
+    return np.abs(a.astype(np.int32) - b.astype(np.int32)).max()
+
+
+def test_full_width_layer_dataflow(ctx, oracle):
+    """The chain configuration's own dataflow on two layers at full width (4096 / 11008):
+    a = bf16(q + k + v); o = Wo a; r = rms_norm(o); m = rms_norm(bf16(gate(r) * up(r))); d = Wd m; h' = rms_norm(d),
+    q|k|v and gate|up as one launch each.  Every step is checked against the oracle on the input it actually saw;
+    then the same launches back to back (no synchronisation, programmatic dependent launches) must give the same bits."""
+    M, Dm, FFm, eps = 8, 4096, 11008, 1e-6
+    shapes = [("qkv", 3 * Dm, Dm), ("o", Dm, Dm), ("gateup", 2 * FFm, Dm), ("down", Dm, FFm)]
+    layers = []
+    for l in range(2):
+        ws = {}
+        for pi, (name, N, K) in enumerate(shapes):
+            wq, s, b = oracle.make_layer(N, K, 4, 64, oracle.BF16, config_id=5, layer=l, proj=pi)
+            ws[name] = (wq, s, b, ctx.upload(wq), ctx.upload(s), ctx.upload(b), N, K)
+        layers.append(ws)
+    x0 = oracle.make_x(M, Dm, oracle.BF16, config_id=5)
+    t = {n: ctx.empty((M, N), np.uint16) for n, N in (("h", Dm), ("qkv", 3 * Dm), ("a", Dm), ("o", Dm), ("r", Dm),
+                                                       ("gateup", 2 * FFm), ("m", FFm), ("d", Dm))}
+
+    def run(check):
+        hb = ctx.upload(x0)
+
+        def mm(ws, name, src, dst, src_shape):
+            wq, s, b, bw, bs, bb, N, K = ws[name]
+            ctx.qmatmul(src, bw, bs, bb, dst, M, K, N, 4, 64, BF16, BF16, BF16)
+            if check:
+                xin, y = src.to_host(src_shape, np.uint16), dst.to_host((M, N), np.uint16)
+                err, nerr = oracle.rel_err(y, oracle.qmatmul_truth(xin, wq, s, b, 4, 64))
+                assert err <= oracle.TOL[oracle.BF16], (name, err, nerr)
+
+        cur = hb
+        for ws in layers:
+            mm(ws, "qkv", cur, t["qkv"], (M, Dm))
+            ctx.sum3(t["qkv"], t["a"], M, Dm, 3 * Dm)
+            if check:  # elementwise, one rounding: bit-exact
+                assert np.array_equal(t["a"].to_host((M, Dm), np.uint16), oracle.sum3(t["qkv"].to_host((M, 3 * Dm), np.uint16), Dm))
+            mm(ws, "o", t["a"], t["o"], (M, Dm))
+            ctx.rms_norm(t["o"], t["r"], M, Dm, eps, BF16, BF16)
+            if check:  # the row sum of squares is accumulated in another order: one bf16 step
+                assert _bf16_ulps(t["r"].to_host((M, Dm), np.uint16), oracle.rms_norm(t["o"].to_host((M, Dm), np.uint16), eps=eps)) <= 1
+            mm(ws, "gateup", t["r"], t["gateup"], (M, Dm))
+            ctx.mul_rms_norm(t["gateup"], t["m"], M, FFm, 2 * FFm, eps)
+            if check:
+                assert _bf16_ulps(t["m"].to_host((M, FFm), np.uint16), oracle.mul_rms_norm(t["gateup"].to_host((M, 2 * FFm), np.uint16), FFm, eps=eps)) <= 1
+            mm(ws, "down", t["m"], t["d"], (M, FFm))
+            ctx.rms_norm(t["d"], t["h"], M, Dm, eps, BF16, BF16)
+            if check:
+                assert _bf16_ulps(t["h"].to_host((M, Dm), np.uint16), oracle.rms_norm(t["d"].to_host((M, Dm), np.uint16), eps=eps)) <= 1
+            cur = t["h"]
+        ctx.sync()
+        out = t["h"].to_host((M, Dm), np.uint16)
+        hb.free()
+        return out
+
+    ref = run(check=True)
+    assert np.isfinite(oracle.from_bf16(ref)).all()
+    for _ in range(3):
+        assert np.array_equal(run(check=False), ref)
+    for ws in layers:
+        for v in ws.values():
+            for h in v[3:6]:
+                h.free()
+    for b in t.values():
+        b.free()
+
+
 def test_weights_written_just_before_use(ctx, oracle):
     """A matmul right behind the kernel that produces its weights (quantize) must see them: such a
     launch is never chained to the decode launch before it."""

@@ -128,3 +128,23 @@ def test_generators_are_seeded(oracle):
     assert q.min() == 0 and q.max() == 15 and abs(q.mean() - 7.5) < 0.05
     assert oracle.alg_bytes(1, 4096, 11008, 4, 64, 2, 2, 2) == 25392640
     assert oracle.alg_bytes(1, 4096, 4096, 4, 64, 4, 4, 4) == 10518528
+
+
+def test_chain_elementwise_steps(oracle):
+    """The two elementwise steps of the chain configuration, restated with numpy in the oracle: checked against a
+    direct scalar evaluation on a small case."""
+    rng = np.random.default_rng(3)
+    rows, cols = 3, 40
+    a = oracle.to_bf16(rng.standard_normal((rows, 3 * cols)).astype(np.float32))
+    f = oracle.from_bf16(a)
+    want = np.empty((rows, cols), np.float32)
+    for r in range(rows):
+        for c in range(cols):
+            want[r, c] = np.float32(np.float32(f[r, c] + f[r, cols + c]) + f[r, 2 * cols + c])
+    assert np.array_equal(oracle.sum3(a, cols), oracle.to_bf16(want))
+    m = oracle.to_bf16((f[:, :cols] * f[:, cols:2 * cols]).astype(np.float32))
+    got = oracle.mul_rms_norm(a, cols, eps=1e-6)
+    assert np.array_equal(got, oracle.rms_norm(m, eps=1e-6))
+    mf = oracle.from_bf16(m).astype(np.float64)
+    ref = mf / np.sqrt((mf * mf).mean(axis=1, keepdims=True) + 1e-6)
+    assert np.abs(oracle.from_bf16(got) - ref).max() <= 2.0 ** -7 * np.abs(ref).max()
