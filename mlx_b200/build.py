@@ -18,7 +18,7 @@ OBJ_DIR = os.path.join(HERE, "lib", "obj")
 LIB_NAME = "libluxgpu_backend_cuda.so"
 LIB_PATH = os.path.join(LIB_DIR, LIB_NAME)
 
-SOURCES = ["plugin.cu", "device_state.cu", "ops_basic.cu", "quant_ops.cu", "quant_api.cu", "qmv_simt.cu",
+SOURCES = ["plugin.cu", "device_state.cu", "ops_basic.cu", "ops_tensor.cu", "quant_ops.cu", "quant_api.cu", "qmv_simt.cu",
            "qmv_mma.cu", "qmm_tc.cu", "shard.cu", "shard_push.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "--expt-relaxed-constexpr"]

@@ -197,6 +197,7 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, c
 // non-zero once a kernel gave up on one of its bounded waits since the last call (clears it)
 int take_device_error();
 int* device_error_word();  // where kernels raise it (null if the mapped word could not be set up)
+cudaError_t reset_peer_lost();    // on the current device: waits for peers are attempted again
 long long peer_wait_limit_ns();  // limit of a device-side wait for a peer rank (LUXCUDA_PEER_WAIT_MS, default 2000)
 
 cudaError_t launch_dequantize(const uint32_t* wq, const void* scales, const void* biases, void* out, int N, int K,
@@ -217,6 +218,14 @@ cudaError_t launch_flush(void* buf, size_t bytes, cudaStream_t stream);
 enum class BinOp { Add, Sub, Mul, Div };
 cudaError_t launch_binary_f32(BinOp op, const float* a, const float* b, float* out, size_t n, cudaStream_t stream);
 cudaError_t launch_matmul_f32(const float* a, const float* b, float* out, int M, int K, int N, cudaStream_t stream);
+// remaining fp32 tensor ops of the base vtable (ops_tensor.cu); unary op codes: 0 exp, 1 log, 2 sqrt, 3 neg, 4 abs,
+// 5 tanh, 6 sigmoid, 7 relu, 8 gelu, 9 copy; reduction op codes: 0 sum, 1 max, 2 min, 3 mean
+cudaError_t launch_unary_f32(int op, const float* in, float* out, size_t n, cudaStream_t stream);
+cudaError_t launch_transpose_f32(const float* in, float* out, int rows, int cols, cudaStream_t stream);
+cudaError_t launch_reduce_rows_f32(int op, const float* in, float* out, size_t outer, size_t inner, cudaStream_t stream);
+cudaError_t launch_softmax_f32(const float* in, float* out, size_t batch, size_t dim, bool log, cudaStream_t stream);
+cudaError_t launch_layer_norm_f32(const float* in, float* out, const float* gamma, const float* beta, size_t batch, size_t dim,
+                                  float eps, cudaStream_t stream);
 cudaError_t ntt_device(uint64_t* host_data, size_t n, uint64_t modulus, bool inverse, cudaStream_t stream);
 
 // extension table (quant_api.cu) and sharding (shard.cu)

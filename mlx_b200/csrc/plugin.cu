@@ -297,6 +297,106 @@ LuxBackendError op_matmul(LuxBackendContext* ctx, LuxBackendBuffer* a, LuxBacken
     return LUX_BACKEND_OK;
 }
 
+// ---------------------------------------------------------------------------
+// the remaining fp32 tensor ops (backend_plugin.h:130-178; forwarded by src/gpu_core.cpp:430-789)
+// ---------------------------------------------------------------------------
+// in -> out over n elements each (unary maps, copy)
+LuxBackendError unary(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t n, int op) {
+    Context* c = as_ctx(ctx);
+    Buffer *bi = as_buf(in), *bo = as_buf(out);
+    if (!c || !bi || !bo || n * sizeof(float) > bi->bytes || n * sizeof(float) > bo->bytes) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (!n) return LUX_BACKEND_OK;
+    DeviceGuard g(c->dev->device());
+    LUX_CUDA_TRY(launch_unary_f32(op, (const float*)bi->ptr, (float*)bo->ptr, n, c->stream));
+    c->launches++;
+    bi->last_stream = bo->last_stream = c->stream;
+    return LUX_BACKEND_OK;
+}
+#define LUXCUDA_UNARY(name, code) \
+    LuxBackendError name(LuxBackendContext* c, LuxBackendBuffer* i, LuxBackendBuffer* o, size_t n) { return unary(c, i, o, n, code); }
+LUXCUDA_UNARY(op_exp, 0)
+LUXCUDA_UNARY(op_log, 1)
+LUXCUDA_UNARY(op_sqrt, 2)
+LUXCUDA_UNARY(op_neg, 3)
+LUXCUDA_UNARY(op_abs, 4)
+LUXCUDA_UNARY(op_tanh, 5)
+LUXCUDA_UNARY(op_sigmoid, 6)
+LUXCUDA_UNARY(op_relu, 7)
+LUXCUDA_UNARY(op_gelu, 8)
+LUXCUDA_UNARY(op_copy, 9)
+#undef LUXCUDA_UNARY
+
+LuxBackendError op_transpose(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out, int rows, int cols) {
+    Context* c = as_ctx(ctx);
+    Buffer *bi = as_buf(in), *bo = as_buf(out);
+    if (!c || !bi || !bo || rows < 0 || cols < 0) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    const size_t bytes = (size_t)rows * cols * sizeof(float);
+    if (bytes > bi->bytes || bytes > bo->bytes) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    DeviceGuard g(c->dev->device());
+    LUX_CUDA_TRY(launch_transpose_f32((const float*)bi->ptr, (float*)bo->ptr, rows, cols, c->stream));
+    c->launches++;
+    bi->last_stream = bo->last_stream = c->stream;
+    return LUX_BACKEND_OK;
+}
+
+// outer rows of inner elements -> outer results
+LuxBackendError reduce_rows(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t outer, size_t inner, int op) {
+    Context* c = as_ctx(ctx);
+    Buffer *bi = as_buf(in), *bo = as_buf(out);
+    if (!c || !bi || !bo || outer * inner * sizeof(float) > bi->bytes || outer * sizeof(float) > bo->bytes)
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    DeviceGuard g(c->dev->device());
+    LUX_CUDA_TRY(launch_reduce_rows_f32(op, (const float*)bi->ptr, (float*)bo->ptr, outer, inner, c->stream));
+    c->launches++;
+    bi->last_stream = bo->last_stream = c->stream;
+    return LUX_BACKEND_OK;
+}
+LuxBackendError op_reduce_sum(LuxBackendContext* c, LuxBackendBuffer* i, LuxBackendBuffer* o, size_t n) { return reduce_rows(c, i, o, 1, n, 0); }
+LuxBackendError op_reduce_max(LuxBackendContext* c, LuxBackendBuffer* i, LuxBackendBuffer* o, size_t n) { return reduce_rows(c, i, o, 1, n, 1); }
+LuxBackendError op_reduce_min(LuxBackendContext* c, LuxBackendBuffer* i, LuxBackendBuffer* o, size_t n) { return reduce_rows(c, i, o, 1, n, 2); }
+LuxBackendError op_reduce_mean(LuxBackendContext* c, LuxBackendBuffer* i, LuxBackendBuffer* o, size_t n) { return reduce_rows(c, i, o, 1, n, 3); }
+LuxBackendError op_reduce_sum_axis(LuxBackendContext* c, LuxBackendBuffer* i, LuxBackendBuffer* o, size_t outer, size_t inner) {
+    return reduce_rows(c, i, o, outer, inner, 0);
+}
+LuxBackendError op_reduce_max_axis(LuxBackendContext* c, LuxBackendBuffer* i, LuxBackendBuffer* o, size_t outer, size_t inner) {
+    return reduce_rows(c, i, o, outer, inner, 1);
+}
+
+LuxBackendError softmax(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t batch, size_t dim, bool log) {
+    Context* c = as_ctx(ctx);
+    Buffer *bi = as_buf(in), *bo = as_buf(out);
+    if (!c || !bi || !bo || batch * dim * sizeof(float) > bi->bytes || batch * dim * sizeof(float) > bo->bytes)
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    DeviceGuard g(c->dev->device());
+    LUX_CUDA_TRY(launch_softmax_f32((const float*)bi->ptr, (float*)bo->ptr, batch, dim, log, c->stream));
+    c->launches++;
+    bi->last_stream = bo->last_stream = c->stream;
+    return LUX_BACKEND_OK;
+}
+LuxBackendError op_softmax(LuxBackendContext* c, LuxBackendBuffer* i, LuxBackendBuffer* o, size_t b, size_t d) { return softmax(c, i, o, b, d, false); }
+LuxBackendError op_log_softmax(LuxBackendContext* c, LuxBackendBuffer* i, LuxBackendBuffer* o, size_t b, size_t d) { return softmax(c, i, o, b, d, true); }
+
+LuxBackendError op_layer_norm(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out, LuxBackendBuffer* gamma,
+                              LuxBackendBuffer* beta, size_t batch, size_t dim, float eps) {
+    Context* c = as_ctx(ctx);
+    Buffer *bi = as_buf(in), *bo = as_buf(out), *bg = gamma ? as_buf(gamma) : nullptr, *bb = beta ? as_buf(beta) : nullptr;
+    if (!c || !bi || !bo || (gamma && !bg) || (beta && !bb)) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (batch * dim * sizeof(float) > bi->bytes || batch * dim * sizeof(float) > bo->bytes || (bg && dim * sizeof(float) > bg->bytes) ||
+        (bb && dim * sizeof(float) > bb->bytes))
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    DeviceGuard g(c->dev->device());
+    LUX_CUDA_TRY(launch_layer_norm_f32((const float*)bi->ptr, (float*)bo->ptr, bg ? (const float*)bg->ptr : nullptr,
+                                       bb ? (const float*)bb->ptr : nullptr, batch, dim, eps, c->stream));
+    c->launches++;
+    bi->last_stream = bo->last_stream = c->stream;
+    return LUX_BACKEND_OK;
+}
+// op_rms_norm_f32 (backend_plugin.h:178): the row kernel of the quantized path with fp32 in and out
+LuxBackendError op_rms_norm(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out, LuxBackendBuffer* weight,
+                            size_t batch, size_t dim, float eps) {
+    return quant_vtbl()->rms_norm(ctx, in, out, weight, batch, dim, eps, LUX_DTYPE_FLOAT32, LUX_DTYPE_FLOAT32);
+}
+
 LuxBackendError op_ntt(LuxBackendContext* ctx, uint64_t* data, size_t n, uint64_t modulus, bool inverse) {
     Context* c = as_ctx(ctx);
     if (!c || !data || n == 0 || (n & (n - 1)) != 0 || modulus < 2) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
@@ -334,6 +434,27 @@ void fill_vtbl() {
     g_vtbl.op_mul_f32 = op_mul;
     g_vtbl.op_div_f32 = op_div;
     g_vtbl.op_matmul_f32 = op_matmul;
+    g_vtbl.op_transpose_f32 = op_transpose;
+    g_vtbl.op_reduce_sum_f32 = op_reduce_sum;
+    g_vtbl.op_reduce_max_f32 = op_reduce_max;
+    g_vtbl.op_reduce_min_f32 = op_reduce_min;
+    g_vtbl.op_reduce_mean_f32 = op_reduce_mean;
+    g_vtbl.op_reduce_sum_axis_f32 = op_reduce_sum_axis;
+    g_vtbl.op_reduce_max_axis_f32 = op_reduce_max_axis;
+    g_vtbl.op_softmax_f32 = op_softmax;
+    g_vtbl.op_log_softmax_f32 = op_log_softmax;
+    g_vtbl.op_exp_f32 = op_exp;
+    g_vtbl.op_log_f32 = op_log;
+    g_vtbl.op_sqrt_f32 = op_sqrt;
+    g_vtbl.op_neg_f32 = op_neg;
+    g_vtbl.op_abs_f32 = op_abs;
+    g_vtbl.op_tanh_f32 = op_tanh;
+    g_vtbl.op_sigmoid_f32 = op_sigmoid;
+    g_vtbl.op_relu_f32 = op_relu;
+    g_vtbl.op_gelu_f32 = op_gelu;
+    g_vtbl.op_copy_f32 = op_copy;
+    g_vtbl.op_layer_norm_f32 = op_layer_norm;
+    g_vtbl.op_rms_norm_f32 = op_rms_norm;
     g_vtbl.op_ntt_forward = op_ntt_forward;
     g_vtbl.op_ntt_inverse = op_ntt_inverse;
     g_vtbl._reserved[0] = const_cast<lux_gpu_quant_vtbl*>(quant_vtbl());

@@ -723,6 +723,13 @@ cudaError_t launch_t(const Params& p, const Plan& pl, cudaStream_t stream, bool 
 
 }  // namespace
 
+// Clears, on the current device, the mark that a wait for a peer has run out (after which no launch waits for
+// peers any more).
+cudaError_t reset_peer_lost() {
+    const int zero = 0;
+    return cudaMemcpyToSymbol(g_peer_lost, &zero, sizeof(zero));
+}
+
 // Limit of a device-side wait for a peer rank, from LUXCUDA_PEER_WAIT_MS (default 2000 ms).
 long long peer_wait_limit_ns() {
     static const long long ns = [] {

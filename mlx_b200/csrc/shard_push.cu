@@ -46,11 +46,11 @@ static_assert(sizeof(Handle) == LUX_CUDA_SYMM_HANDLE_BYTES, "handle size");
 // are bounded (on a time-out the host-visible error word is raised and the kernel returns).
 // Flag words used: [kBarEpoch] this rank's count, [kBarSlot + q] the count announced by rank q.
 constexpr int kBarEpoch = 2, kBarSlot = 32;
-constexpr long long kBarWaitNs = 2000000000ll;
 struct BarrierArgs {
     uint32_t* flags[kMaxShardWorld];
     int world, me;
     int* error;
+    long long limit_ns;  // of a wait for a peer's count
 };
 __global__ void symm_barrier_kernel(const __grid_constant__ BarrierArgs a) {
     const int q = threadIdx.x;
@@ -69,7 +69,7 @@ __global__ void symm_barrier_kernel(const __grid_constant__ BarrierArgs a) {
             if ((int32_t)(v - e) >= 0) break;
             long long t1;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-            if (t1 - t0 > kBarWaitNs) {
+            if (t1 - t0 > a.limit_ns) {
                 ok = false;
                 break;
             }
@@ -156,6 +156,8 @@ LuxBackendError symm_attach(LuxCudaSymmBuffer* sb, const void* handles) {
         }
     }
     sb->attached = true;
+    // A rank that once gave up on a peer stops waiting for peers for good; a fresh attachment is a fresh start.
+    LUX_CUDA_TRY(reset_peer_lost());
     return LUX_BACKEND_OK;
 }
 
@@ -219,6 +221,7 @@ LuxBackendError qmatmul_sharded_push(LuxCudaSymmBuffer* sb, LuxBackendBuffer* x,
         ba.world = sb->world;
         ba.me = sb->rank;
         ba.error = device_error_word();
+        ba.limit_ns = peer_wait_limit_ns();
         for (int r = 0; r < kMaxShardWorld; r++) ba.flags[r] = nullptr;
         for (int r = 0; r < sb->world; r++) {
             sp.y[r] = static_cast<char*>(sb->peer_base[r]) + kHeader;

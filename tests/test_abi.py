@@ -100,6 +100,65 @@ def test_null_arguments_are_errors_not_crashes():
     v.destroy_context(None)
 
 
+def test_tensor_op_slots_are_filled_and_reject_null():
+    """The fp32 tensor ops the public API forwards (src/gpu_core.cpp:430-789) are all present; NULL handles are
+    errors, not crashes."""
+    p = mlx_b200.Plugin(require_gpu=False)
+    v = p.vtbl
+    un = ["op_reduce_sum_f32", "op_reduce_max_f32", "op_reduce_min_f32", "op_reduce_mean_f32", "op_exp_f32", "op_log_f32",
+          "op_sqrt_f32", "op_neg_f32", "op_abs_f32", "op_tanh_f32", "op_sigmoid_f32", "op_relu_f32", "op_gelu_f32", "op_copy_f32"]
+    for name in un:
+        assert getattr(v, name)(None, None, None, 4) == P.ERR_INVALID, name
+    assert v.op_transpose_f32(None, None, None, 2, 2) == P.ERR_INVALID
+    for name in ("op_reduce_sum_axis_f32", "op_reduce_max_axis_f32", "op_softmax_f32", "op_log_softmax_f32"):
+        assert getattr(v, name)(None, None, None, 2, 2) == P.ERR_INVALID, name
+    assert v.op_layer_norm_f32(None, None, None, None, None, 1, 4, 1e-5) == P.ERR_INVALID
+    assert v.op_rms_norm_f32(None, None, None, None, 1, 4, 1e-5) == P.ERR_INVALID
+    assert p.quant.sum3(None, None, None, 1, 4, 12) == P.ERR_INVALID
+    assert p.quant.mul_rms_norm(None, None, None, 1, 4, 8, 1e-6) == P.ERR_INVALID
+
+
+STUB_SRC = r"""
+#include <stdint.h>
+#include <stdbool.h>
+/* layout of lux_gpu_backend_desc (include/lux/gpu/backend_plugin.h:388-394) */
+typedef struct { uint32_t abi_version; const char* backend_name; const char* backend_version; uint32_t capabilities; const void* vtbl; } desc_t;
+static void* slots[64];
+__attribute__((visibility("default"))) bool lux_gpu_backend_init(desc_t* out) {
+    out->abi_version = 3; out->backend_name = "cuda"; out->backend_version = "stub"; out->capabilities = 0; out->vtbl = slots;
+    return true;
+}
+"""
+
+
+def test_reference_loader_rejects_a_plugin_of_another_abi_version(tmp_path):
+    """The reference loader checks the descriptor's ABI version (src/plugin_loader.hpp:213-223): a library named
+    like this plugin that reports version 3 is closed again with a message, and the core falls back to its CPU
+    backend.  (Host-side fault test: no GPU involved.)"""
+    import subprocess
+    import sys
+    from oracle import refcore
+    if not refcore.available():
+        pytest.skip("compiled reference core not present")
+    src = tmp_path / "stub.c"
+    src.write_text(STUB_SRC)
+    lib = tmp_path / "libluxgpu_backend_cuda.so"
+    subprocess.run(["/usr/bin/gcc", "-shared", "-fPIC", "-o", str(lib), str(src)], check=True)
+    code = ("import sys; sys.path.insert(0, %r)\n"
+            "from oracle import refcore\n"
+            "r = refcore.RefCore(backend=refcore.BACKEND_CUDA)\n"
+            "print('BACKEND', r.backend_name)\n"
+            "import numpy as np\n"
+            "print('MATMUL', r.matmul(np.array([[1,2],[3,4]], np.float32), np.array([[5,6],[7,8]], np.float32)).ravel().tolist())\n"
+            "r.close()\n") % ROOT
+    out = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, LUX_GPU_BACKEND_PATH=str(tmp_path)),
+                         capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    assert "has ABI version 3, expected 2" in out.stderr
+    assert "BACKEND cpu" in out.stdout
+    assert "MATMUL [19.0, 22.0, 43.0, 50.0]" in out.stdout
+
+
 def test_no_gpu_means_unavailable_not_fallback():
     import torch
     p = mlx_b200.Plugin(require_gpu=False)

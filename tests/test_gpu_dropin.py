@@ -118,3 +118,17 @@ def test_reference_public_api_on_the_plugin(oracle):
         assert np.array_equal(rc.binary("add", A, A), A + A)
     finally:
         rc.close()
+
+
+def test_allocation_failure_is_a_null_buffer_with_a_message(plugin, ctx):
+    """A request beyond the device's memory comes back as NULL (the reference's convention for a failed
+    buffer_alloc, src/cpu_backend.cpp:121-131) with an out-of-memory text, and the context stays usable."""
+    info = ctx.device_info()
+    too_much = int(info.memory_total) * 4 if getattr(info, "memory_total", 0) else (1 << 42)
+    h = plugin.vtbl.buffer_alloc(ctx.handle, too_much)
+    assert not h
+    msg = plugin.last_error().lower()
+    assert "memory" in msg, msg
+    b = ctx.upload(np.arange(8, dtype=np.float32))   # still works
+    assert np.array_equal(b.to_host(), np.arange(8, dtype=np.float32))
+    b.free()

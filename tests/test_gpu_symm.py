@@ -70,3 +70,55 @@ def test_ranks_bit_exact_including_split_k(plugin):
            "--master-port", "29537", os.path.join(ROOT, "tests", "symm_ranks_check.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT)
     assert r.returncode == 0 and "SYMM_RANKS_OK" in r.stdout, (r.stdout[-1500:], r.stderr[-1500:])
+
+
+WAIT_RUNS_OUT = r"""
+import sys
+sys.path.insert(0, %r)
+import numpy as np
+import mlx_b200
+from mlx_b200 import BF16, BackendError
+from mlx_b200 import plugin as P
+import oracle as O
+plugin = mlx_b200.Plugin(require_gpu=True)
+ctx = plugin.context(0)
+M, K, Nl = %d, 1024, 128
+wq, s, b = O.make_layer(Nl, K, 4, 64, O.BF16, config_id=8)
+x = O.make_x(M, K, O.BF16, config_id=8)
+bx, bw, bs, bb = ctx.upload(x), ctx.upload(wq), ctx.upload(s), ctx.upload(b)
+# rank 0 of a world of two; "rank 1" is a second buffer on the same GPU on which nothing is ever launched
+mine, other = P.SymmBuffer(ctx, 0, 2, (M, 2 * Nl), np.uint16), P.SymmBuffer(ctx, 1, 2, (M, 2 * Nl), np.uint16)
+hs = [mine.export(), other.export()]
+mine.attach(hs)
+other.attach(hs)
+before = mine.to_host().copy()
+mine.qmatmul(bx, bw, bs, bb, M, K, Nl, 4, 64, BF16)      # returns: the wait happens on the device
+try:
+    ctx.sync()
+    print("NO_ERROR")
+except BackendError as e:
+    print("SYNC_ERROR", e)
+after = mine.to_host()
+print("PEER_COLUMNS_UNTOUCHED", bool(np.array_equal(after[:, Nl:], before[:, Nl:])))
+ctx.sync()                                                  # the context stays usable
+y = ctx.empty((M, Nl), np.uint16)
+ctx.qmatmul(bx, bw, bs, bb, y, M, K, Nl, 4, 64, BF16, BF16, BF16)
+err, _ = O.rel_err(y.to_host(), O.qmatmul_truth(x, wq, s, b, 4, 64))
+print("STILL_WORKS", bool(err <= 1e-2))
+"""
+
+
+@pytest.mark.parametrize("M", [8, 64])
+def test_a_wait_for_a_peer_runs_out_and_is_reported(M):
+    """Bounded device-side waits, exercised the harmless way: the 'peer' is a buffer nobody launches on, the limit
+    is 50 ms (LUXCUDA_PEER_WAIT_MS).  The kernel gives up by itself, the next sync reports INTERNAL, nothing faults
+    or hangs, and the context keeps working.  M = 8: the decode kernel's wait for the peer's ready word; M = 64: the
+    rank barrier around the prefill GEMM.  In a process of its own: having given up once, a process stops waiting
+    for peers."""
+    env = dict(os.environ, LUXCUDA_PEER_WAIT_MS="50")
+    r = subprocess.run([sys.executable, "-c", WAIT_RUNS_OUT % (ROOT, M)], capture_output=True, text=True, timeout=120, env=env, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "SYNC_ERROR" in r.stdout and "NO_ERROR" not in r.stdout, r.stdout
+    assert "STILL_WORKS True" in r.stdout, r.stdout
+    if M <= 16:
+        assert "PEER_COLUMNS_UNTOUCHED True" in r.stdout, r.stdout
