@@ -42,6 +42,7 @@
 #define LUX_CUDA_QUANT_H
 
 #include "lux/gpu/backend_plugin.h"
+#include "lux/gpu/kernel_loader.h"
 
 #ifdef __cplusplus
 extern "C" {
@@ -241,6 +242,13 @@ LUX_GPU_BACKEND_EXPORT LuxBackendError lux_gpu_cuda_qmatmul_decode_noalloc(
     LuxBackendContext* ctx, LuxBackendBuffer* x, LuxBackendBuffer* wq, LuxBackendBuffer* scales,
     LuxBackendBuffer* biases, LuxBackendBuffer* y, int M, int K, int N, int bits, int group,
     LuxBackendDtype y_dtype);
+/* The reference's hook for a backend's table of built-in kernels: the core declares it as a weak function that
+ * returns NULL (src/kernel_loader.cpp:191-210) and looks kernels up in whatever a backend linked into the same
+ * image returns (lux_kernel_registry_get / _find, include/lux/gpu/kernel_loader.h:84-97).  The plugin's table
+ * lists the kernel variants behind "lux.qmm.affine" (entry_point = the variant: bits, rows of x it takes) and the
+ * helper kernels; they are compiled into the library (source and binary are NULL: nothing to compile at run
+ * time), so the table is a directory of names, in the reference's own format. */
+LUX_GPU_BACKEND_EXPORT const LuxKernelRegistry* lux_kernel_registry_cuda_get(void);
 /* Last error text of the calling thread ("" if none). */
 LUX_GPU_BACKEND_EXPORT const char* lux_gpu_cuda_last_error(void);
 

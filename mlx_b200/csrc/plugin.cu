@@ -460,9 +460,30 @@ void fill_vtbl() {
     g_vtbl._reserved[0] = const_cast<lux_gpu_quant_vtbl*>(quant_vtbl());
 }
 
+// Directory of the kernels compiled into the library, in the format of the reference's kernel registry
+// (include/lux/gpu/kernel_loader.h:70-90).  name = kernel family, entry_point = variant.
+const LuxEmbeddedKernel g_kernels[] = {
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<4,m8>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},   // decode GEMV, 4-bit, M <= 8
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<4,m16>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},  // decode GEMV, 4-bit, M <= 16
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<8,m8>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<8,m16>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<4>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},       // prefill GEMM (tcgen05), M > 16
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<8>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_simt", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},        // fp32 activations, odd K
+    {"lux.qmm.dequantize", "dequantize", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {"lux.qmm.unpack", "unpack", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {"lux.qmm.quantize", "quantize", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {"lux.rms_norm", "rms_norm", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {"lux.sum3", "sum3", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {"lux.mul_rms_norm", "mul_rms_norm", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+};
+const LuxKernelRegistry g_registry = {"cuda", g_kernels, sizeof(g_kernels) / sizeof(g_kernels[0])};
+
 }  // namespace
 
 extern "C" {
+
+LUX_GPU_BACKEND_EXPORT const LuxKernelRegistry* lux_kernel_registry_cuda_get(void) { return &g_registry; }
 
 LUX_GPU_BACKEND_EXPORT bool lux_gpu_backend_init(lux_gpu_backend_desc* out) {
     if (!out) return false;

@@ -159,6 +159,26 @@ def test_reference_loader_rejects_a_plugin_of_another_abi_version(tmp_path):
     assert "MATMUL [19.0, 22.0, 43.0, 50.0]" in out.stdout
 
 
+def test_kernel_registry_hook():
+    """lux_kernel_registry_cuda_get (the reference's weak hook, src/kernel_loader.cpp:191-210) returns a table in
+    the reference's format (include/lux/gpu/kernel_loader.h:70-90) that names every quantized-matmul variant."""
+    class Embedded(C.Structure):
+        _fields_ = [("name", C.c_char_p), ("entry_point", C.c_char_p), ("lang", C.c_int), ("source", C.c_char_p),
+                    ("source_len", C.c_size_t), ("binary", C.c_void_p), ("binary_len", C.c_size_t)]
+
+    class Registry(C.Structure):
+        _fields_ = [("backend", C.c_char_p), ("kernels", C.POINTER(Embedded)), ("count", C.c_size_t)]
+
+    lib = P.load_library()
+    lib.lux_kernel_registry_cuda_get.restype = C.POINTER(Registry)
+    reg = lib.lux_kernel_registry_cuda_get().contents
+    assert reg.backend == b"cuda" and reg.count >= 7
+    entries = [(reg.kernels[i].name.decode(), reg.kernels[i].entry_point.decode(), reg.kernels[i].lang) for i in range(reg.count)]
+    variants = {e for n, e, _ in entries if n == "lux.qmm.affine"}
+    assert {"qmv_mma<4,m8>", "qmv_mma<4,m16>", "qmv_mma<8,m8>", "qmv_mma<8,m16>", "qmm_tc<4>", "qmm_tc<8>", "qmv_simt"} <= variants
+    assert all(lang == 1 for _, _, lang in entries)  # LUX_KERNEL_LANG_CUDA
+
+
 def test_no_gpu_means_unavailable_not_fallback():
     import torch
     p = mlx_b200.Plugin(require_gpu=False)
