@@ -37,8 +37,8 @@ import time
 
 import numpy as np
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one qmv_mma launch (M=1) of this workload, from the ncu
-# capture summarised in profiles/qmv_mma_decode_gemv_4bit_K4096_N11008.md
+# dram__bytes_read.sum + dram__bytes_write.sum of one qmv_mma launch (M=1) of this workload, from an ncu capture
+# of `bench.py --kernel-only --no-graph` (counters cannot be read inside the timed run)
 NCU_TRAFFIC_BYTES = 25449472.0
 SWEEPS_PER_GRAPH = 5  # sweeps (of 4 x 12 launches) recorded in the CUDA graph the timed step replays
 
@@ -59,6 +59,13 @@ def measured_peaks():
         d = json.load(open(p))
         return d, "measured"
     return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def shared_config():
+    """The workload as both arms (GPU, CPU reference) name it."""
+    return {"workload": "decode_gemv_sweep", "M": list(M_SWEEP), "K": K_DEC, "N": N_DEC, "bits": BITS, "group": GROUP,
+            "l2": f"GPU arm: inputs larger than L2 ({R_SETS} rotating weight sets = {R_SETS * alg_bytes(1) / 1e6:.0f} MB, each launch "
+                  "reads a set last touched 11 launches earlier); CPU arm: one layer, host caches as they fall"}
 
 
 def alg_bytes(M, K=K_DEC, N=N_DEC):
@@ -155,7 +162,7 @@ def run_reference(args, rank):
         "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
         "warmup": args.warmup, "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "decode_gemv_sweep", "M": list(M_SWEEP), "K": K_DEC, "N": N_DEC, "bits": BITS, "group": GROUP},
+        "config": shared_config(),
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": O.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference has no quantized matmul; this is its CPU backend's matmul loop "
@@ -163,7 +170,52 @@ def run_reference(args, rank):
     }))
 
 
-def prefill_legs(ctx, O, BF16, peaks):
+def cpu_reference_config_leg(ctx, O):
+    """The CPU-backend reference configuration (x fp32 [1,4096]; W [4096,4096] 4-bit g64, fp32 scales, biases =
+    -8*scale + N(0,1e-3); y fp32): the GPU fp32 path (qmv_simt) and the CPU restatement in the reference backend's
+    loop style, on the same inputs, each checked against the fp64 truth before it is timed."""
+    from mlx_b200 import F32
+    M, K, N, bits, group = 1, 4096, 4096, 4, 64
+    wq, s, b = O.make_layer(N, K, bits, group, O.F32, config_id=1, bias_noise=1e-3)
+    x = O.make_x(M, K, O.F32, config_id=1)
+    truth = O.qmatmul_truth(x, wq, s, b, bits, group)
+    nbytes = N * K * bits // 8 + 2 * (N * K // group) * 4 + M * K * 4 + M * N * 4
+    bx, bw, bs, bb = ctx.upload(x), ctx.upload(wq), ctx.upload(s), ctx.upload(b)
+    by = ctx.empty((M, N), np.float32)
+    ctx.qmatmul(bx, bw, bs, bb, by, M, K, N, bits, group, F32, F32, F32)
+    err_gpu, _ = O.rel_err(by.to_host(), truth)
+    for _ in range(5):
+        ctx.qmatmul(bx, bw, bs, bb, by, M, K, N, bits, group, F32, F32, F32)
+    ctx.sync()
+    iters = 50
+    ctx.timer_record(12)
+    for _ in range(iters):
+        ctx.qmatmul(bx, bw, bs, bb, by, M, K, N, bits, group, F32, F32, F32)
+    ctx.timer_record(13)
+    us_gpu = ctx.timer_elapsed_ms(12, 13) * 1e3 / iters
+    kern = ctx.last_kernel()
+    for h in (bx, bw, bs, bb, by):
+        h.free()
+    y_cpu = O.qmatmul_ref(x, wq, s, b, bits, group)
+    err_cpu, _ = O.rel_err(y_cpu, truth)
+    for _ in range(3):
+        O.qmatmul_ref(x, wq, s, b, bits, group)
+    ts = []
+    for _ in range(10):
+        t0 = time.perf_counter()
+        O.qmatmul_ref(x, wq, s, b, bits, group)
+        ts.append(time.perf_counter() - t0)
+    us_cpu = statistics.median(ts) * 1e6
+    return {"workload": "x fp32 [1,4096], W [4096,4096] 4-bit g64 fp32 scales/biases, y fp32", "algorithmic_bytes": nbytes,
+            "gpu": {"kernel": kern, "us_per_call": us_gpu, "GBps": nbytes / us_gpu / 1e3, "max_rel_err": err_gpu,
+                    "note": "weights L2-resident (8 MB): the same layer is launched back to back"},
+            "cpu": {"us_per_call": us_cpu, "GBps": nbytes / us_cpu / 1e3, "cores": O.num_threads(), "max_rel_err": err_cpu,
+                    "how": "oracle port in the reference CPU backend's loop style (src/cpu_backend.cpp:243-266), OpenMP over outputs, "
+                           "median of 10 after 3 warm-up calls"},
+            "tolerance": O.TOL[O.F32]}
+
+
+def prefill_legs(ctx, O, BF16, peaks, only=None):
     """Tensor-bound legs (the prefill and the 8-bit large-GEMM configurations at one GPU): TFLOP/s = 2*M*N*K / device time.
     Rotating input sets keep every launch's operands colder than L2 capacity in total."""
     out = {}
@@ -171,6 +223,8 @@ def prefill_legs(ctx, O, BF16, peaks):
         "prefill_4bit_M2048_K4096_N4096": (2048, 4096, 4096, 4, 64, 4, 10),
         "gemm_8bit_M512_K8192_N28672": (512, 8192, 28672, 8, 128, 2, 5),
     }.items():
+        if only and name != only:
+            continue
         sets = []
         for r in range(R):
             wq, s, b = O.make_layer(N, K, bits, group, O.BF16, config_id=3 if bits == 4 else 4, layer=r)
@@ -349,8 +403,14 @@ def gemm_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks, use_push):
         staging.free()
     tf = 2.0 * M * N * K / ms / 1e9
     how = "tiles stored into every rank's y from the GEMM epilogue" if use_push else "NCCL all-gather + interleave"
+    # the same layer unsharded on one GPU (rank 0, the other ranks wait): T1 of the efficiency T1 / (G * T_G)
+    t1 = None
+    if rank == 0:
+        t1 = prefill_legs(ctx, O, BF16, peaks, only="gemm_8bit_M512_K8192_N28672")["gemm_8bit_M512_K8192_N28672"]["us_per_launch"]
+    dist.barrier()
     return {"workload": f"M=512 K=8192 N=28672 8-bit g128, N column-sharded over {world} GPUs, {how}",
-            "scaling": "strong", "us_per_call": ms * 1e3, "TFLOPS_aggregate": tf,
+            "scaling": "strong", "us_per_call": ms * 1e3, "TFLOPS_aggregate": tf, "us_per_call_one_gpu": t1,
+            "efficiency": (t1 / (world * ms * 1e3)) if t1 else None,
             "allgather_bytes_per_rank": M * N * 2, "verified": verified}
 
 
@@ -385,20 +445,20 @@ def chain_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks):
     dist.barrier()
     h0 = O.make_x(M, D, O.BF16, config_id=5)
     h = ctx.upload(h0)
-    a = ctx.upload(O.make_x(M, D, O.BF16, config_id=5, tag=1))
-    gu = ctx.upload(O.make_x(M, FF, O.BF16, config_id=5, tag=2))
+    a = ctx.empty((M, D), np.uint16)
     r_buf, m_buf = ctx.empty((M, D), np.uint16), ctx.empty((M, FF), np.uint16)
 
     def mm(ws, name, src):
         bw, bs, bb, nl, K = ws[name]
         symm[name].qmatmul(src, bw, bs, bb, M, K, nl, BITS, GROUP, BF16)
 
-    def layer(ws):
+    def layer(ws):  # the dataflow of chain_leg; the elementwise steps run on every rank on the gathered rows
         mm(ws, "qkv", h)
+        ctx.sum3(symm["qkv"].buffer, a, M, D, 3 * D)
         mm(ws, "o", a)
         ctx.rms_norm(symm["o"].buffer, r_buf, M, D, 1e-6, BF16, BF16)
         mm(ws, "gateup", r_buf)
-        ctx.rms_norm(gu, m_buf, M, FF, 1e-6, BF16, BF16)
+        ctx.mul_rms_norm(symm["gateup"].buffer, m_buf, M, FF, 2 * FF, 1e-6)
         mm(ws, "down", m_buf)
         ctx.rms_norm(symm["down"].buffer, h, M, D, 1e-6, BF16, BF16)
 
@@ -453,11 +513,18 @@ def chain_sharded_leg(ctx, plugin, dist, rank, world, O, BF16, peaks):
     for ws in layers:
         for (bw, bs, bb, _, _) in ws.values():
             bw.free(); bs.free(); bb.free()
-    for b in (h, a, gu, r_buf, m_buf):
+    for b in (h, a, r_buf, m_buf):
         b.free()
-    return {"workload": f"32 layers x (qkv, o, gate/up, down) + 3 rms-norms, M=8, every projection column-sharded over {world} GPUs",
-            "scaling": "strong", "ms_per_step": ms, "launches_per_step": L * 7, "algorithmic_GB": nbytes / 1e9,
-            "GBps_aggregate": nbytes / ms / 1e6, "verified": verified}
+    # the same chain on one GPU (rank 0, the other ranks wait): T1 of the efficiency T1 / (G * T_G)
+    t1 = None
+    if rank == 0:
+        t1 = chain_leg(ctx, O, BF16, peaks)["ms_per_step"]
+    dist.barrier()
+    return {"workload": f"32 layers x (qkv, sum3, o, rms-norm, gate/up, mul+rms-norm, down, rms-norm), M=8, every projection "
+                        f"column-sharded over {world} GPUs, full dataflow",
+            "scaling": "strong", "ms_per_step": ms, "launches_per_step": L * 8, "algorithmic_GB": nbytes / 1e9,
+            "GBps_aggregate": nbytes / ms / 1e6, "ms_per_step_one_gpu": t1,
+            "efficiency": (t1 / (world * ms)) if t1 else None, "verified": verified}
 
 
 # ---------------------------------------------------------------------------
@@ -642,11 +709,13 @@ def run_ours(args, rank, world):
                 else:
                     for r in range(R_SETS):
                         launch(M, r)
+        launch(M, 0)  # (eagerly once: a graph replay does not update the context's "last kernel")
+        kernel_name = ctx.last_kernel()
         run_m()
         ms = timed(run_m, 2, 3)
         n_launch = reps_m * R_SETS
         per_m[M] = {"us_per_launch": ms * 1e3 / n_launch, "GBps": alg_bytes(M) * world * n_launch / ms / 1e6,
-                    "kernel": ctx.last_kernel()}
+                    "kernel": kernel_name}
 
     sweep_bytes = sum(alg_bytes(M) for M in M_SWEEP) * R_SETS * world
     total_bytes = sweep_bytes * args.reps * args.steps
@@ -685,6 +754,7 @@ def run_ours(args, rank, world):
     d2h = sum(M * n_total * 2 for M in M_SWEEP) * R_SETS * e2e_reps
 
     peaks, which = measured_peaks()
+    cpu_ref_config = cpu_reference_config_leg(ctx, O) if (world == 1 and not args.kernel_only) else None
     prefill = prefill_legs(ctx, O, BF16, peaks) if (world == 1 and not args.kernel_only) else None
     chain = chain_leg(ctx, O, BF16, peaks) if (world == 1 and not args.kernel_only) else None
     # the sharded configurations proper (strong scaling), after the sweep; a failure here must not lose the sweep
@@ -719,9 +789,10 @@ def run_ours(args, rank, world):
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "decode_gemv_sweep" if world == 1 else "decode_gemv_sweep_column_sharded_allgather",
-                   "M": list(M_SWEEP), "K": K_DEC, "N": N_DEC, "N_total": n_total, "bits": BITS, "group": GROUP,
-                   "weight_sets": R_SETS, "sweeps_per_step": args.reps, "cuda_graph": use_graph,
+        "config": shared_config(),
+        "run": {"layout": "one GPU" if world == 1 else f"weak scaling: each of {world} ranks holds its own {N_DEC}-column slice of a "
+                          f"{n_total}-column layer and every rank ends with the whole y (all-gather of output slices)",
+                   "N_total": n_total, "weight_sets": R_SETS, "sweeps_per_step": args.reps, "cuda_graph": use_graph,
                    "launches_per_graph": SWEEPS_PER_GRAPH * len(M_SWEEP) * R_SETS if use_graph else None,
                    "allgather": None if world == 1 else ("peer stores from the decode kernel (one launch per call)" if use_push
                                                          else "NCCL all-gather + interleave pass"),
@@ -735,6 +806,7 @@ def run_ours(args, rank, world):
                      "traffic": args.traffic_bytes, "traffic_unit": "bytes per launch (ncu dram read+write, M=1 launch)",
                      "traffic_over_algorithmic": args.traffic_bytes / alg_bytes(1) if args.traffic_bytes else None},
         "per_M": {str(M): per_m[M] for M in M_SWEEP},
+        "cpu_reference_config": cpu_ref_config,
         "prefill": prefill,
         "chain": chain,
         "chain_sharded": chain_sharded,
@@ -771,7 +843,7 @@ def main():
     ap.add_argument("--chain-only", action="store_true", help="run only the quantized-linear chain leg")
     ap.add_argument("--prefill-only", action="store_true", help="run only the tensor-bound legs (short, for profiling)")
     ap.add_argument("--traffic-bytes", type=float, default=NCU_TRAFFIC_BYTES,
-                    help="dram bytes per launch from the committed ncu summary (profiles/), echoed into roofline.traffic")
+                    help="dram bytes per launch of the dominant kernel from an ncu capture, echoed into roofline.traffic")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
