@@ -469,41 +469,52 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
     // The warp's tasks, in order: for each batch of tb tiles, for each of its k-blocks, the tiles of the
     // batch ("run": they share the x fragments of that k-block).  D-1 tasks are in flight while one is
     // computed; the fetch runs that far ahead of the computation, one commit group per task (empty past the end).
-    const size_t half_tile = 8 * row_bytes;
+    const size_t half_tile = 8 * row_bytes, tile_stride = 16 * row_bytes;
     int f_b0 = rt_lo, f_kb = kb_lo + warp, f_rt = rt_lo;  // the task fetched next
     uint32_t f_dst = ring_lo;                             // and the stage it goes to
+    // this lane's sources of that task: rows g and g+8 of the tile (its 16-byte pieces t and t+4 of the k-block),
+    // the scales (lanes 0-15) or biases (16-31) of row lane%16.  Inside a run they move by constant strides.
+    const unsigned char* f_p0 = nullptr;
+    const unsigned char* f_p1 = nullptr;
+    const __nv_bfloat16* f_sb = nullptr;
+    auto fetch_point = [&]() {
+        if (f_rt != tail_tile) {
+            f_p0 = wbase + (size_t)(f_rt * 16 + g) * row_bytes + f_kb * 128;
+            f_p1 = f_p0 + half_tile;
+            f_sb = sb_src + ((f_rt * 16 + (lane & 15)) * gpr + f_kb * gpk);
+        } else {  // rows past N read row N-1 (their results are never stored)
+            const int n0 = f_rt * 16;
+            f_p0 = wbase + (size_t)min(n0 + g, p.N - 1) * row_bytes + f_kb * 128;
+            f_p1 = wbase + (size_t)min(n0 + g + 8, p.N - 1) * row_bytes + f_kb * 128;
+            f_sb = sb_src + (min(n0 + (lane & 15), p.N - 1) * gpr + f_kb * gpk);
+        }
+    };
+    if (has_work) fetch_point();
     auto fetch_next = [&]() {
         if (has_work && f_b0 < rt_hi) {
-            const int rt = f_rt, kb = f_kb;
-            const unsigned char* p0;
-            const unsigned char* p1;
-            int elem;
-            if (rt != tail_tile) {
-                p0 = wbase + (size_t)(rt * 16 + g) * row_bytes + kb * 128;
-                p1 = p0 + half_tile;
-                elem = (rt * 16 + (lane & 15)) * gpr + kb * gpk;
-            } else {  // rows past N read row N-1 (their results are never stored)
-                const int n0 = rt * 16;
-                p0 = wbase + (size_t)min(n0 + g, p.N - 1) * row_bytes + kb * 128;
-                p1 = wbase + (size_t)min(n0 + g + 8, p.N - 1) * row_bytes + kb * 128;
-                elem = min(n0 + (lane & 15), p.N - 1) * gpr + kb * gpk;
-            }
-            cp_async16(f_dst, p0);
-            cp_async16(f_dst + 512, p0 + 64);
-            cp_async16(f_dst + 1024, p1);
-            cp_async16(f_dst + 1536, p1 + 64);
-            if (p.sb_bytes == 16) cp_async16(f_dst + 2048, sb_src + elem);
-            else if (p.sb_bytes == 8) cp_async8(f_dst + 2048, sb_src + elem);
-            else cp_async4(f_dst + 2048, sb_src + (p.sb_bytes == 2 ? (elem & ~1) : elem));  // a lone scale travels with its neighbour
+            cp_async16(f_dst, f_p0);
+            cp_async16(f_dst + 512, f_p0 + 64);
+            cp_async16(f_dst + 1024, f_p1);
+            cp_async16(f_dst + 1536, f_p1 + 64);
+            if (p.sb_bytes == 16) cp_async16(f_dst + 2048, f_sb);
+            else if (p.sb_bytes == 8) cp_async8(f_dst + 2048, f_sb);
+            else cp_async4(f_dst + 2048, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(f_sb) & ~uintptr_t(3)));  // a lone scale travels with its neighbour
             // on to the task after it
             f_dst = f_dst + kStageBytes == ring_lo + D * kStageBytes ? ring_lo : f_dst + kStageBytes;
-            if (++f_rt == min(f_b0 + tb, rt_hi)) {
+            if (++f_rt == min(f_b0 + tb, rt_hi)) {  // next run: next k-block of the batch, else first k-block of the next batch
                 f_kb += kWarps;
                 if (f_kb >= kb_hi) {
                     f_kb = kb_lo + warp;
                     f_b0 += tb;
                 }
                 f_rt = f_b0;
+                if (f_b0 < rt_hi) fetch_point();
+            } else if (f_rt == tail_tile) {
+                fetch_point();
+            } else {
+                f_p0 += tile_stride;
+                f_p1 += tile_stride;
+                f_sb += 16 * gpr;
             }
         }
         cp_async_commit();
