@@ -103,6 +103,8 @@ struct Context {
     // Outgrown workspaces stay allocated until the context goes: launches recorded in CUDA graphs keep
     // using the block they were recorded with.
     std::vector<Block*> qmv_ws_retired;
+    // scratch of the prefill GEMM (partial accumulators of tiles shared between CTAs + their flags)
+    Block* qmm_ws = nullptr;
     const char* last_kernel = "";
     std::atomic<uint64_t> launches{0};
     std::atomic<uint64_t> copies{0};  // memcpy / memset enqueues
@@ -192,7 +194,8 @@ void note_decode_launch(Context* c, const QmmArgs& a);  // call right after a de
 cudaError_t launch_qmv_simt(const QmmArgs& a, cudaStream_t stream, const char** name);
 // prefill GEMM, bf16 activations: TMA + tcgen05 + TMEM
 bool qmm_tc_supported(const QmmArgs& a);
-cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, const char** name,
+size_t qmm_tc_workspace_bytes(int sm_count);  // scratch of a launch (flags at its head: zero between launches)
+cudaError_t launch_qmm_tc(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name,
                           const ShardPush* push = nullptr);
 // non-zero once a kernel gave up on one of its bounded waits since the last call (clears it)
 int take_device_error();
@@ -234,5 +237,6 @@ LuxBackendError qmatmul_on_stream(Context* c, const QmmArgs& a);
 void fill_shard_entries(lux_gpu_quant_vtbl* t);
 void fill_symm_entries(lux_gpu_quant_vtbl* t);
 LuxBackendError ensure_qmv_workspace(Context* c, size_t bytes);  // scratch of the decode kernel, grown on demand
+LuxBackendError ensure_qmm_workspace(Context* c);                // scratch of the prefill GEMM, created on first use
 
 }  // namespace luxcuda

@@ -63,6 +63,7 @@ void destroy_context(LuxBackendContext* ctx) {
     }
     if (c->qmv_ws) c->dev->release(c->qmv_ws, c->stream);
     for (Block* b : c->qmv_ws_retired) c->dev->release(b, c->stream);
+    if (c->qmm_ws) c->dev->release(c->qmm_ws, c->stream);
     c->dev->release_stream(c->stream);
     c->magic = 0;
     delete c;

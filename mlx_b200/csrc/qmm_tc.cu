@@ -45,6 +45,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cmath>
 #include <atomic>
 
 #include "dequant.cuh"
@@ -60,6 +61,7 @@ constexpr int kTileN = 128;        // rows of W per tile (MMA M)
 constexpr int kMaxBM = 256;        // rows of x per tile (MMA N)
 constexpr int kSub = 2;            // 64-weight sub-blocks per pipeline stage (one barrier round per 128 k)
 constexpr int kBBytes = kMaxBM * 128;   // one sub-block of B
+constexpr int kEpiStageBytes = 16 * 32 * 2;  // per epilogue warp: 16 rows of y x 32 columns, bf16
 constexpr int kWUnitBytes = kTileN * 64;  // one unit of packed weights: 128 rows x 64 bytes (128 k at 4 bit, 64 k at 8 bit)
 constexpr int kEpiWarps = 8, kDqGroups = 3, kDqWarps = 4 * kDqGroups;
 // A dequantising group goes from stage s straight to stage s + kDqGroups.  Its wait for that slot is by
@@ -70,6 +72,7 @@ constexpr int kTmaWarp = kEpiWarps + kDqWarps, kMmaWarp = kTmaWarp + 1;
 constexpr int kNumThreads = (kMmaWarp + 1) * 32;
 constexpr uint32_t kTmemCols = 512, kAColBase = 256, kAColsPerSub = kBK / 2, kAColsPerSlot = kSub * kAColsPerSub;
 constexpr uint32_t kSpinLimit = 1u << 20;
+constexpr size_t kWsFlagBytes = 1024;  // flag words of the stream-K workspace (one per CTA), ahead of the partials
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* b, uint32_t n) {
@@ -152,6 +155,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
 // 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
@@ -186,7 +198,57 @@ struct GemmParams {
     void* y_all[kMaxShardWorld];
     int bm;                  // rows of x per tile (multiple of 16, <= 256)
     int n_tiles, m_tiles;
+    float* ws;               // partial accumulators of tiles shared between CTAs: [CTA][bm][128] fp32
+    uint32_t* ws_flags;      // [CTA]: 1 while that CTA's partial waits to be added (zero between launches)
 };
+
+// The work of a launch is the sequence of (tile, k-stage) units, tile after tile.  Two schedules:
+//   * whole tiles, round robin: CTA c takes tiles c, c + G, c + 2G, ... (neighbouring CTAs work on neighbouring
+//     tiles at the same k, which L2 likes); the launch lasts ceil(T/G) tiles;
+//   * "stream-K": CTA c takes the units [U*c/G, U*(c+1)/G), so every SM gets the same number of k-stages
+//     whatever the number of tiles, at the price of one more epilogue per CTA and of the exchange of partial
+//     accumulators described next.  The host picks the cheaper one by a small cost model (make_gemm_plan).
+// A CTA's range is a sequence of segments, each a run of stages [s_lo, s_hi) of one tile.  Only its first
+// segment can start inside a tile (s_lo > 0): that partial accumulator goes to the CTA's slot of the
+// workspace; the CTA that owns the tile's first stages (s_lo == 0) adds the partials of the CTAs after it
+// (c+1 .. the owner of the tile's last stage) in its epilogue and writes y.  Those partials are produced
+// either at the start of the neighbour's range or, when a range is shorter than a tile, at the same time
+// as the head: the head's wait for them is short, and bounded.
+template <bool SK>
+struct SegIter;
+template <>
+struct SegIter<true> {  // stream-K: the CTA's range of units, segment by segment
+    long long u, u_hi;
+    int nst;
+    __device__ __forceinline__ void init(long long total_units, int nst_) {
+        nst = nst_;
+        u = total_units * blockIdx.x / gridDim.x;
+        u_hi = total_units * (blockIdx.x + 1) / gridDim.x;
+    }
+    __device__ __forceinline__ bool valid() const { return u < u_hi; }
+    __device__ __forceinline__ int tile() const { return (int)(u / nst); }
+    __device__ __forceinline__ int s_lo() const { return (int)(u % nst); }
+    __device__ __forceinline__ int s_hi() const { return (int)min((long long)nst, (long long)s_lo() + (u_hi - u)); }
+    __device__ __forceinline__ void next() { u += (long long)(s_hi() - s_lo()); }
+};
+template <>
+struct SegIter<false> {  // whole tiles, round robin: every segment is a tile
+    int t, tiles, nst;
+    __device__ __forceinline__ void init(long long total_units, int nst_) {
+        nst = nst_;
+        tiles = (int)(total_units / nst_);
+        t = blockIdx.x;
+    }
+    __device__ __forceinline__ bool valid() const { return t < tiles; }
+    __device__ __forceinline__ int tile() const { return t; }
+    __device__ __forceinline__ int s_lo() const { return 0; }
+    __device__ __forceinline__ int s_hi() const { return nst; }
+    __device__ __forceinline__ void next() { t += gridDim.x; }
+};
+// the CTA whose range holds unit u
+__device__ __forceinline__ int cta_of_unit(long long u, long long total_units) {
+    return (int)(((u + 1) * gridDim.x - 1) / total_units);
+}
 
 struct SmemLayout {
     uint64_t full[kStagesB], empty[kStagesB], wfull[kDqGroups], tmem_full, tmem_empty;
@@ -243,7 +305,7 @@ __device__ __forceinline__ void dequant_row_stage(const uint32_t* w, uint32_t s0
         }
     }
 }
-template <int BITS>
+template <int BITS, bool SK>
 __global__ void __launch_bounds__(kNumThreads, 1)
 qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
               const __grid_constant__ GemmParams p) {
@@ -253,13 +315,15 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
     unsigned char* sB = smem;  // [kStagesB][bm rows][128 B], swizzled (TMA)
     const uint32_t b_bytes = (uint32_t)p.bm * 128;
     unsigned char* sW = sB + (size_t)kStagesB * kSub * kBBytes;  // [kDqGroups][128 rows][64 B], 64-byte swizzle (TMA)
-    SmemLayout* sl = reinterpret_cast<SmemLayout*>(sW + (size_t)kDqGroups * kWUnitBytes);
+    unsigned char* sEpi = sW + (size_t)kDqGroups * kWUnitBytes;  // [kEpiWarps][16 rows of x][32 rows of the tile] bf16: the epilogue's transposer
+    SmemLayout* sl = reinterpret_cast<SmemLayout*>(sEpi + (size_t)kEpiWarps * kEpiStageBytes);
     volatile int* abort_flag = &sl->abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nks = p.K / kBK;                  // 64-weight sub-blocks along K
     const int nst = (nks + kSub - 1) / kSub;    // pipeline stages per tile
     const int total_tiles = p.n_tiles * p.m_tiles;
+    const long long total_units = (long long)total_tiles * nst;
 
     if (tid == 0) {
         for (int s = 0; s < kStagesB; s++) {
@@ -285,9 +349,11 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
             asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            SegIter<SK> seg;
+            for (seg.init(total_units, nst); seg.valid() && ok; seg.next()) {
+                const int tile = seg.tile(), s_hi = seg.s_hi();
                 const int m0 = (tile % p.m_tiles) * p.bm;
-                for (int st = 0; st < nst; st++, it++) {
+                for (int st = seg.s_lo(); st < s_hi; st++, it++) {
                     const int sb = it % kStagesB;
                     const uint32_t ph = (it / kStagesB) & 1;
                     const int nsub = min(kSub, nks - st * kSub);
@@ -305,10 +371,12 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
             uint32_t tile_i = 0, slot = 0, phase = 0;
             const uint64_t db0 = umma_desc_sw128(s32(sB));
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, tile_i++) {
+            SegIter<SK> seg;
+            for (seg.init(total_units, nst); seg.valid() && ok; seg.next(), tile_i++) {
+                const int s_lo = seg.s_lo(), s_hi = seg.s_hi();
                 if (!mbar_wait(&sl->tmem_empty, (tile_i & 1) ^ 1, abort_flag)) break;
                 tc_fence_after();
-                for (int st = 0; st < nst; st++) {
+                for (int st = s_lo; st < s_hi; st++) {
                     const int nsub = min(kSub, nks - st * kSub);
                     if (!mbar_wait_spin(&sl->full[slot], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
@@ -317,7 +385,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
                         const uint32_t a_tmem = tmem_base + kAColBase + slot * kAColsPerSlot + u * kAColsPerSub;
 #pragma unroll
                         for (int kk = 0; kk < kBK / 16; kk++)  // 16 k = 8 TMEM columns of A, 32 bytes of each B row
-                            tc_mma_ts(tmem_base, a_tmem + 8 * kk, db + 2 * kk, idesc, (st | u | kk) != 0 ? 1u : 0u);
+                            tc_mma_ts(tmem_base, a_tmem + 8 * kk, db + 2 * kk, idesc, (st != s_lo || u || kk) ? 1u : 0u);
                     }
                     tc_commit(&sl->empty[slot]);  // arrives when the MMAs above have consumed their operands
                     if (++slot == kStagesB) { slot = 0; phase ^= 1; }
@@ -342,21 +410,25 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
         uint64_t* wbar = &sl->wfull[grp];
         uint32_t wround = 0;  // units of this group consumed so far
 
-        struct Cur { int tile, st; uint32_t it0; };  // an owned stage: tile, stage in the tile, stage counter at tile start
-        auto settle = [&](Cur& c) {  // first stage of c.tile owned by the group; tiles without one are skipped
-            while (c.tile < total_tiles) {
-                c.st = (int)((grp + kDqGroups - c.it0 % kDqGroups) % kDqGroups);
-                if (c.st < nst) break;
-                c.tile += gridDim.x;
-                c.it0 += nst;
+        // An owned stage: the CTA's stages are counted 0, 1, 2, ... along its range of units (the same count
+        // the producer and the MMA issuer keep); group grp owns the counts = grp (mod kDqGroups).
+        struct Cur { int tile, st; uint32_t it; };  // tile and stage in the tile of count `it`; tile >= total_tiles: past the end
+        const long long u_lo = SK ? total_units * blockIdx.x / gridDim.x : 0;
+        const uint32_t u_cnt = SK ? (uint32_t)(total_units * (blockIdx.x + 1) / gridDim.x - u_lo)
+                                  : (uint32_t)((total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x * nst);
+        const int tile_lo = SK ? (int)(u_lo / nst) : (int)blockIdx.x;  // (the one 64-bit division of the walk)
+        const int st_lo = SK ? (int)(u_lo % nst) : 0;
+        const int tile_step = SK ? 1 : (int)gridDim.x;
+        auto advance = [&](Cur& c, int by) {  // `by` stages further along the CTA's sequence of stages
+            c.it += by;
+            if (c.it >= u_cnt) {
+                c.tile = total_tiles;
+                return;
             }
-        };
-        auto advance = [&](Cur& c) {
-            c.st += kDqGroups;
-            if (c.st >= nst) {
-                c.tile += gridDim.x;
-                c.it0 += nst;
-                settle(c);
+            c.st += by;
+            while (c.st >= nst) {
+                c.st -= nst;
+                c.tile += tile_step;
             }
         };
         auto issue = [&](const Cur& c, int u) {  // leader: bring unit u of stage c into the group's slot
@@ -386,8 +458,8 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
             }
         };
 
-        Cur cur{(int)blockIdx.x, 0, 0u};
-        settle(cur);
+        Cur cur{tile_lo, st_lo, 0u};
+        advance(cur, grp);
         if (cur.tile < total_tiles) {
             if (leader) issue(cur, 0);
             fetch_sb(cur);
@@ -395,8 +467,8 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
         bool ok = true;
         while (cur.tile < total_tiles) {
             Cur nxt = cur;
-            advance(nxt);
-            const uint32_t it = cur.it0 + cur.st;
+            advance(nxt, kDqGroups);
+            const uint32_t it = cur.it;
             const int sa = it % kStagesB;
             const int nsub = min(kSub, nks - cur.st * kSub);
             const uint32_t sc[2] = {sp[0], sp[1]}, bc[2] = {bp[0], bp[1]};
@@ -456,40 +528,163 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
         // ---------------- epilogue: warp w reads TMEM lanes 32*(w%4).., half w/4 of the column blocks ----------------
         const int q = warp & 3, half = warp >> 2;
         const int nblk = (p.bm + 31) / 32, blk_lo = half ? (nblk + 1) / 2 : 0, blk_hi = half ? nblk : (nblk + 1) / 2;
+        const int et = tid;                       // 0 .. 255: the epilogue threads are the first eight warps
+        const int nl = q * 32 + lane;             // this thread's row of the tile (TMEM lane)
+        constexpr int kEpiBar = 1 + kDqGroups;    // named barrier of the epilogue warps
         uint32_t tile_i = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tile_i++) {
-            const int n = (tile / p.m_tiles) * kTileN + q * 32 + lane;
+        bool ok = true;
+        SegIter<SK> seg;
+        for (seg.init(total_units, nst); seg.valid() && ok; seg.next(), tile_i++) {
+            const int tile = seg.tile(), s_lo = seg.s_lo(), s_hi = seg.s_hi();
+            const int n = (tile / p.m_tiles) * kTileN + nl;
             const int m0 = (tile % p.m_tiles) * p.bm;
             if (!mbar_wait(&sl->tmem_full, tile_i & 1, abort_flag)) break;
             tc_fence_after();
-            // this thread: column n of y, rows m0 + c (32 consecutive n per warp: 64-byte row segments)
             const int m_end = min(p.bm, p.M - m0);
-            for (int blk = blk_lo; blk < blk_hi; blk++) {
-                const int c0 = blk * 32;
-                uint32_t v[32];
-                __syncwarp();
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
-                if (n < p.N) {
+            if (s_lo != 0) {
+                // The segment starts inside a tile: its accumulator is a partial sum, for the CTA that owns the
+                // tile's first stages.  [row of x][row of the tile] fp32 in this CTA's slot, then the flag.
+                float* ws = p.ws + (size_t)blockIdx.x * (kTileN * kMaxBM);
+                for (int blk = blk_lo; blk < blk_hi; blk++) {
+                    const int c0 = blk * 32;
+                    uint32_t v[32];
+                    __syncwarp();
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
+                    // (rows past the tile's last row of x are stored too: the slot has room for them and nobody adds them)
+#pragma unroll
+                    for (int j = 0; j < 32; j++) __stcg(ws + (size_t)(c0 + j) * kTileN + nl, __uint_as_float(v[j]));
+                }
+                // The stores of all epilogue threads are ordered before the barrier, the barrier before the release
+                // of the flag: whoever acquires the flag sees them.  (No fence per thread: it would wait for the
+                // stores, with the accumulator still held.)
+                asm volatile("bar.sync %0, %1;" ::"n"(kEpiBar), "n"(kEpiWarps * 32) : "memory");
+                if (et == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ws_flags + blockIdx.x), "r"(1u) : "memory");
+            } else {
+                // The segment starts the tile.  If it does not also end it, the CTAs after this one hold the rest:
+                // wait (bounded) for their partials, add them in CTA order, then write y.
+                const int c_last = s_hi == nst ? (int)blockIdx.x : cta_of_unit((long long)(tile + 1) * nst - 1, total_units);
+                const int parts = c_last - (int)blockIdx.x;
+                if (parts > 0) {
+                    bool got = true;
+                    if (et < parts) {
+                        const uint32_t* f = p.ws_flags + blockIdx.x + 1 + et;
+                        uint32_t v = 0;
+                        for (uint32_t i = 0; i < kSpinLimit * 4; i++) {
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                            if (v || ((i & 1023u) == 1023u && *abort_flag)) break;
+                            __nanosleep(100);
+                        }
+                        got = v != 0;
+                    }
+                    uint32_t all;
+                    asm volatile(
+                        "{ .reg .pred p, q; setp.ne.u32 q, %1, 0; bar.red.and.pred p, %2, %3, q; selp.u32 %0, 1, 0, p; }"
+                        : "=r"(all) : "r"((uint32_t)got), "n"(kEpiBar), "n"(kEpiWarps * 32) : "memory");
+                    if (!all) {
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                }
+                // y[m][n] for this thread's n and `cnt` consecutive rows m0 + c0 + j
+                // bf16: the thread holds one column of y (its n) for consecutive rows, but y is contiguous along n.
+                // Sixteen rows at a time go through the warp's 1 KB of shared memory, [row][n], and leave as
+                // 16-byte stores, eight rows of 64 bytes per instruction, instead of 2-byte stores of one row.
+                const bool y_vec = p.y_bf16 && ((p.ld | p.col0) & 7) == 0;
+                unsigned char* stg = sEpi + (size_t)warp * kEpiStageBytes;
+                const int ncol0 = (tile / p.m_tiles) * kTileN + q * 32 + (lane & 3) * 8;  // first of this thread's 8 columns on the way out
+                auto store_rows = [&](const uint32_t* v, int c0, int cnt) {
+                    if (y_vec) {
+                        {
+                            constexpr int h = 0;  // (callers on this path pass sixteen rows)
+                            __syncwarp();  // the previous sixteen rows have been read
+#pragma unroll
+                            for (int j = 0; j < 16; j += 2) {
+                                const __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(v[h + j]), __uint_as_float(v[h + j + 1]));
+                                *reinterpret_cast<__nv_bfloat16*>(stg + j * 64 + lane * 2) = pr.x;
+                                *reinterpret_cast<__nv_bfloat16*>(stg + (j + 1) * 64 + lane * 2) = pr.y;
+                            }
+                            __syncwarp();
+#pragma unroll
+                            for (int i = 0; i < 2; i++) {
+                                const int row = i * 8 + (lane >> 2), m = c0 + h + row;
+                                const uint4 val = *reinterpret_cast<const uint4*>(stg + row * 64 + (lane & 3) * 16);
+                                if (m >= m_end || ncol0 >= p.N) continue;
+                                const size_t idx = (size_t)(m0 + m) * p.ld + p.col0 + ncol0;
+                                if (ncol0 + 8 <= p.N) {
+                                    for (int dst = 0; dst < p.world; dst++)
+                                        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y_all[dst]) + idx) = val;
+                                } else {  // the last columns of y: one by one
+                                    const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
+                                    for (int dst = 0; dst < p.world; dst++) {
+                                        uint16_t* yp = reinterpret_cast<uint16_t*>(p.y_all[dst]) + idx;
+#pragma unroll
+                                        for (int e = 0; e < 8; e++)
+                                            if (ncol0 + e < p.N) yp[e] = (uint16_t)(w4[e >> 1] >> ((e & 1) * 16));
+                                    }
+                                }
+                            }
+                        }
+                        return;
+                    }
+                    if (n >= p.N) return;
                     // column-sharded layers: the tile goes into every rank's copy of y (peer stores over NVLink)
                     const size_t idx0 = (size_t)(m0 + c0) * p.ld + p.col0 + n;
                     for (int dst = 0; dst < p.world; dst++) {
                         if (p.y_bf16) {
                             __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(p.y_all[dst]) + idx0;
-                            if (c0 + 32 <= m_end) {
 #pragma unroll
-                                for (int j = 0; j < 32; j++) yp[(size_t)j * p.ld] = __float2bfloat16_rn(__uint_as_float(v[j]));
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; j++)
-                                    if (c0 + j < m_end) yp[(size_t)j * p.ld] = __float2bfloat16_rn(__uint_as_float(v[j]));
-                            }
+                            for (int j = 0; j < 32; j++)
+                                if (j < cnt && c0 + j < m_end) yp[(size_t)j * p.ld] = __float2bfloat16_rn(__uint_as_float(v[j]));
                         } else {
                             float* yp = reinterpret_cast<float*>(p.y_all[dst]) + idx0;
 #pragma unroll
                             for (int j = 0; j < 32; j++)
-                                if (c0 + j < m_end) yp[(size_t)j * p.ld] = __uint_as_float(v[j]);
+                                if (j < cnt && c0 + j < m_end) yp[(size_t)j * p.ld] = __uint_as_float(v[j]);
                         }
                     }
+                };
+                if (parts == 0 && y_vec) {
+                    for (int c0 = blk_lo * 32; c0 < blk_hi * 32; c0 += 16) {
+                        uint32_t v[16];
+                        __syncwarp();
+                        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
+                        store_rows(v, c0, 16);
+                    }
+                } else if (parts == 0) {
+                    for (int blk = blk_lo; blk < blk_hi; blk++) {
+                        uint32_t v[32];
+                        __syncwarp();
+                        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + blk * 32, v);
+                        store_rows(v, blk * 32, 32);
+                    }
+                } else {
+                    // 16 rows of x at a time (accumulator + one partial in registers); the partial is requested
+                    // before the accumulator is read
+                    for (int c0 = blk_lo * 32; c0 < blk_hi * 32; c0 += 16) {
+                        uint32_t v[32];
+                        float pv[16];
+                        const float* ws = p.ws + (size_t)(blockIdx.x + 1) * (kTileN * kMaxBM) + (size_t)c0 * kTileN + nl;
+#pragma unroll
+                        for (int j = 0; j < 16; j++) pv[j] = __ldcg(ws + (size_t)j * kTileN);
+                        __syncwarp();
+                        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c0, reinterpret_cast<uint32_t(&)[16]>(v));
+                        for (int pt = 1; pt <= parts; pt++) {
+#pragma unroll
+                            for (int j = 0; j < 16; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + pv[j]);
+                            if (pt < parts) {
+                                ws += (size_t)kTileN * kMaxBM;
+#pragma unroll
+                                for (int j = 0; j < 16; j++) pv[j] = __ldcg(ws + (size_t)j * kTileN);
+                            }
+                        }
+                        store_rows(v, c0, 16);
+                    }
+                }
+                if (parts > 0) {
+                    // every epilogue thread has read the partials: their flags go back to zero for the next launch
+                    asm volatile("bar.sync %0, %1;" ::"n"(kEpiBar), "n"(kEpiWarps * 32) : "memory");
+                    if (et < parts) p.ws_flags[blockIdx.x + 1 + et] = 0;
                 }
             }
             tc_fence_before();
@@ -540,7 +735,7 @@ int* error_word() {
 }
 
 struct GemmPlan {
-    int bm, m_tiles, n_tiles;
+    int bm, m_tiles, n_tiles, streamk;
     size_t smem;
 };
 
@@ -558,13 +753,28 @@ bool make_gemm_plan(const QmmArgs& a, int sm_count, GemmPlan* pl) {
     (void)sm_count;
     pl->m_tiles = (a.M + kMaxBM - 1) / kMaxBM;
     pl->bm = (((a.M + pl->m_tiles - 1) / pl->m_tiles) + 15) & ~15;
-    pl->smem = 1024 + (size_t)kStagesB * kSub * kBBytes + (size_t)kDqGroups * kWUnitBytes + sizeof(SmemLayout) + 64;
+    pl->smem = 1024 + (size_t)kStagesB * kSub * kBBytes + (size_t)kDqGroups * kWUnitBytes + (size_t)kEpiWarps * kEpiStageBytes +
+               sizeof(SmemLayout) + 64;
+    // Schedule.  In units of one k-stage of a tile (about 0.8 us): an epilogue costs about e = 4 * bm/256 (the
+    // accumulator is single: nothing else runs meanwhile), handing over and adding one partial accumulator about
+    // 7 * bm/256 more, and a stage of a stream-K launch about 1.12 stages of a whole-tile launch (fitted to
+    // measurements of both schedules on shapes from 32 to 512 tiles).  Whole tiles: ceil(T/G) * (nst + e).
+    // Stream-K: 1.12 * T*nst/G, one epilogue more, and the partials of the tile a CTA starts.
+    {
+        const double T = (double)pl->n_tiles * pl->m_tiles, G = sm_count, nst = (a.K / kBK + kSub - 1) / kSub;
+        const double e = 4.0 * pl->bm / 256.0, rounds = std::ceil(T / G);
+        const double parts = T < G ? std::ceil(G / T) : 1.0;
+        const double whole = rounds * (nst + e);
+        const double sk = 1.12 * T * nst / G + (rounds + 1.0) * e + 7.0 * pl->bm / 256.0 * parts;
+        pl->streamk = sk < whole && T * nst >= G;
+        if (const char* env = getenv("LUXCUDA_QMM_SCHEDULE")) pl->streamk = env[0] == 's';  // "streamk" | "tiles" (experiments)
+    }
     return encode_tiled_fn() != nullptr;
 }
 
-template <int BITS>
+template <int BITS, bool SK>
 cudaError_t launch_gemm_t(const CUtensorMap& tmap, const CUtensorMap& tmap_w, const GemmParams& p, const GemmPlan& pl, int sm_count, cudaStream_t stream) {
-    auto kern = qmm_tc_kernel<BITS>;
+    auto kern = qmm_tc_kernel<BITS, SK>;
     static std::atomic<size_t> attr_smem[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -573,7 +783,9 @@ cudaError_t launch_gemm_t(const CUtensorMap& tmap, const CUtensorMap& tmap_w, co
         if (e != cudaSuccess) return e;
         attr_smem[dev & 63].store(pl.smem);
     }
-    const int grid = std::min(sm_count, pl.m_tiles * pl.n_tiles);
+    // one CTA per SM, unless the launch has fewer units of work (tiles, or k-stages under stream-K) than that
+    const long long units = (long long)pl.m_tiles * pl.n_tiles * (SK ? (p.K / kBK + kSub - 1) / kSub : 1);
+    const int grid = (int)std::min<long long>(sm_count, units);
     kern<<<grid, kNumThreads, pl.smem, stream>>>(tmap, tmap_w, p);
     return cudaGetLastError();
 }
@@ -585,9 +797,14 @@ bool qmm_tc_supported(const QmmArgs& a) {
     return make_gemm_plan(a, 148, &pl);
 }
 
-cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, const char** name, const ShardPush* push) {
+// Scratch of a launch: one partial accumulator and one flag word per CTA (see SegIter).  The flags must be zero
+// before the first launch; every launch leaves them zero.
+size_t qmm_tc_workspace_bytes(int sm_count) { return kWsFlagBytes + (size_t)sm_count * kTileN * kMaxBM * sizeof(float); }
+
+cudaError_t launch_qmm_tc(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name,
+                          const ShardPush* push) {
     GemmPlan pl;
-    if (!make_gemm_plan(a, sm_count, &pl)) return cudaErrorInvalidValue;
+    if (!make_gemm_plan(a, sm_count, &pl) || !workspace || sm_count * sizeof(uint32_t) > kWsFlagBytes) return cudaErrorInvalidValue;
     int* err = error_word();
     if (!err) return cudaErrorMemoryAllocation;
     // x as a 2-D tensor [M rows][K], boxes of 64 elements (128 bytes) x bm rows, 128-byte swizzle;
@@ -642,12 +859,16 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, int sm_count, cudaStream_t stream, c
             if (r != push->me) p.y_all[k++] = push->y[r];
     }
     p.bm = pl.bm; p.n_tiles = pl.n_tiles; p.m_tiles = pl.m_tiles;
+    p.ws_flags = static_cast<uint32_t*>(workspace);
+    p.ws = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kWsFlagBytes);
     if (a.bits == 4) {
         if (name) *name = "qmm_tc<4>";
-        return launch_gemm_t<4>(tmap, tmap_w, p, pl, sm_count, stream);
+        return pl.streamk ? launch_gemm_t<4, true>(tmap, tmap_w, p, pl, sm_count, stream)
+                          : launch_gemm_t<4, false>(tmap, tmap_w, p, pl, sm_count, stream);
     }
     if (name) *name = "qmm_tc<8>";
-    return launch_gemm_t<8>(tmap, tmap_w, p, pl, sm_count, stream);
+    return pl.streamk ? launch_gemm_t<8, true>(tmap, tmap_w, p, pl, sm_count, stream)
+                      : launch_gemm_t<8, false>(tmap, tmap_w, p, pl, sm_count, stream);
 }
 
 // Device-side address of the host-visible error word (the same on every GPU: portable mapped memory).

@@ -94,6 +94,27 @@ LuxBackendError ensure_qmv_workspace(Context* c, size_t bytes) {
     return LUX_BACKEND_OK;
 }
 
+LuxBackendError ensure_qmm_workspace(Context* c) {
+    if (c->qmm_ws) return LUX_BACKEND_OK;
+    const size_t bytes = qmm_tc_workspace_bytes(c->dev->sm_count);
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(c->stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone) {
+        set_last_error("qmatmul: the prefill kernel's workspace does not exist yet; run one M > 16 call outside the graph capture first");
+        return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    }
+    cudaError_t e = cudaSuccess;
+    Block* nb = c->dev->acquire(bytes, c->stream, &e);
+    if (!nb) return map_cuda_error(e, "qmm workspace");
+    e = cudaMemsetAsync(nb->ptr, 0, bytes, c->stream);  // the flags start at zero; every launch leaves them at zero
+    c->copies++;
+    if (e != cudaSuccess) {
+        c->dev->release(nb, c->stream);
+        return map_cuda_error(e, "qmm workspace memset");
+    }
+    c->qmm_ws = nb;
+    return LUX_BACKEND_OK;
+}
+
 LuxBackendError qmatmul_on_stream(Context* c, const QmmArgs& a) {
     if (a.M == 0 || a.N == 0) return LUX_BACKEND_OK;
     const char* name = "";
@@ -101,7 +122,9 @@ LuxBackendError qmatmul_on_stream(Context* c, const QmmArgs& a) {
     int launches = 1;
     if (a.x_dtype == LUX_DTYPE_BFLOAT16) {
         if (a.M > 16 && qmm_tc_supported(a)) {
-            e = launch_qmm_tc(a, c->dev->sm_count, c->stream, &name);
+            LuxBackendError le = ensure_qmm_workspace(c);
+            if (le != LUX_BACKEND_OK) return le;
+            e = launch_qmm_tc(a, c->qmm_ws->ptr, c->dev->sm_count, c->stream, &name);
         } else {
             // decode kernel, 16 rows of x per launch
             QmmArgs chunk = a;

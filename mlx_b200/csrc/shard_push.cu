@@ -232,7 +232,9 @@ LuxBackendError qmatmul_sharded_push(LuxCudaSymmBuffer* sb, LuxBackendBuffer* x,
             symm_barrier_kernel<<<1, 32, 0, c->stream>>>(ba);
             LUX_CUDA_TRY(cudaGetLastError());
         }
-        cudaError_t e = launch_qmm_tc(a, c->dev->sm_count, c->stream, &name, &sp);
+        LuxBackendError le = ensure_qmm_workspace(c);
+        if (le != LUX_BACKEND_OK) return le;
+        cudaError_t e = launch_qmm_tc(a, c->qmm_ws->ptr, c->dev->sm_count, c->stream, &name, &sp);
         if (e != cudaSuccess) return map_cuda_error(e, name);
         if (sb->world > 1) {
             symm_barrier_kernel<<<1, 32, 0, c->stream>>>(ba);
