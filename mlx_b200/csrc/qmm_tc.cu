@@ -102,6 +102,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, volatile
     return false;
 }
 
+// One look at a barrier, never suspended: the answer comes back some hundred cycles later, which the caller
+// can spend on other instructions.
+__device__ __forceinline__ bool mbar_test_addr(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
 // Same bound, no back-off: for the one thread whose wake-up latency is on the tensor pipe's critical path.
 __device__ __forceinline__ bool mbar_wait_spin(uint64_t* b, uint32_t parity, volatile int* abort_flag) {
     for (uint32_t i = 0; i < kSpinLimit * 8; i++) {
@@ -125,12 +134,19 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
 }
-// D[tmem] (+)= A[tmem] * B[smem desc], bf16 inputs, fp32 accumulate
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem desc], bf16 inputs, fp32 accumulate.  The B descriptor comes as two words:
+// only the low one, which holds the address, changes between calls.
+__device__ __forceinline__ void tc_mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc) {
     asm volatile(
-        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
-        "  tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+        "{ .reg .pred p; .reg .b64 bd; setp.eq.u32 p, 1, 1; mov.b64 bd, {%2, %3};\n"
+        "  tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p; }"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts_first(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p; .reg .b64 bd; setp.ne.b32 p, %5, 0; mov.b64 bd, {%2, %3};\n"
+        "  tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p; }"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 // 32 consecutive 32-bit columns of this thread's TMEM lane <- 32 registers
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -370,25 +386,39 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
             const uint32_t idesc = umma_idesc(kTileN, p.bm);
             uint32_t tile_i = 0, slot = 0, phase = 0;
             const uint64_t db0 = umma_desc_sw128(s32(sB));
+            const uint32_t b_hi = (uint32_t)(db0 >> 32), b_lo0 = (uint32_t)db0;  // the address is in the low word, 16-byte units
+            const uint32_t a0 = tmem_base + kAColBase, bar0 = s32(&sl->full[0]);
             bool ok = true;
+            // This thread's instructions are the pipeline's critical path (it shares its scheduler with working
+            // warps, and a look at a barrier costs it some hundred cycles even when the phase is long over): the
+            // barrier of the NEXT stage is looked at before the MMAs of the current one are issued, the answer read
+            // after; an MMA is an add or two and the instruction.
+            bool ready = false;
             SegIter<SK> seg;
             for (seg.init(total_units, nst); seg.valid() && ok; seg.next(), tile_i++) {
                 const int s_lo = seg.s_lo(), s_hi = seg.s_hi();
                 if (!mbar_wait(&sl->tmem_empty, (tile_i & 1) ^ 1, abort_flag)) break;
                 tc_fence_after();
                 for (int st = s_lo; st < s_hi; st++) {
-                    const int nsub = min(kSub, nks - st * kSub);
-                    if (!mbar_wait_spin(&sl->full[slot], phase, abort_flag)) { ok = false; break; }
+                    if (!ready && !mbar_wait_spin(&sl->full[slot], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    for (int u = 0; u < nsub; u++) {
-                        const uint64_t db = db0 + (uint64_t)(slot * kSub + u) * (kBBytes >> 4);
-                        const uint32_t a_tmem = tmem_base + kAColBase + slot * kAColsPerSlot + u * kAColsPerSub;
+                    uint32_t nslot = slot + 1, nphase = phase;
+                    if (nslot == (uint32_t)kStagesB) { nslot = 0; nphase ^= 1; }
+                    const bool rn = mbar_test_addr(bar0 + 8 * nslot, nphase);  // (past the CTA's last stage: "not yet", and not used)
+                    const uint32_t b_lo = b_lo0 + slot * (uint32_t)(kSub * kBBytes >> 4);
+                    const uint32_t a_tmem = a0 + slot * kAColsPerSlot;
+                    // 16 k per MMA = 8 TMEM columns of A, 32 bytes of each B row
+                    tc_mma_ts_first(tmem_base, a_tmem, b_lo, b_hi, idesc, st != s_lo ? 1u : 0u);
 #pragma unroll
-                        for (int kk = 0; kk < kBK / 16; kk++)  // 16 k = 8 TMEM columns of A, 32 bytes of each B row
-                            tc_mma_ts(tmem_base, a_tmem + 8 * kk, db + 2 * kk, idesc, (st != s_lo || u || kk) ? 1u : 0u);
+                    for (int kk = 1; kk < kBK / 16; kk++) tc_mma_ts_acc(tmem_base, a_tmem + 8 * kk, b_lo + 2 * kk, b_hi, idesc);
+                    if (st * kSub + 1 < nks) {  // (the last stage of an odd K has one sub-block)
+#pragma unroll
+                        for (int kk = 0; kk < kBK / 16; kk++)
+                            tc_mma_ts_acc(tmem_base, a_tmem + kAColsPerSub + 8 * kk, b_lo + (kBBytes >> 4) + 2 * kk, b_hi, idesc);
                     }
                     tc_commit(&sl->empty[slot]);  // arrives when the MMAs above have consumed their operands
-                    if (++slot == kStagesB) { slot = 0; phase ^= 1; }
+                    ready = rn;
+                    slot = nslot; phase = nphase;
                 }
                 if (ok) tc_commit(&sl->tmem_full);
             }
@@ -507,6 +537,8 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
                 if (scale_fast_ok(s0) && scale_fast_ok(s1)) dequant_row_stage<BITS, true>(ws, s0, b0, s1, b1, out);
                 else dequant_row_stage<BITS, false>(ws, s0, b0, s1, b1, out);  // whole-block branch: not if-converted
                 if (u == 0) {
+                    // (every lane waits: with one lane polling for the warp the wake-up came later and the launch
+                    // took 3 % longer)
                     const bool freed = ok && mbar_wait(&sl->empty[sa], ((it / kStagesB) & 1) ^ 1, abort_flag);
                     ok = __all_sync(0xFFFFFFFFu, freed);  // tcgen05.st below is warp-collective
                     tc_fence_after();
@@ -645,6 +677,7 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
                     }
                 };
                 if (parts == 0 && y_vec) {
+                    // (requesting the next sixteen columns before the current ones are stored was tried: 3 % slower)
                     for (int c0 = blk_lo * 32; c0 < blk_hi * 32; c0 += 16) {
                         uint32_t v[16];
                         __syncwarp();
