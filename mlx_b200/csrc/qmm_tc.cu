@@ -134,7 +134,14 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
 }
-// D[tmem] (+)= A[tmem] * B[smem desc], bf16 inputs, fp32 accumulate.  The B descriptor comes as two words:
+// D[tmem] (+)= A[tmem] * B[smem desc], bf16 inputs, fp32 accumulate
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+        "  tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The same with the B descriptor as two words:
 // only the low one, which holds the address, changes between calls.
 __device__ __forceinline__ void tc_mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc) {
     asm volatile(
@@ -246,20 +253,6 @@ struct SegIter<true> {  // stream-K: the CTA's range of units, segment by segmen
     __device__ __forceinline__ int s_lo() const { return (int)(u % nst); }
     __device__ __forceinline__ int s_hi() const { return (int)min((long long)nst, (long long)s_lo() + (u_hi - u)); }
     __device__ __forceinline__ void next() { u += (long long)(s_hi() - s_lo()); }
-};
-template <>
-struct SegIter<false> {  // whole tiles, round robin: every segment is a tile
-    int t, tiles, nst;
-    __device__ __forceinline__ void init(long long total_units, int nst_) {
-        nst = nst_;
-        tiles = (int)(total_units / nst_);
-        t = blockIdx.x;
-    }
-    __device__ __forceinline__ bool valid() const { return t < tiles; }
-    __device__ __forceinline__ int tile() const { return t; }
-    __device__ __forceinline__ int s_lo() const { return 0; }
-    __device__ __forceinline__ int s_hi() const { return nst; }
-    __device__ __forceinline__ void next() { t += gridDim.x; }
 };
 // the CTA whose range holds unit u
 __device__ __forceinline__ int cta_of_unit(long long u, long long total_units) {
@@ -734,6 +727,273 @@ qmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant_
     }
 }
 
+// Whole tiles, round robin, as a kernel of its own: the same roles without the bookkeeping of split tiles.  (One
+// body for both schedules ran this one 5 % slower, and so did every addition tried here -- 16-byte stores through
+// shared memory in the epilogue, the look-ahead of the MMA issuer: the launch is sensitive to the amount of code
+// its roles execute side by side.)
+template <int BITS>
+__global__ void __launch_bounds__(kNumThreads, 1)
+qmm_tc_tiles_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+              const __grid_constant__ GemmParams p) {
+    constexpr int WPS = kBK * BITS / 32;  // packed words per row per stage: 8 | 16
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* sB = smem;  // [kStagesB][bm rows][128 B], swizzled (TMA)
+    const uint32_t b_bytes = (uint32_t)p.bm * 128;
+    unsigned char* sW = sB + (size_t)kStagesB * kSub * kBBytes;  // [kDqGroups][128 rows][64 B], 64-byte swizzle (TMA)
+    SmemLayout* sl = reinterpret_cast<SmemLayout*>(sW + (size_t)kDqGroups * kWUnitBytes);
+    volatile int* abort_flag = &sl->abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nks = p.K / kBK;                  // 64-weight sub-blocks along K
+    const int nst = (nks + kSub - 1) / kSub;    // pipeline stages per tile
+    const int total_tiles = p.n_tiles * p.m_tiles;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStagesB; s++) {
+            mbar_init(&sl->full[s], 128 + 1);  // 128 dequantising threads + the TMA producer (with its byte count)
+            mbar_init(&sl->empty[s], 1);        // one tcgen05.commit
+        }
+        for (int g = 0; g < kDqGroups; g++) mbar_init(&sl->wfull[g], 1);  // the group leader's expect_tx
+        mbar_init(&sl->tmem_full, 1);
+        mbar_init(&sl->tmem_empty, kEpiWarps * 32);
+        sl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kMmaWarp) tmem_alloc(&sl->tmem_base, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sl->tmem_base;
+
+    if (warp == kTmaWarp) {
+        // ---------------- TMA producer: x tiles ----------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % p.m_tiles) * p.bm;
+                for (int st = 0; st < nst; st++, it++) {
+                    const int sb = it % kStagesB;
+                    const uint32_t ph = (it / kStagesB) & 1;
+                    const int nsub = min(kSub, nks - st * kSub);
+                    if (!mbar_wait(&sl->empty[sb], ph ^ 1, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(&sl->full[sb], b_bytes * nsub);
+                    for (int u = 0; u < nsub; u++)
+                        tma_load_2d(sB + ((size_t)sb * kSub + u) * kBBytes, &tmap_x, (st * kSub + u) * kBK, m0, &sl->full[sb]);
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(kTileN, p.bm);
+            uint32_t tile_i = 0, slot = 0, phase = 0;
+            const uint64_t db0 = umma_desc_sw128(s32(sB));
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, tile_i++) {
+                if (!mbar_wait(&sl->tmem_empty, (tile_i & 1) ^ 1, abort_flag)) break;
+                tc_fence_after();
+                for (int st = 0; st < nst; st++) {
+                    const int nsub = min(kSub, nks - st * kSub);
+                    if (!mbar_wait_spin(&sl->full[slot], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    for (int u = 0; u < nsub; u++) {
+                        const uint64_t db = db0 + (uint64_t)(slot * kSub + u) * (kBBytes >> 4);
+                        const uint32_t a_tmem = tmem_base + kAColBase + slot * kAColsPerSlot + u * kAColsPerSub;
+#pragma unroll
+                        for (int kk = 0; kk < kBK / 16; kk++)  // 16 k = 8 TMEM columns of A, 32 bytes of each B row
+                            tc_mma_ts(tmem_base, a_tmem + 8 * kk, db + 2 * kk, idesc, (st | u | kk) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(&sl->empty[slot]);  // arrives when the MMAs above have consumed their operands
+                    if (++slot == kStagesB) { slot = 0; phase ^= 1; }
+                }
+                if (ok) tc_commit(&sl->tmem_full);
+            }
+        }
+    } else if (warp >= kEpiWarps) {
+        // ---------------- dequantisers: group grp owns the stages = grp (mod kDqGroups); thread owns row n0 + r ----------------
+        constexpr int UPS = BITS == 8 ? 2 : 1;  // weight units (128 rows x 64 packed bytes) per pipeline stage
+        const int q = warp & 3, grp = (warp - kEpiWarps) >> 2;
+        const int r = q * 32 + lane;
+        const bool leader = (q == 0 && lane == 0);
+        const int bar_id = 1 + grp;  // named barrier of the group (0 is __syncthreads)
+        const int gpr = p.K >> p.gshift;
+        const int ng_full = (kSub * kBK) >> p.gshift;  // scale groups per full stage: 4, 2 or 1
+        const bool vec_ok = (gpr % ng_full) == 0;      // then a stage's scales of one row are one aligned vector
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kAColBase;
+        // this group's weight unit in shared memory; row r is 64 bytes, its 16-byte chunk c sits at c ^ ((r >> 1) & 3)
+        const unsigned char* wrow = sW + (size_t)grp * kWUnitBytes + r * 64;
+        const uint32_t wsw = (uint32_t)(r >> 1) & 3u;
+        uint64_t* wbar = &sl->wfull[grp];
+        uint32_t wround = 0;  // units of this group consumed so far
+
+        struct Cur { int tile, st; uint32_t it0; };  // an owned stage: tile, stage in the tile, stage counter at tile start
+        auto settle = [&](Cur& c) {  // first stage of c.tile owned by the group; tiles without one are skipped
+            while (c.tile < total_tiles) {
+                c.st = (int)((grp + kDqGroups - c.it0 % kDqGroups) % kDqGroups);
+                if (c.st < nst) break;
+                c.tile += gridDim.x;
+                c.it0 += nst;
+            }
+        };
+        auto advance = [&](Cur& c) {
+            c.st += kDqGroups;
+            if (c.st >= nst) {
+                c.tile += gridDim.x;
+                c.it0 += nst;
+                settle(c);
+            }
+        };
+        auto issue = [&](const Cur& c, int u) {  // leader: bring unit u of stage c into the group's slot
+            mbar_expect_tx(wbar, kWUnitBytes);
+            tma_load_2d(const_cast<unsigned char*>(sW) + (size_t)grp * kWUnitBytes, &tmap_w,
+                        c.st * (kSub * kBK * BITS / 8) + u * 64, (c.tile / p.m_tiles) * kTileN, wbar);
+        };
+        uint32_t sp[2], bp[2];  // scales / biases of the next owned stage of this row, bf16 pairs in group order
+        auto fetch_sb = [&](const Cur& c) {
+            const int n = min((c.tile / p.m_tiles) * kTileN + r, p.N - 1);
+            const int g0 = (c.st * kSub * kBK) >> p.gshift;
+            const int ng = min(gpr - g0, ng_full);
+            const uint16_t* sr = reinterpret_cast<const uint16_t*>(p.scales) + (size_t)n * gpr + g0;
+            const uint16_t* br = reinterpret_cast<const uint16_t*>(p.biases) + (size_t)n * gpr + g0;
+            sp[1] = 0; bp[1] = 0;
+            if (vec_ok && ng == ng_full && ng == 4) {
+                asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(sp[0]), "=r"(sp[1]) : "l"(sr));
+                asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(bp[0]), "=r"(bp[1]) : "l"(br));
+            } else if (vec_ok && ng == ng_full && ng == 2) {
+                asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(sp[0]) : "l"(sr));
+                asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(bp[0]) : "l"(br));
+            } else {
+                sp[0] = ldg_u16(sr); bp[0] = ldg_u16(br);
+                if (ng > 1) { sp[0] |= ldg_u16(sr + 1) << 16; bp[0] |= ldg_u16(br + 1) << 16; }
+                if (ng > 2) { sp[1] = ldg_u16(sr + 2); bp[1] = ldg_u16(br + 2); }
+                if (ng > 3) { sp[1] |= ldg_u16(sr + 3) << 16; bp[1] |= ldg_u16(br + 3) << 16; }
+            }
+        };
+
+        Cur cur{(int)blockIdx.x, 0, 0u};
+        settle(cur);
+        if (cur.tile < total_tiles) {
+            if (leader) issue(cur, 0);
+            fetch_sb(cur);
+        }
+        bool ok = true;
+        while (cur.tile < total_tiles) {
+            Cur nxt = cur;
+            advance(nxt);
+            const uint32_t it = cur.it0 + cur.st;
+            const int sa = it % kStagesB;
+            const int nsub = min(kSub, nks - cur.st * kSub);
+            const uint32_t sc[2] = {sp[0], sp[1]}, bc[2] = {bp[0], bp[1]};
+            if (nxt.tile < total_tiles) fetch_sb(nxt);  // three stages ahead of its use
+            uint32_t w[16];
+            bool group_fail = false;
+#pragma unroll
+            for (int u = 0; u < kSub; u++) {
+                if (u >= nsub) break;
+                if (UPS == 2 || u == 0) {
+                    const bool got = ok && mbar_wait(wbar, wround & 1, abort_flag);
+                    wround++;
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(wrow + ((c ^ wsw) << 4));
+                        w[4 * c] = v.x; w[4 * c + 1] = v.y; w[4 * c + 2] = v.z; w[4 * c + 3] = v.w;
+                    }
+                    // The reads above are generic-proxy accesses, the refill is an async-proxy write: the proxy
+                    // fence orders the two (without it a read still in the load pipe could see the next unit).
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    // every thread of the group has its bytes: the slot may be refilled.  The same barrier makes
+                    // a failed wait a decision of the whole group, so nobody is left waiting at it.
+                    ok = group_all(bar_id, got);
+                    if (!ok) { group_fail = true; break; }
+                    if (leader) {
+                        if (UPS == 2 && u + 1 < nsub) issue(cur, u + 1);
+                        else if (nxt.tile < total_tiles) issue(nxt, 0);
+                    }
+                }
+                // scales of the two 32-weight halves of this sub-block
+                const int h0 = (2 * u * 32) >> p.gshift, h1 = ((2 * u + 1) * 32) >> p.gshift;
+                const uint32_t s0 = (sc[h0 >> 1] >> ((h0 & 1) * 16)) & 0xFFFFu, b0 = (bc[h0 >> 1] >> ((h0 & 1) * 16)) & 0xFFFFu;
+                const uint32_t s1 = (sc[h1 >> 1] >> ((h1 & 1) * 16)) & 0xFFFFu, b1 = (bc[h1 >> 1] >> ((h1 & 1) * 16)) & 0xFFFFu;
+                uint32_t out[32];
+                const uint32_t (&ws)[WPS] = *reinterpret_cast<const uint32_t (*)[WPS]>(&w[BITS == 4 ? 8 * u : 0]);
+                if (scale_fast_ok(s0) && scale_fast_ok(s1)) dequant_row_stage<BITS, true>(ws, s0, b0, s1, b1, out);
+                else dequant_row_stage<BITS, false>(ws, s0, b0, s1, b1, out);  // whole-block branch: not if-converted
+                if (u == 0) {
+                    const bool freed = ok && mbar_wait(&sl->empty[sa], ((it / kStagesB) & 1) ^ 1, abort_flag);
+                    ok = __all_sync(0xFFFFFFFFu, freed);  // tcgen05.st below is warp-collective
+                    tc_fence_after();
+                }
+                __syncwarp();
+                if (ok) tmem_st32(lane_addr + sa * kAColsPerSlot + u * kAColsPerSub, out);
+            }
+            if (ok) {
+                tmem_st_wait();  // once per stage: both sub-blocks are in tensor memory
+                tc_fence_before();
+                mbar_arrive(&sl->full[sa]);
+            } else if (!*abort_flag) {
+                *abort_flag = 1;
+            }
+            if (group_fail) break;  // decided by the whole group at its barrier
+            cur = nxt;                // a warp that failed alone goes on to the next barrier, where the group ends
+        }
+    } else {
+        // ---------------- epilogue: warp w reads TMEM lanes 32*(w%4).., half w/4 of the column blocks ----------------
+        const int q = warp & 3, half = warp >> 2;
+        const int nblk = (p.bm + 31) / 32, blk_lo = half ? (nblk + 1) / 2 : 0, blk_hi = half ? nblk : (nblk + 1) / 2;
+        uint32_t tile_i = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tile_i++) {
+            const int n = (tile / p.m_tiles) * kTileN + q * 32 + lane;
+            const int m0 = (tile % p.m_tiles) * p.bm;
+            if (!mbar_wait(&sl->tmem_full, tile_i & 1, abort_flag)) break;
+            tc_fence_after();
+            // this thread: column n of y, rows m0 + c (32 consecutive n per warp: 64-byte row segments)
+            const int m_end = min(p.bm, p.M - m0);
+            for (int blk = blk_lo; blk < blk_hi; blk++) {
+                const int c0 = blk * 32;
+                uint32_t v[32];
+                __syncwarp();
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
+                if (n < p.N) {
+                    // column-sharded layers: the tile goes into every rank's copy of y (peer stores over NVLink)
+                    const size_t idx0 = (size_t)(m0 + c0) * p.ld + p.col0 + n;
+                    for (int dst = 0; dst < p.world; dst++) {
+                        if (p.y_bf16) {
+                            __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(p.y_all[dst]) + idx0;
+                            if (c0 + 32 <= m_end) {
+#pragma unroll
+                                for (int j = 0; j < 32; j++) yp[(size_t)j * p.ld] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    if (c0 + j < m_end) yp[(size_t)j * p.ld] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                            }
+                        } else {
+                            float* yp = reinterpret_cast<float*>(p.y_all[dst]) + idx0;
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (c0 + j < m_end) yp[(size_t)j * p.ld] = __uint_as_float(v[j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&sl->tmem_empty);
+        }
+    }
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && sl->abort_flag) *p.error = 1;
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
 // ---- host side -------------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -788,17 +1048,18 @@ bool make_gemm_plan(const QmmArgs& a, int sm_count, GemmPlan* pl) {
     pl->bm = (((a.M + pl->m_tiles - 1) / pl->m_tiles) + 15) & ~15;
     pl->smem = 1024 + (size_t)kStagesB * kSub * kBBytes + (size_t)kDqGroups * kWUnitBytes + (size_t)kEpiWarps * kEpiStageBytes +
                sizeof(SmemLayout) + 64;
-    // Schedule.  In units of one k-stage of a tile (about 0.8 us): an epilogue costs about e = 4 * bm/256 (the
-    // accumulator is single: nothing else runs meanwhile), handing over and adding one partial accumulator about
-    // 7 * bm/256 more, and a stage of a stream-K launch about 1.12 stages of a whole-tile launch (fitted to
-    // measurements of both schedules on shapes from 32 to 512 tiles).  Whole tiles: ceil(T/G) * (nst + e).
-    // Stream-K: 1.12 * T*nst/G, one epilogue more, and the partials of the tile a CTA starts.
+    // Schedule.  In units of one k-stage of a tile (about 0.8 us) of the whole-tile kernel: an epilogue costs
+    // about e = 4 * bm/256 (the accumulator is single: nothing else runs meanwhile), handing over and adding one
+    // partial accumulator about 7 * bm/256 more, and a stage of the stream-K kernel about 1.3 (fitted to
+    // measurements of both kernels on shapes from 32 to 512 tiles).  Whole tiles: ceil(T/G) * (nst + e).
+    // Stream-K: 1.3 * T*nst/G, one epilogue more, and the partials of the tile a CTA starts.  Stream-K wins
+    // where the tiles are few against the SMs (a column-sharded slice, a small M).
     {
         const double T = (double)pl->n_tiles * pl->m_tiles, G = sm_count, nst = (a.K / kBK + kSub - 1) / kSub;
         const double e = 4.0 * pl->bm / 256.0, rounds = std::ceil(T / G);
         const double parts = T < G ? std::ceil(G / T) : 1.0;
         const double whole = rounds * (nst + e);
-        const double sk = 1.12 * T * nst / G + (rounds + 1.0) * e + 7.0 * pl->bm / 256.0 * parts;
+        const double sk = 1.3 * T * nst / G + (rounds + 1.0) * e + 7.0 * pl->bm / 256.0 * parts;
         pl->streamk = sk < whole && T * nst >= G;
         if (const char* env = getenv("LUXCUDA_QMM_SCHEDULE")) pl->streamk = env[0] == 's';  // "streamk" | "tiles" (experiments)
     }
@@ -807,7 +1068,7 @@ bool make_gemm_plan(const QmmArgs& a, int sm_count, GemmPlan* pl) {
 
 template <int BITS, bool SK>
 cudaError_t launch_gemm_t(const CUtensorMap& tmap, const CUtensorMap& tmap_w, const GemmParams& p, const GemmPlan& pl, int sm_count, cudaStream_t stream) {
-    auto kern = qmm_tc_kernel<BITS, SK>;
+    auto kern = SK ? qmm_tc_kernel<BITS, true> : qmm_tc_tiles_kernel<BITS>;
     static std::atomic<size_t> attr_smem[64];
     int dev = 0;
     cudaGetDevice(&dev);
