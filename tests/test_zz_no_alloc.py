@@ -79,3 +79,27 @@ def test_noalloc_refuses_what_does_not_fit(ctx, oracle, plugin):
     assert ei.value.code == P.ERR_NOT_SUPPORTED
     for h in (bx, bw, bs, bb, y):
         h.free()
+
+
+def test_noalloc_scratch_shared_between_split_shapes(plugin, ctx, oracle):
+    """One scratch array serves every shape: a K-split call with few row tiles, then one with more than 64 row
+    tiles (whose arrival counters used to reach into the region where the first call's partials had lain), then
+    the first again.  Each must give the bits of the ordinary qmatmul on a fresh context."""
+    fresh = plugin.context(0)
+    try:
+        for (M, K, N, bits, group) in ((8, 8192, 64, 4, 64), (1, 8192, 1120, 4, 64), (8, 8192, 64, 4, 64), (1, 8192, 1120, 4, 64)):
+            wq, s, b = oracle.make_layer(N, K, bits, group, oracle.BF16, config_id=13, layer=K, proj=N)
+            x = oracle.make_x(M, K, oracle.BF16, config_id=13, tag=M)
+            fx, fw, fs, fb = fresh.upload(x), fresh.upload(wq), fresh.upload(s), fresh.upload(b)
+            y_ref = fresh.empty((M, N), np.uint16)
+            fresh.qmatmul(fx, fw, fs, fb, y_ref, M, K, N, bits, group, BF16, BF16, BF16)
+            want = y_ref.to_host()
+            bx, bw, bs, bb = ctx.upload(x), ctx.upload(wq), ctx.upload(s), ctx.upload(b)
+            y = ctx.empty((M, N), np.uint16)
+            ctx.qmatmul_decode_noalloc(bx, bw, bs, bb, y, M, K, N, bits, group, BF16)
+            assert ctx.last_kernel().startswith("qmv_mma")
+            assert np.array_equal(y.to_host(), want), (M, K, N)
+            for h in (fx, fw, fs, fb, y_ref, bx, bw, bs, bb, y):
+                h.free()
+    finally:
+        fresh.close()
