@@ -39,7 +39,7 @@ import numpy as np
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one qmv_mma launch (M=1) of this workload, from an ncu capture
 # of `bench.py --kernel-only --no-graph` (counters cannot be read inside the timed run)
-NCU_TRAFFIC_BYTES = 25460736.0
+NCU_TRAFFIC_BYTES = 25461632.0
 SWEEPS_PER_GRAPH = 5  # sweeps (of 4 x 12 launches) recorded in the CUDA graph the timed step replays
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -222,6 +222,9 @@ def prefill_legs(ctx, O, BF16, peaks, only=None):
     for name, (M, K, N, bits, group, R, iters) in {
         "prefill_4bit_M2048_K4096_N4096": (2048, 4096, 4096, 4, 64, 4, 10),
         "gemm_8bit_M512_K8192_N28672": (512, 8192, 28672, 8, 128, 2, 5),
+        # the slice of the 8-bit configuration that one rank computes at 8 GPUs: 56 tiles on 148 SMs, the shape
+        # the stream-K schedule is for
+        "gemm_8bit_slice_M512_K8192_N3584": (512, 8192, 3584, 8, 128, 8, 5),
     }.items():
         if only and name != only:
             continue
@@ -278,7 +281,7 @@ def chain_leg(ctx, O, BF16, peaks):
         bw, bs, bb, N, K = ws[name]
         ctx.qmatmul(src, bw, bs, bb, dst, M, K, N, BITS, GROUP, BF16, BF16, BF16)
 
-    def step():
+    def step_separate():
         for l in range(L):
             ws = layers[l % DISTINCT]
             mm(ws, "qkv", h, t["qkv"])
@@ -290,31 +293,74 @@ def chain_leg(ctx, O, BF16, peaks):
             mm(ws, "down", t["m"], t["d"])
             ctx.rms_norm(t["d"], h, M, D, 1e-6, BF16, BF16)
 
-    step()
-    ctx.sync()
-    ctx.graph_begin()
-    step()
-    g = ctx.graph_end()
-    for _ in range(3):
-        ctx.graph_launch(g)
-    ctx.sync()
-    iters = 10
-    ctx.timer_record(8)
-    for _ in range(iters):
-        ctx.graph_launch(g)
-    ctx.timer_record(9)
-    ms = ctx.timer_elapsed_ms(8, 9) / iters
+    from mlx_b200.plugin import PRO_RMS_NORM, PRO_SUM3
+
+    def pro(ws, name, src, dst, which, ld):
+        bw, bs, bb, N, K = ws[name]
+        ctx.qmatmul_pro(src, bw, bs, bb, dst, M, K, N, BITS, GROUP, BF16, which, ld, 1e-6)
+
+    def step_fused():
+        # the same dataflow with sum3 and the two rms-norms whose row is 4096 long applied by the consuming decode
+        # launch as it loads x: 5 launches per layer, and one rms-norm for the step's output
+        for l in range(L):
+            ws = layers[l % DISTINCT]
+            if l == 0:
+                mm(ws, "qkv", h, t["qkv"])
+            else:
+                pro(ws, "qkv", t["d"], t["qkv"], PRO_RMS_NORM, D)
+            pro(ws, "o", t["qkv"], t["o"], PRO_SUM3, 3 * D)
+            pro(ws, "gateup", t["o"], t["gateup"], PRO_RMS_NORM, D)
+            ctx.mul_rms_norm(t["gateup"], t["m"], M, FF, 2 * FF, 1e-6)
+            mm(ws, "down", t["m"], t["d"])
+        ctx.rms_norm(t["d"], h, M, D, 1e-6, BF16, BF16)
+
+    def timed(step):
+        step()
+        ctx.sync()
+        ctx.graph_begin()
+        step()
+        g = ctx.graph_end()
+        for _ in range(3):
+            ctx.graph_launch(g)
+        ctx.sync()
+        iters = 10
+        ctx.timer_record(8)
+        for _ in range(iters):
+            ctx.graph_launch(g)
+        ctx.timer_record(9)
+        ms = ctx.timer_elapsed_ms(8, 9) / iters
+        ctx.graph_destroy(g)
+        return ms
+
+    # one step each way from the same input: the step's output must agree (the fused rms-norm sums a row's squares
+    # in another order, so not bit for bit: the bar of the parity tests, 1e-2 of the largest output)
+    h0 = h.to_host((M, D), np.uint16)
+    step_separate()
+    out_sep = O.from_bf16(h.to_host((M, D), np.uint16)).astype(np.float64)
+    h.from_host(h0)
+    step_fused()
+    out_fus = O.from_bf16(h.to_host((M, D), np.uint16)).astype(np.float64)
+    h.from_host(h0)
+    dev = float(np.abs(out_fus - out_sep).max() / np.abs(out_sep).max())
+    verified = (f"output of a 32-layer step, fused against separate launches: max deviation {dev:.2e} of the largest output"
+                if np.isfinite(dev) and dev <= 1e-2 else f"FAILED: fused step deviates by {dev:.2e}")
+    ms_sep = timed(step_separate)
+    h.from_host(h0)
+    ms = timed(step_fused)
     nbytes = L * sum(alg_bytes(M, K, N) for _, N, K in shapes)
     gbs = nbytes / ms / 1e6
-    ctx.graph_destroy(g)
     for ws in layers:
         for (bw, bs, bb, _, _) in ws.values():
             bw.free(); bs.free(); bb.free()
     for b in list(t.values()) + [h]:
         b.free()
-    return {"workload": "32 layers x (qkv, sum3, o, rms-norm, gate/up, mul+rms-norm, down, rms-norm), M=8, one GPU, "
-                        "every launch consumes the previous one's output, one CUDA graph per step",
-            "ms_per_step": ms, "launches_per_step": L * 8, "algorithmic_GB": nbytes / 1e9, "GBps": gbs,
+    return {"workload": "32 layers x (qkv, o, gate/up, mul+rms-norm, down) + one rms-norm, M=8, one GPU: the dataflow "
+                        "qkv, sum3, o, rms-norm, gate/up, mul+rms-norm, down, rms-norm with sum3 and the 4096-wide rms-norms "
+                        "applied by the consuming decode launch as it loads x; every launch consumes the previous one's "
+                        "output, one CUDA graph per step",
+            "ms_per_step": ms, "launches_per_step": L * 5 + 1, "algorithmic_GB": nbytes / 1e9, "GBps": gbs,
+            "separate_launches": {"ms_per_step": ms_sep, "launches_per_step": L * 8, "GBps": nbytes / ms_sep / 1e6},
+            "verified": verified,
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"]}}
 
 

@@ -49,7 +49,9 @@ extern "C" {
 #endif
 
 #define LUX_CUDA_QUANT_MAGIC 0x4C515854u /* "LQXT" */
-#define LUX_CUDA_QUANT_VERSION 3u /* 2: symm_* and qmatmul_sharded_push appended; 3: sum3, mul_rms_norm */
+#define LUX_CUDA_PRO_RMS_NORM 1
+#define LUX_CUDA_PRO_SUM3 2
+#define LUX_CUDA_QUANT_VERSION 4u /* 2: symm_* and qmatmul_sharded_push appended; 3: sum3, mul_rms_norm; 4: qmatmul_pro */
 #define LUX_CUDA_QMM_KERNEL_NAME "lux.qmm.affine"
 #define LUX_CUDA_NCCL_UID_BYTES 128
 
@@ -210,6 +212,20 @@ typedef struct lux_gpu_quant_vtbl {
                             size_t ld);
     LuxBackendError (*mul_rms_norm)(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBackendBuffer* out, size_t rows,
                                     size_t cols, size_t ld, float eps);
+
+    /* --- decode matmul with one of those steps applied to x as the kernel loads it (version >= 4) ---
+     * y = prologue(x) . dequant(Wq)^T for M <= 8, bf16 x / scales / biases, in ONE launch:
+     *   LUX_CUDA_PRO_RMS_NORM: x' = rms_norm(x) per row (unit weight, eps; rounded to bf16 as op_rms_norm_f32's
+     *                          output would be); x is [M][x_ld], its first K columns are used;
+     *   LUX_CUDA_PRO_SUM3:     x' = bf16(x[r][k] + x[r][K+k] + x[r][2K+k]), x is [M][x_ld], x_ld >= 3K.
+     * The same results as the step followed by qmatmul (bit for bit for SUM3; for RMS_NORM the row's sum of
+     * squares is accumulated in another order, which can move a normalised value by one bf16 step), without
+     * the launch and the round trip of x'.  NOT_SUPPORTED when the shape is not taken (M > 8, a K the decode
+     * kernel does not take, or for RMS_NORM a K longer than 16 k-blocks of 128 packed bytes): call the step and
+     * qmatmul instead. */
+    LuxBackendError (*qmatmul_pro)(LuxBackendContext* ctx, LuxBackendBuffer* x, LuxBackendBuffer* wq, LuxBackendBuffer* scales,
+                                   LuxBackendBuffer* biases, LuxBackendBuffer* y, int M, int K, int N, int bits, int group,
+                                   LuxBackendDtype y_dtype, int prologue, size_t x_ld, float eps);
 } lux_gpu_quant_vtbl;
 
 /* Entry points exported with default visibility. */

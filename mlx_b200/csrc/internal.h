@@ -165,6 +165,10 @@ struct QmmArgs {
     void* y;
     int M, K, N, bits, group;
     int x_dtype, sb_dtype, y_dtype;  // LuxBackendDtype values
+    // decode kernel, M <= 8, bf16: x is computed from the buffer as it is loaded (0: as it is; 1: rms-norm of each
+    // row with eps; 2: bf16(sum of the column blocks [0,K), [K,2K), [2K,3K)); x_ld = row stride of the buffer)
+    int pro = 0, x_ld = 0;
+    float eps = 0.0f;
 };
 
 // Column-sharded decode launch: where the finished output tiles go besides this rank's own copy of y.

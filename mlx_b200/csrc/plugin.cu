@@ -466,10 +466,16 @@ void fill_vtbl() {
 const LuxEmbeddedKernel g_kernels[] = {
     {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<4,m8>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},   // decode GEMV, 4-bit, M <= 8
     {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<4,m16>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},  // decode GEMV, 4-bit, M <= 16
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<4,m8,rms>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},   // x = rms-norm of the buffer, applied as it is loaded
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<4,m8,sum3>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},  // x = sum of three column blocks
     {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<8,m8>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<8,m8,rms>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<8,m8,sum3>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<8,m16>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<4>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},       // prefill GEMM (tcgen05), M > 16
     {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<8>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<4,stream-k>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},  // the same, k-stages split evenly over the SMs
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<8,stream-k>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {LUX_CUDA_QMM_KERNEL_NAME, "qmv_simt", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},        // fp32 activations, odd K
     {"lux.qmm.dequantize", "dequantize", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {"lux.qmm.unpack", "unpack", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},

@@ -1156,11 +1156,11 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, void* workspace, int sm_count, cudaS
     p.ws_flags = static_cast<uint32_t*>(workspace);
     p.ws = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kWsFlagBytes);
     if (a.bits == 4) {
-        if (name) *name = "qmm_tc<4>";
+        if (name) *name = pl.streamk ? "qmm_tc<4,stream-k>" : "qmm_tc<4>";
         return pl.streamk ? launch_gemm_t<4, true>(tmap, tmap_w, p, pl, sm_count, stream)
                           : launch_gemm_t<4, false>(tmap, tmap_w, p, pl, sm_count, stream);
     }
-    if (name) *name = "qmm_tc<8>";
+    if (name) *name = pl.streamk ? "qmm_tc<8,stream-k>" : "qmm_tc<8>";
     return pl.streamk ? launch_gemm_t<8, true>(tmap, tmap_w, p, pl, sm_count, stream)
                       : launch_gemm_t<8, false>(tmap, tmap_w, p, pl, sm_count, stream);
 }

@@ -95,6 +95,8 @@ struct Params {
     int sb_bytes;            // bytes of scales per row per k-block: 2, 4, 8 or 16
     int ld, col0;            // y row stride and first column (elements): N and 0 unless the layer is column-sharded
     int x_early;             // x is not written by the previous kernel of the stream: it may be read before the wait for it
+    int x_ld;                // row stride of x in elements (K unless a prologue reads column blocks of a wider buffer)
+    float eps;               // of the rms-norm prologue
     long long peer_wait_ns;  // limit of a wait for a peer (column-sharded launches)
     ShardPush sp;            // sp.world > 1: the finished tiles are also stored into the peers' copies of y
 };
@@ -387,25 +389,72 @@ __device__ __forceinline__ void task_mma(const uint4 (&w)[2][2], const uint32_t 
 // x fragments of k-block kb for lane (g, t), in the order the unpack yields the weights.
 //   4-bit: fragment j = h*4+i covers k = kb*256 + h*128 + t*32 + i*8 + (0,4,1,5 | 2,6,3,7)
 //   8-bit: fragment j = h*2+i covers k = kb*128 + h*64  + t*16 + i*8 + (0,2,1,3 | 4,6,5,7)
-template <int BITS, int MT>
+// PRO: what x is -- 0: the buffer as it is; 1: its rms-norm, row by row (the caller scales the fragments, see
+// rms_scale); 2: bf16(a + b + c) of the three column blocks [0,K), [K,2K), [2K,3K) of a wider row (fp32 adds,
+// left to right, one rounding: the bits of the stand-alone sum3 kernel).
+__device__ __forceinline__ uint32_t add3_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
+    const float lo = __fadd_rn(__fadd_rn(__uint_as_float(a << 16), __uint_as_float(b << 16)), __uint_as_float(c << 16));
+    const float hi = __fadd_rn(__fadd_rn(__uint_as_float(a & 0xFFFF0000u), __uint_as_float(b & 0xFFFF0000u)), __uint_as_float(c & 0xFFFF0000u));
+    const __nv_bfloat162 r = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ uint4 ldg_nc_v4(const uint4* src) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src));
+    return v;
+}
+template <int BITS, int MT, int PRO>
 __device__ __forceinline__ void load_x_raw(const Params& p, int kb, int g, int t, uint4 (&xr)[MT][BITS == 4 ? 8 : 4]) {
     constexpr int XV = BITS == 4 ? 8 : 4;
     constexpr int KB = 1024 / BITS;
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
         const int m = mt * 8 + g;
-        const __nv_bfloat16* row = p.x + (size_t)m * p.K + kb * KB + t * (KB / 8);
+        const __nv_bfloat16* row = p.x + (size_t)m * (PRO == 0 ? p.K : p.x_ld) + kb * KB + t * (KB / 8);
 #pragma unroll
         for (int j = 0; j < XV; j++) {
             const int h = j / (XV / 2), i = j % (XV / 2);
             xr[mt][j] = make_uint4(0, 0, 0, 0);
             if (m < p.M) {
                 const uint4* src = reinterpret_cast<const uint4*>(row + h * (KB / 2) + i * 8);
-                asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(xr[mt][j].x), "=r"(xr[mt][j].y), "=r"(xr[mt][j].z), "=r"(xr[mt][j].w) : "l"(src));
+                if (PRO == 2) {
+                    const uint4 a = ldg_nc_v4(src), b = ldg_nc_v4(reinterpret_cast<const uint4*>(row + p.K + h * (KB / 2) + i * 8)),
+                                c = ldg_nc_v4(reinterpret_cast<const uint4*>(row + 2 * p.K + h * (KB / 2) + i * 8));
+                    xr[mt][j] = make_uint4(add3_bf16x2(a.x, b.x, c.x), add3_bf16x2(a.y, b.y, c.y), add3_bf16x2(a.z, b.z, c.z),
+                                           add3_bf16x2(a.w, b.w, c.w));
+                } else {
+                    xr[mt][j] = ldg_nc_v4(src);
+                }
             }
         }
     }
+}
+// rms-norm prologue: the sum of squares of this lane's fragments (fp32), and the fragments scaled and rounded
+// as the stand-alone rms-norm kernel does it: bf16(fl32(x * inv)).
+template <int XV>
+__device__ __forceinline__ float sumsq_frags(const uint4 (&xr)[XV]) {
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < XV; j++) {
+        const uint32_t w[4] = {xr[j].x, xr[j].y, xr[j].z, xr[j].w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xFFFF0000u);
+            ss = fmaf(lo, lo, ss);
+            ss = fmaf(hi, hi, ss);
+        }
+    }
+    return ss;
+}
+__device__ __forceinline__ uint32_t scale_bf16x2(uint32_t v, float inv) {
+    const __nv_bfloat162 r = __floats2bfloat162_rn(__fmul_rn(__uint_as_float(v << 16), inv), __fmul_rn(__uint_as_float(v & 0xFFFF0000u), inv));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <int XV>
+__device__ __forceinline__ void rms_scale(uint4 (&xr)[XV], float inv) {
+#pragma unroll
+    for (int j = 0; j < XV; j++)
+        xr[j] = make_uint4(scale_bf16x2(xr[j].x, inv), scale_bf16x2(xr[j].y, inv), scale_bf16x2(xr[j].z, inv), scale_bf16x2(xr[j].w, inv));
 }
 template <int BITS, int MT>
 __device__ __forceinline__ void permute_x(uint4 (&xr)[MT][BITS == 4 ? 8 : 4]) {
@@ -437,9 +486,11 @@ __device__ __forceinline__ bool scales_fast_ok4(uint32_t s00, uint32_t s01, uint
     return ((a | b) & 0x80008000u) == 0u;
 }
 
-// BITS: 4 | 8.  MT: number of 8-row blocks of x (M <= 8*MT).
-template <int BITS, int MT>
+// BITS: 4 | 8.  MT: number of 8-row blocks of x (M <= 8*MT).  PRO: prologue applied to x as it is loaded (load_x_raw;
+// MT == 1 only).
+template <int BITS, int MT, int PRO>
 __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_constant__ Params p) {
+    static_assert(PRO == 0 || MT == 1, "prologues are built for M <= 8");
     constexpr int XV = BITS == 4 ? 8 : 4;  // x fragments (uint4) per lane per k-block per 8-row block
     constexpr int KB = 1024 / BITS;        // weights per k-block (128 bytes per row)
     constexpr int E4 = MT * 32;            // float4 per partial
@@ -527,7 +578,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
     // fetch code and spill; they stay behind it.)
     constexpr bool kXFirst = MT == 1;
     uint4 xr[MT][XV];
-    if (kXFirst && p.x_early && has_work) load_x_raw<BITS, MT>(p, kb_lo + warp, g, t, xr);
+    if (kXFirst && p.x_early && has_work) load_x_raw<BITS, MT, PRO>(p, kb_lo + warp, g, t, xr);
 #pragma unroll
     for (int i = 0; i < D - 1; i++) fetch_next();
 
@@ -546,8 +597,30 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
         // (a relaxed store: it publishes no data of this kernel, only that the kernel has started)
         if (blockIdx.x == 0 && tid < p.sp.world && tid != p.sp.me) st_relaxed_sys(p.sp.flags[tid] + kFlagReady + p.sp.me, epoch);
     }
-    if (kXFirst && !p.x_early && has_work) load_x_raw<BITS, MT>(p, kb_lo + warp, g, t, xr);
+    if (kXFirst && !p.x_early && has_work) load_x_raw<BITS, MT, PRO>(p, kb_lo + warp, g, t, xr);
     bool x_loaded = kXFirst;  // (of the first run)
+    // rms-norm prologue.  The host launches it only when every warp has at most one k-block and K is not split:
+    // the fragments just loaded by the 16 warps are then the whole of x, each lane holding 1/4 of a k-block of
+    // row g.  Sum of squares per row: the four lanes of a row in the warp, then the warps in order through shared
+    // memory; every lane ends up with the factor of its row.
+    float rms_inv = 1.0f;
+    if (PRO == 1) {
+        __shared__ float s_rms[kWarps][8];
+        if (!has_work) {
+#pragma unroll
+            for (int j = 0; j < XV; j++) xr[0][j] = make_uint4(0, 0, 0, 0);
+        }
+        float ss = sumsq_frags<XV>(xr[0]);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        if (t == 0) s_rms[warp][g] = ss;
+        __syncthreads();
+        float tot = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) tot += s_rms[w][g];
+        rms_inv = __fdiv_rn(1.0f, sqrtf(__fadd_rn(__fdiv_rn(tot, (float)p.K), p.eps)));
+        rms_scale<XV>(xr[0], rms_inv);
+    }
 
     uint32_t src_c = ring_lo;  // stage of the task computed next (this lane's slot)
     uint32_t sboff[2][2];      // byte offsets of this lane's scales inside a stage, by row half r and piece h
@@ -558,7 +631,10 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
 #pragma unroll 1
             for (int kb = kb_lo + warp; kb < kb_hi; kb += kWarps) {
                 fetch_next();  // (the run's first fetch goes out ahead of the x loads)
-                if (!x_loaded) load_x_raw<BITS, MT>(p, kb, g, t, xr);
+                if (!x_loaded) {
+                    load_x_raw<BITS, MT, PRO>(p, kb, g, t, xr);
+                    if (PRO == 1) rms_scale<XV>(xr[0], rms_inv);
+                }
                 x_loaded = false;
                 permute_x<BITS, MT>(xr);
                 if (MT == 2 && kX1Shared) {
@@ -705,9 +781,9 @@ bool make_plan(const QmmArgs& a, int sm_count, Plan* pl, bool sharded = false) {
     return true;
 }
 
-template <int BITS, int MT>
+template <int BITS, int MT, int PRO>
 cudaError_t launch_t(const Params& p, const Plan& pl, cudaStream_t stream, bool overlap_prev) {
-    auto kern = qmv_mma_kernel<BITS, MT>;
+    auto kern = qmv_mma_kernel<BITS, MT, PRO>;
     // opt in to large dynamic shared memory (static + dynamic stay within the 227 KiB per-block limit)
     static std::atomic<size_t> attr_smem[64];
     int dev = 0;
@@ -788,6 +864,13 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
     p.yt_off = pl.yt_off;
     p.ld = a.N; p.col0 = 0;
     p.x_early = (!overlap_prev || x_stable) ? 1 : 0;
+    p.x_ld = a.pro ? a.x_ld : a.K;
+    p.eps = a.eps;
+    if (a.pro) {
+        // prologues: M <= 8; the rms-norm needs the whole of x in the first fragments of the CTA's warps
+        if (pl.mt != 1 || a.pro < 0 || a.pro > 2 || (a.pro == 1 && (pl.ks != 1 || pl.nkb > kWarps))) return cudaErrorNotSupported;
+        if ((a.x_ld & 7) || a.x_ld < (a.pro == 2 ? 3 * a.K : a.K)) return cudaErrorInvalidValue;
+    }
     p.error = nullptr;
     p.peer_wait_ns = peer_wait_limit_ns();
     if (push && push->world > 1) {
@@ -798,11 +881,15 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
         if (!p.error) return cudaErrorMemoryAllocation;
     }
     if (a.bits == 4) {
-        if (name) *name = pl.mt == 1 ? "qmv_mma<4,m8>" : "qmv_mma<4,m16>";
-        return pl.mt == 1 ? launch_t<4, 1>(p, pl, stream, overlap_prev) : launch_t<4, 2>(p, pl, stream, overlap_prev);
+        if (name) *name = pl.mt == 2 ? "qmv_mma<4,m16>" : a.pro == 1 ? "qmv_mma<4,m8,rms>" : a.pro == 2 ? "qmv_mma<4,m8,sum3>" : "qmv_mma<4,m8>";
+        if (pl.mt == 2) return launch_t<4, 2, 0>(p, pl, stream, overlap_prev);
+        return a.pro == 1 ? launch_t<4, 1, 1>(p, pl, stream, overlap_prev)
+             : a.pro == 2 ? launch_t<4, 1, 2>(p, pl, stream, overlap_prev) : launch_t<4, 1, 0>(p, pl, stream, overlap_prev);
     }
-    if (name) *name = pl.mt == 1 ? "qmv_mma<8,m8>" : "qmv_mma<8,m16>";
-    return pl.mt == 1 ? launch_t<8, 1>(p, pl, stream, overlap_prev) : launch_t<8, 2>(p, pl, stream, overlap_prev);
+    if (name) *name = pl.mt == 2 ? "qmv_mma<8,m16>" : a.pro == 1 ? "qmv_mma<8,m8,rms>" : a.pro == 2 ? "qmv_mma<8,m8,sum3>" : "qmv_mma<8,m8>";
+    if (pl.mt == 2) return launch_t<8, 2, 0>(p, pl, stream, overlap_prev);
+    return a.pro == 1 ? launch_t<8, 1, 1>(p, pl, stream, overlap_prev)
+         : a.pro == 2 ? launch_t<8, 1, 2>(p, pl, stream, overlap_prev) : launch_t<8, 1, 0>(p, pl, stream, overlap_prev);
 }
 
 

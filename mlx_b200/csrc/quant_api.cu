@@ -307,6 +307,60 @@ LuxBackendError mul_rms_norm(LuxBackendContext* ctx, LuxBackendBuffer* in, LuxBa
     return LUX_BACKEND_OK;
 }
 
+LuxBackendError qmatmul_pro(LuxBackendContext* ctx, LuxBackendBuffer* x, LuxBackendBuffer* wq, LuxBackendBuffer* scales,
+                            LuxBackendBuffer* biases, LuxBackendBuffer* y, int M, int K, int N, int bits, int group,
+                            LuxBackendDtype y_dtype, int prologue, size_t x_ld, float eps) {
+    Context* c = as_ctx(ctx);
+    Buffer *bx = as_buf(x), *bw = as_buf(wq), *bs = as_buf(scales), *bb = as_buf(biases), *by = as_buf(y);
+    if (!c || !bx || !bw || !bs || !bb || !by || M < 0 || N < 0) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    LuxBackendError fe = check_format(K, bits, group);
+    if (fe != LUX_BACKEND_OK) return fe;
+    const size_t ys = dtype_size(y_dtype);
+    const size_t span = prologue == LUX_CUDA_PRO_SUM3 ? (size_t)3 * K : (size_t)K;
+    if (!ys || (prologue != LUX_CUDA_PRO_RMS_NORM && prologue != LUX_CUDA_PRO_SUM3) || x_ld < span || (x_ld & 7) ||
+        x_ld > (size_t)INT32_MAX) {
+        set_last_error("qmatmul_pro: prologue must be RMS_NORM or SUM3, x_ld a multiple of 8 that holds the columns read");
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    }
+    if (M == 0 || N == 0) return LUX_BACKEND_OK;
+    if (((size_t)(M - 1) * x_ld + span) * 2 > bx->bytes || (size_t)N * K * bits / 8 > bw->bytes ||
+        (size_t)N * (K / group) * 2 > bs->bytes || (size_t)N * (K / group) * 2 > bb->bytes || (size_t)M * N * ys > by->bytes) {
+        set_last_error("qmatmul_pro: a buffer is smaller than its shape needs");
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    }
+    if (((uintptr_t)bx->ptr | (uintptr_t)bw->ptr | (uintptr_t)bs->ptr | (uintptr_t)bb->ptr | (uintptr_t)by->ptr) & 15) {
+        set_last_error("qmatmul_pro: buffers must be 16-byte aligned");
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    }
+    std::lock_guard<std::mutex> lk(c->mu);
+    DeviceGuard g(c->dev->device());
+    QmmArgs a{bx->ptr, (const uint32_t*)bw->ptr, bs->ptr, bb->ptr, by->ptr, M, K, N, bits, group,
+              (int)LUX_DTYPE_BFLOAT16, (int)LUX_DTYPE_BFLOAT16, (int)y_dtype};
+    a.pro = prologue;
+    a.x_ld = (int)x_ld;
+    a.eps = eps;
+    if (M > 8 || !qmv_mma_supported(a)) {
+        set_last_error("qmatmul_pro: shape not taken by the decode kernel with a prologue (M <= 8, K as qmatmul's decode path)");
+        return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    }
+    LuxBackendError le = ensure_qmv_workspace(c, qmv_mma_workspace_bytes(a, c->dev->sm_count));
+    if (le != LUX_BACKEND_OK) return le;
+    const char* name = "";
+    // (x is the output of the launch before: never read ahead of the wait for it)
+    cudaError_t e = launch_qmv_mma(a, c->qmv_ws->ptr, c->dev->sm_count, c->stream, &name, decode_may_overlap(c, a), nullptr, false);
+    if (e == cudaErrorNotSupported) {
+        cudaGetLastError();
+        set_last_error("qmatmul_pro: the rms-norm prologue needs K within 16 k-blocks of 128 packed bytes and no K split");
+        return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    }
+    if (e != cudaSuccess) return map_cuda_error(e, name);
+    c->launches++;
+    note_decode_launch(c, a);
+    c->last_kernel = name;
+    bx->last_stream = bw->last_stream = bs->last_stream = bb->last_stream = by->last_stream = c->stream;
+    return LUX_BACKEND_OK;
+}
+
 // --- buffer interop ---------------------------------------------------------
 void* buffer_device_ptr(LuxBackendContext*, LuxBackendBuffer* buf) {
     Buffer* b = as_buf(buf);
@@ -503,6 +557,7 @@ void fill_quant() {
     fill_symm_entries(&g_quant);
     g_quant.sum3 = sum3;
     g_quant.mul_rms_norm = mul_rms_norm;
+    g_quant.qmatmul_pro = qmatmul_pro;
 }
 
 }  // namespace

@@ -137,10 +137,13 @@ class QuantVtbl(C.Structure):  # include/lux_cuda_quant.h: lux_gpu_quant_vtbl
         # version >= 3
         ("sum3", _fn(_i, _vp, _vp, _vp, _sz, _sz, _sz)),
         ("mul_rms_norm", _fn(_i, _vp, _vp, _vp, _sz, _sz, _sz, C.c_float)),
+        # version >= 4
+        ("qmatmul_pro", _fn(_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _sz, C.c_float)),
     ]
 
 
 SYMM_HANDLE_BYTES = 96  # LUX_CUDA_SYMM_HANDLE_BYTES
+PRO_RMS_NORM, PRO_SUM3 = 1, 2  # LUX_CUDA_PRO_*: prologues of qmatmul_pro
 
 
 EXPORTED_SYMBOLS = ("lux_gpu_backend_init", "lux_gpu_cuda_quant_vtbl", "lux_gpu_cuda_abi_layout",
@@ -370,6 +373,11 @@ class Context:
     def mul_rms_norm(self, src, dst, rows, cols, ld, eps):
         """dst = rms_norm(bf16(src[r][c] * src[r][cols+c])) per row (bf16, fp32 math)."""
         self.plugin.check(self.plugin.quant.mul_rms_norm(self.handle, src.handle, dst.handle, rows, cols, ld, eps), "mul_rms_norm")
+
+    def qmatmul_pro(self, x, wq, scales, biases, y, M, K, N, bits, group, y_dtype, prologue, x_ld, eps=0.0):
+        """y = prologue(x) . dequant(Wq)^T in one decode launch (M <= 8, bf16): PRO_RMS_NORM | PRO_SUM3."""
+        self.plugin.check(self.plugin.quant.qmatmul_pro(self.handle, x.handle, wq.handle, scales.handle, biases.handle, y.handle,
+                                                        M, K, N, bits, group, y_dtype, prologue, x_ld, eps), "qmatmul_pro")
 
     def timer_record(self, slot):
         self.plugin.check(self.plugin.quant.timer_record(self.handle, slot), "timer_record")

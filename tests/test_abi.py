@@ -61,7 +61,7 @@ def test_descriptor_and_layout():
 def test_quant_table():
     p = mlx_b200.Plugin(require_gpu=False)
     q = p.quant
-    assert q.magic == P.QUANT_MAGIC and q.version == 3 and q.size == C.sizeof(P.QuantVtbl)
+    assert q.magic == P.QUANT_MAGIC and q.version == 4 and q.size == C.sizeof(P.QuantVtbl)
     getter = p.lib.lux_gpu_cuda_quant_vtbl()
     assert C.addressof(getter.contents) == p.vtbl._reserved[0]
     for name, _ in P.QuantVtbl._fields_[4:]:
@@ -116,6 +116,7 @@ def test_tensor_op_slots_are_filled_and_reject_null():
     assert v.op_rms_norm_f32(None, None, None, None, 1, 4, 1e-5) == P.ERR_INVALID
     assert p.quant.sum3(None, None, None, 1, 4, 12) == P.ERR_INVALID
     assert p.quant.mul_rms_norm(None, None, None, 1, 4, 8, 1e-6) == P.ERR_INVALID
+    assert p.quant.qmatmul_pro(None, None, None, None, None, None, 1, 64, 1, 4, 64, 0, P.PRO_SUM3, 192, 0.0) == P.ERR_INVALID
 
 
 STUB_SRC = r"""
@@ -175,7 +176,8 @@ def test_kernel_registry_hook():
     assert reg.backend == b"cuda" and reg.count >= 7
     entries = [(reg.kernels[i].name.decode(), reg.kernels[i].entry_point.decode(), reg.kernels[i].lang) for i in range(reg.count)]
     variants = {e for n, e, _ in entries if n == "lux.qmm.affine"}
-    assert {"qmv_mma<4,m8>", "qmv_mma<4,m16>", "qmv_mma<8,m8>", "qmv_mma<8,m16>", "qmm_tc<4>", "qmm_tc<8>", "qmv_simt"} <= variants
+    assert {"qmv_mma<4,m8>", "qmv_mma<4,m16>", "qmv_mma<8,m8>", "qmv_mma<8,m16>", "qmm_tc<4>", "qmm_tc<8>", "qmm_tc<4,stream-k>",
+            "qmm_tc<8,stream-k>", "qmv_mma<4,m8,rms>", "qmv_mma<4,m8,sum3>", "qmv_simt"} <= variants
     assert all(lang == 1 for _, _, lang in entries)  # LUX_KERNEL_LANG_CUDA
 
 

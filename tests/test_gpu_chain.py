@@ -201,3 +201,57 @@ def test_decode_is_repeatable(ctx, oracle, M, K, N, bits, group):
     for h in (bx, bw, bs, bb, *ys):
         h.free()
     assert bad == 0, f"{bad} of 320 launches differed from the first"
+
+
+@pytest.mark.parametrize("M,K,N,bits,group", [(8, 4096, 512, 4, 64), (3, 2048, 96, 8, 128), (1, 1024, 1030, 4, 32)])
+def test_prologues_equal_the_separate_steps(ctx, oracle, M, K, N, bits, group):
+    """qmatmul_pro applies sum3 or the rms-norm to x while the decode kernel loads it.  sum3 is one rounding per
+    element, so the fused launch must give the bits of sum3 followed by qmatmul; the rms-norm accumulates the row's
+    sum of squares in another order than the stand-alone kernel (one bf16 step on a normalised value at most), so
+    the fused launch is held to the oracle's bar on the oracle's normalised input, and to the same bar against the
+    two-launch result."""
+    eps = 1e-6
+    wq, s, b = oracle.make_layer(N, K, bits, group, oracle.BF16, config_id=5, layer=K, proj=N)
+    bw, bs, bb = ctx.upload(wq), ctx.upload(s), ctx.upload(b)
+    wide = oracle.make_x(M, 3 * K, oracle.BF16, config_id=5, layer=K, tag=M)     # q | k | v of one launch
+    bwide = ctx.upload(wide)
+    a, y_two, y_one = ctx.empty((M, K), np.uint16), ctx.empty((M, N), np.uint16), ctx.empty((M, N), np.uint16)
+    # sum3
+    ctx.sum3(bwide, a, M, K, 3 * K)
+    ctx.qmatmul(a, bw, bs, bb, y_two, M, K, N, bits, group, BF16, BF16, BF16)
+    ctx.qmatmul_pro(bwide, bw, bs, bb, y_one, M, K, N, bits, group, BF16, P.PRO_SUM3, 3 * K)
+    assert ctx.last_kernel().endswith("sum3>")
+    assert np.array_equal(y_one.to_host(), y_two.to_host())
+    t = oracle.qmatmul_truth(oracle.sum3(wide, K), wq, s, b, bits, group)
+    assert oracle.rel_err(y_one.to_host(), t)[0] <= oracle.TOL[oracle.BF16]
+    # rms-norm of the first K columns of the wide buffer (row stride 3K), and of a plain [M][K] buffer
+    x = np.ascontiguousarray(wide[:, :K])
+    ctx.rms_norm(ctx.upload(x), a, M, K, eps, BF16, BF16)
+    ctx.qmatmul(a, bw, bs, bb, y_two, M, K, N, bits, group, BF16, BF16, BF16)
+    t = oracle.qmatmul_truth(oracle.rms_norm(x, eps=eps), wq, s, b, bits, group)
+    for buf, ld in ((bwide, 3 * K), (ctx.upload(x), K)):
+        ctx.qmatmul_pro(buf, bw, bs, bb, y_one, M, K, N, bits, group, BF16, P.PRO_RMS_NORM, ld, eps)
+        assert ctx.last_kernel().endswith("rms>")
+        got = y_one.to_host()
+        assert oracle.rel_err(got, t)[0] <= oracle.TOL[oracle.BF16]
+        assert oracle.rel_err(got, oracle.from_bf16(y_two.to_host()).astype(np.float64))[0] <= oracle.TOL[oracle.BF16]
+    # repeated launches give the same bits
+    first = y_one.to_host()
+    for _ in range(10):
+        ctx.qmatmul_pro(bwide, bw, bs, bb, y_one, M, K, N, bits, group, BF16, P.PRO_RMS_NORM, 3 * K, eps)
+        assert np.array_equal(y_one.to_host(), first)
+
+
+def test_prologue_refuses_what_it_does_not_take(ctx, oracle, plugin):
+    K, N = 8192, 64
+    wq, s, b = oracle.make_layer(N, K, 4, 64, oracle.BF16, config_id=5, layer=9)
+    bw, bs, bb = ctx.upload(wq), ctx.upload(s), ctx.upload(b)
+    x16 = ctx.upload(oracle.make_x(16, K, oracle.BF16, config_id=5))
+    y = ctx.empty((16, N), np.uint16)
+    for M, pro in ((16, P.PRO_SUM3), (8, P.PRO_RMS_NORM)):   # more than 8 rows; K of 32 k-blocks (and split) for the norm
+        with pytest.raises(P.BackendError) as ei:
+            ctx.qmatmul_pro(x16, bw, bs, bb, y, M, K if pro == P.PRO_RMS_NORM else K // 4, N, 4, 64, BF16, pro, K, 1e-6)
+        assert ei.value.code == P.ERR_NOT_SUPPORTED, plugin.last_error()
+    with pytest.raises(P.BackendError) as ei:   # x_ld too short for three column blocks
+        ctx.qmatmul_pro(x16, bw, bs, bb, y, 8, K // 4, N, 4, 64, BF16, P.PRO_SUM3, K // 2)
+    assert ei.value.code == P.ERR_INVALID
