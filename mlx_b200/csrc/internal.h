@@ -105,6 +105,10 @@ struct Context {
     std::vector<Block*> qmv_ws_retired;
     // scratch of the prefill GEMM (partial accumulators of tiles shared between CTAs + their flags)
     Block* qmm_ws = nullptr;
+    // A kernel that gives up on a bounded wait says so here (page-locked host memory mapped into the device's
+    // address space, one word per context): the context's next sync / copy-to-host reads and clears it.
+    int* err_host = nullptr;
+    int* err_dev = nullptr;
     const char* last_kernel = "";
     std::atomic<uint64_t> launches{0};
     std::atomic<uint64_t> copies{0};  // memcpy / memset enqueues
@@ -169,6 +173,9 @@ struct QmmArgs {
     // row with eps; 2: bf16(sum of the column blocks [0,K), [K,2K), [2K,3K)); x_ld = row stride of the buffer)
     int pro = 0, x_ld = 0;
     float eps = 0.0f;
+    // where the kernels raise a time-out of one of their bounded waits: the calling context's word (device
+    // address of page-locked, mapped host memory); null: the word shared by the process
+    int* error = nullptr;
 };
 
 // Column-sharded decode launch: where the finished output tiles go besides this rank's own copy of y.
@@ -203,6 +210,7 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, void* workspace, int sm_count, cudaS
                           const ShardPush* push = nullptr);
 // non-zero once a kernel gave up on one of its bounded waits since the last call (clears it)
 int take_device_error();
+int take_context_error(Context* c);  // the context's own word, read and cleared in one atomic step
 int* device_error_word();  // where kernels raise it (null if the mapped word could not be set up)
 cudaError_t reset_peer_lost();    // on the current device: waits for peers are attempted again
 long long peer_wait_limit_ns();  // limit of a device-side wait for a peer rank (LUXCUDA_PEER_WAIT_MS, default 2000)

@@ -49,6 +49,21 @@ LuxBackendContext* create_context(int device_index) {
         delete c;
         return nullptr;
     }
+    {
+        // the context's error word (see Context::err_host); without it the kernels fall back to the process's word
+        DeviceGuard g(dev->device());
+        void* hp = nullptr;
+        void* dp = nullptr;
+        if (cudaHostAlloc(&hp, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess &&
+            cudaHostGetDevicePointer(&dp, hp, 0) == cudaSuccess) {
+            c->err_host = static_cast<int*>(hp);
+            *c->err_host = 0;
+            c->err_dev = static_cast<int*>(dp);
+        } else {
+            if (hp) cudaFreeHost(hp);
+            cudaGetLastError();
+        }
+    }
     return reinterpret_cast<LuxBackendContext*>(c);
 }
 
@@ -64,6 +79,7 @@ void destroy_context(LuxBackendContext* ctx) {
     if (c->qmv_ws) c->dev->release(c->qmv_ws, c->stream);
     for (Block* b : c->qmv_ws_retired) c->dev->release(b, c->stream);
     if (c->qmm_ws) c->dev->release(c->qmm_ws, c->stream);
+    if (c->err_host) cudaFreeHost(c->err_host);
     c->dev->release_stream(c->stream);
     c->magic = 0;
     delete c;
@@ -102,7 +118,7 @@ LuxBackendError sync(LuxBackendContext* ctx) {
     if (!c) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
     DeviceGuard g(c->dev->device());
     LUX_CUDA_TRY(cudaStreamSynchronize(c->stream));
-    if (take_device_error()) {
+    if (take_context_error(c) | take_device_error()) {
         set_last_error("a kernel timed out on an internal wait and returned early; results are invalid");
         return LUX_BACKEND_ERROR_INTERNAL;
     }
@@ -189,7 +205,7 @@ LuxBackendError buffer_copy_to_host(LuxBackendContext* ctx, LuxBackendBuffer* bu
     c->copies++;
     LUX_CUDA_TRY(cudaMemcpyAsync(dst, b->ptr, n, cudaMemcpyDeviceToHost, c->stream));
     LUX_CUDA_TRY(cudaStreamSynchronize(c->stream));
-    if (take_device_error()) {
+    if (take_context_error(c) | take_device_error()) {
         set_last_error("a kernel timed out on an internal wait and returned early; results are invalid");
         return LUX_BACKEND_ERROR_INTERNAL;
     }

@@ -1099,7 +1099,7 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, void* workspace, int sm_count, cudaS
                           const ShardPush* push) {
     GemmPlan pl;
     if (!make_gemm_plan(a, sm_count, &pl) || !workspace || sm_count * sizeof(uint32_t) > kWsFlagBytes) return cudaErrorInvalidValue;
-    int* err = error_word();
+    int* err = a.error ? a.error : error_word();
     if (!err) return cudaErrorMemoryAllocation;
     // x as a 2-D tensor [M rows][K], boxes of 64 elements (128 bytes) x bm rows, 128-byte swizzle;
     // rows past M are filled with zeros by the copy engine
@@ -1176,12 +1176,15 @@ int* device_error_word() {
     return derr;
 }
 
+int take_context_error(Context* c) {
+    if (!c || !c->err_host) return 0;
+    return __atomic_exchange_n(c->err_host, 0, __ATOMIC_ACQ_REL);
+}
+
 // Non-zero once a kernel has given up on a bounded wait; reading clears it.
 int take_device_error() {
     if (!g_error_host || !*g_error_host) return 0;
-    const int v = *g_error_host;
-    *g_error_host = 0;
-    return v;
+    return __atomic_exchange_n(g_error_host, 0, __ATOMIC_ACQ_REL);
 }
 
 }  // namespace luxcuda

@@ -877,7 +877,7 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
         if (push->world > kMaxShardWorld || (a.N & 15)) return cudaErrorInvalidValue;  // whole 16-column tiles only
         p.sp = *push;
         p.ld = push->ld; p.col0 = push->col0;
-        p.error = device_error_word();
+        p.error = a.error ? a.error : device_error_word();
         if (!p.error) return cudaErrorMemoryAllocation;
     }
     if (a.bits == 4) {

@@ -193,6 +193,7 @@ LuxBackendError qmatmul(LuxBackendContext* ctx, LuxBackendBuffer* x, LuxBackendB
     DeviceGuard g(c->dev->device());
     QmmArgs a{bx->ptr, (const uint32_t*)bw->ptr, bs->ptr, bb->ptr, by->ptr, M, K, N, bits, group,
               (int)x_dtype, (int)sb_dtype, (int)y_dtype};
+    a.error = c->err_dev;
     LuxBackendError r = qmatmul_on_stream(c, a);
     bx->last_stream = bw->last_stream = bs->last_stream = bb->last_stream = by->last_stream = c->stream;
     return r;
@@ -337,6 +338,7 @@ LuxBackendError qmatmul_pro(LuxBackendContext* ctx, LuxBackendBuffer* x, LuxBack
     QmmArgs a{bx->ptr, (const uint32_t*)bw->ptr, bs->ptr, bb->ptr, by->ptr, M, K, N, bits, group,
               (int)LUX_DTYPE_BFLOAT16, (int)LUX_DTYPE_BFLOAT16, (int)y_dtype};
     a.pro = prologue;
+    a.error = c->err_dev;
     a.x_ld = (int)x_ld;
     a.eps = eps;
     if (M > 8 || !qmv_mma_supported(a)) {

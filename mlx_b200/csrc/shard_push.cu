@@ -202,6 +202,7 @@ LuxBackendError qmatmul_sharded_push(LuxCudaSymmBuffer* sb, LuxBackendBuffer* x,
     }
     QmmArgs a{bx->ptr, (const uint32_t*)bw->ptr, bs->ptr, bb->ptr, sb->view.ptr, M, K, Nl, bits, group,
               LUX_DTYPE_BFLOAT16, LUX_DTYPE_BFLOAT16, (int)y_dtype};
+    a.error = c->err_dev;
     std::lock_guard<std::mutex> lk(c->mu);
     DeviceGuard g(c->dev->device());
     if (M > 16) {
@@ -220,7 +221,7 @@ LuxBackendError qmatmul_sharded_push(LuxCudaSymmBuffer* sb, LuxBackendBuffer* x,
         BarrierArgs ba;
         ba.world = sb->world;
         ba.me = sb->rank;
-        ba.error = device_error_word();
+        ba.error = c->err_dev ? c->err_dev : device_error_word();
         ba.limit_ns = peer_wait_limit_ns();
         for (int r = 0; r < kMaxShardWorld; r++) ba.flags[r] = nullptr;
         for (int r = 0; r < sb->world; r++) {
