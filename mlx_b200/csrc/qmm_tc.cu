@@ -994,6 +994,330 @@ qmm_tc_tiles_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     }
 }
 
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster share one MMA stream ------------------------------------
+// The MMA is 256 rows of W (128 from each CTA's tensor memory) x bm rows of x, of which each CTA stages half in
+// its shared memory; the thread that issues it (in CTA 0) issues for both tensor cores, so the instruction
+// stream that bounds a stage is halved per SM, and x takes half the shared memory per stage.
+constexpr int kStagesP = 4;                   // k-stages in flight: x halves in shared memory, A in TMEM
+constexpr int kPairBBytes = (kMaxBM / 2) * 128;  // one sub-block of this CTA's half of x
+static_assert(kDqGroups <= kStagesP, "parity waits would alias");
+static_assert(kAColBase + kStagesP * kAColsPerSlot <= kTmemCols, "A ring does not fit");
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // a shared::cluster address with this bit cleared is CTA 0's copy
+struct PairSmemLayout {
+    uint64_t full[kStagesP], empty[kStagesP], wfull[kDqGroups], tmem_full, tmem_empty;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t ncols) {  // whole warp, the same warp in both CTAs
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(dst_smem)), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// arrive on CTA 0's copy of a barrier (from either CTA)
+__device__ __forceinline__ void mbar_arrive_cta0(uint64_t* b) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(s32(b) & kPeerBitMask) : "memory");
+}
+// arrives once on the barrier at this offset in both CTAs when the MMAs issued so far have completed
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(s32(bar)), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t z = 0;
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+        "  tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p; }"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z) : "memory");
+}
+// this CTA's half of an x tile into its own shared memory, completion counted on CTA 0's barrier (no multicast)
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(s32(dst)), "l"(map), "r"(x), "r"(y), "r"(s32(bar) & kPeerBitMask) : "memory");
+}
+
+template <int BITS>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+qmm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+              const __grid_constant__ GemmParams p) {
+    constexpr int WPS = kBK * BITS / 32;  // packed words per row per stage: 8 | 16
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* sB = smem;  // [kStagesP][kSub][bm/2 rows][128 B], swizzled (TMA): this CTA's half of the x tile
+    const uint32_t b_bytes = (uint32_t)(p.bm >> 1) * 128;
+    unsigned char* sW = sB + (size_t)kStagesP * kSub * kPairBBytes;  // [kDqGroups][128 rows][64 B], 64-byte swizzle (TMA)
+    PairSmemLayout* sl = reinterpret_cast<PairSmemLayout*>(sW + (size_t)kDqGroups * kWUnitBytes);
+    uint32_t rank;  // of this CTA in its pair: 0 issues the MMAs of both
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int cl = (int)(blockIdx.x >> 1), ncl = (int)(gridDim.x >> 1);
+    volatile int* abort_flag = &sl->abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nks = p.K / kBK;                  // 64-weight sub-blocks along K
+    const int nst = (nks + kSub - 1) / kSub;    // pipeline stages per tile
+    // A pair takes two neighbouring 128-row tiles of W (CTA `rank` the tile 2*np + rank) against the same rows of x;
+    // with an odd number of W tiles the last pair's second CTA works on rows past N (zeros in, nothing out).
+    const int total_tiles = ((p.n_tiles + 1) >> 1) * p.m_tiles;  // pair tiles
+    auto n0_of = [&](int pt) { return ((pt / p.m_tiles) * 2 + (int)rank) * kTileN; };
+
+    if (tid == 0) {
+        for (int s = 0; s < kStagesP; s++) {
+            // (used in CTA 0 only) the four warps of the owning group in either CTA + CTA 0's TMA producer, whose
+            // byte count covers both CTAs' halves of x
+            mbar_init(&sl->full[s], 4 + 4 + 1);
+            mbar_init(&sl->empty[s], 1);  // one tcgen05.commit, multicast to both CTAs
+        }
+        for (int g = 0; g < kDqGroups; g++) mbar_init(&sl->wfull[g], 1);  // the group leader's expect_tx
+        mbar_init(&sl->tmem_full, 1);
+        mbar_init(&sl->tmem_empty, 2 * kEpiWarps);  // (used in CTA 0 only) the epilogue warps of both CTAs
+        sl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kMmaWarp) tmem_alloc_pair(&sl->tmem_base, kTmemCols);  // the same warp of both CTAs
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();  // the peer's barriers are initialised before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = sl->tmem_base;
+
+    if (warp == kTmaWarp) {
+        // ---------------- TMA producer: x tiles ----------------
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_x) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_w) : "memory");
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = cl; tile < total_tiles && ok; tile += ncl) {
+                const int m0 = (tile % p.m_tiles) * p.bm + (int)rank * (p.bm >> 1);  // this CTA's half of the rows of x
+                for (int st = 0; st < nst; st++, it++) {
+                    const int sb = it % kStagesP;
+                    const uint32_t ph = (it / kStagesP) & 1;
+                    const int nsub = min(kSub, nks - st * kSub);
+                    if (!mbar_wait(&sl->empty[sb], ph ^ 1, abort_flag)) { ok = false; break; }
+                    // both halves complete on CTA 0's barrier, which expects the bytes of both
+                    if (rank == 0) mbar_expect_tx(&sl->full[sb], 2 * b_bytes * nsub);
+                    for (int u = 0; u < nsub; u++)
+                        tma_load_2d_pair(sB + ((size_t)sb * kSub + u) * kPairBBytes, &tmap_x, (st * kSub + u) * kBK, m0, &sl->full[sb]);
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = umma_idesc(2 * kTileN, p.bm);  // 256 rows of W over the two CTAs x bm rows of x
+            uint32_t tile_i = 0, slot = 0, phase = 0;
+            const uint64_t db0 = umma_desc_sw128(s32(sB));
+            bool ok = true;
+            for (int tile = cl; tile < total_tiles && ok; tile += ncl, tile_i++) {
+                if (!mbar_wait(&sl->tmem_empty, (tile_i & 1) ^ 1, abort_flag)) break;
+                tc_fence_after();
+                for (int st = 0; st < nst; st++) {
+                    const int nsub = min(kSub, nks - st * kSub);
+                    if (!mbar_wait_spin(&sl->full[slot], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    for (int u = 0; u < nsub; u++) {
+                        const uint64_t db = db0 + (uint64_t)(slot * kSub + u) * (kPairBBytes >> 4);
+                        const uint32_t a_tmem = tmem_base + kAColBase + slot * kAColsPerSlot + u * kAColsPerSub;
+#pragma unroll
+                        for (int kk = 0; kk < kBK / 16; kk++)  // 16 k = 8 TMEM columns of A, 32 bytes of each B row
+                            tc_mma_ts_pair(tmem_base, a_tmem + 8 * kk, db + 2 * kk, idesc, (st | u | kk) != 0 ? 1u : 0u);
+                    }
+                    tc_commit_pair(&sl->empty[slot]);  // arrives, in both CTAs, when the MMAs above have consumed their operands
+                    if (++slot == kStagesP) { slot = 0; phase ^= 1; }
+                }
+                if (ok) tc_commit_pair(&sl->tmem_full);
+            }
+        }
+    } else if (warp >= kEpiWarps) {
+        // ---------------- dequantisers: group grp owns the stages = grp (mod kDqGroups); thread owns row n0 + r ----------------
+        constexpr int UPS = BITS == 8 ? 2 : 1;  // weight units (128 rows x 64 packed bytes) per pipeline stage
+        const int q = warp & 3, grp = (warp - kEpiWarps) >> 2;
+        const int r = q * 32 + lane;
+        const bool leader = (q == 0 && lane == 0);
+        const int bar_id = 1 + grp;  // named barrier of the group (0 is __syncthreads)
+        const int gpr = p.K >> p.gshift;
+        const int ng_full = (kSub * kBK) >> p.gshift;  // scale groups per full stage: 4, 2 or 1
+        const bool vec_ok = (gpr % ng_full) == 0;      // then a stage's scales of one row are one aligned vector
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + kAColBase;
+        // this group's weight unit in shared memory; row r is 64 bytes, its 16-byte chunk c sits at c ^ ((r >> 1) & 3)
+        const unsigned char* wrow = sW + (size_t)grp * kWUnitBytes + r * 64;
+        const uint32_t wsw = (uint32_t)(r >> 1) & 3u;
+        uint64_t* wbar = &sl->wfull[grp];
+        uint32_t wround = 0;  // units of this group consumed so far
+
+        struct Cur { int tile, st; uint32_t it0; };  // an owned stage: tile, stage in the tile, stage counter at tile start
+        auto settle = [&](Cur& c) {  // first stage of c.tile owned by the group; tiles without one are skipped
+            while (c.tile < total_tiles) {
+                c.st = (int)((grp + kDqGroups - c.it0 % kDqGroups) % kDqGroups);
+                if (c.st < nst) break;
+                c.tile += ncl;
+                c.it0 += nst;
+            }
+        };
+        auto advance = [&](Cur& c) {
+            c.st += kDqGroups;
+            if (c.st >= nst) {
+                c.tile += ncl;
+                c.it0 += nst;
+                settle(c);
+            }
+        };
+        auto issue = [&](const Cur& c, int u) {  // leader: bring unit u of stage c into the group's slot
+            mbar_expect_tx(wbar, kWUnitBytes);
+            tma_load_2d(const_cast<unsigned char*>(sW) + (size_t)grp * kWUnitBytes, &tmap_w,
+                        c.st * (kSub * kBK * BITS / 8) + u * 64, n0_of(c.tile), wbar);
+        };
+        uint32_t sp[2], bp[2];  // scales / biases of the next owned stage of this row, bf16 pairs in group order
+        auto fetch_sb = [&](const Cur& c) {
+            const int n = min(n0_of(c.tile) + r, p.N - 1);
+            const int g0 = (c.st * kSub * kBK) >> p.gshift;
+            const int ng = min(gpr - g0, ng_full);
+            const uint16_t* sr = reinterpret_cast<const uint16_t*>(p.scales) + (size_t)n * gpr + g0;
+            const uint16_t* br = reinterpret_cast<const uint16_t*>(p.biases) + (size_t)n * gpr + g0;
+            sp[1] = 0; bp[1] = 0;
+            if (vec_ok && ng == ng_full && ng == 4) {
+                asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(sp[0]), "=r"(sp[1]) : "l"(sr));
+                asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(bp[0]), "=r"(bp[1]) : "l"(br));
+            } else if (vec_ok && ng == ng_full && ng == 2) {
+                asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(sp[0]) : "l"(sr));
+                asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(bp[0]) : "l"(br));
+            } else {
+                sp[0] = ldg_u16(sr); bp[0] = ldg_u16(br);
+                if (ng > 1) { sp[0] |= ldg_u16(sr + 1) << 16; bp[0] |= ldg_u16(br + 1) << 16; }
+                if (ng > 2) { sp[1] = ldg_u16(sr + 2); bp[1] = ldg_u16(br + 2); }
+                if (ng > 3) { sp[1] |= ldg_u16(sr + 3) << 16; bp[1] |= ldg_u16(br + 3) << 16; }
+            }
+        };
+
+        Cur cur{cl, 0, 0u};
+        settle(cur);
+        if (cur.tile < total_tiles) {
+            if (leader) issue(cur, 0);
+            fetch_sb(cur);
+        }
+        bool ok = true;
+        while (cur.tile < total_tiles) {
+            Cur nxt = cur;
+            advance(nxt);
+            const uint32_t it = cur.it0 + cur.st;
+            const int sa = it % kStagesP;
+            const int nsub = min(kSub, nks - cur.st * kSub);
+            const uint32_t sc[2] = {sp[0], sp[1]}, bc[2] = {bp[0], bp[1]};
+            if (nxt.tile < total_tiles) fetch_sb(nxt);  // three stages ahead of its use
+            uint32_t w[16];
+            bool group_fail = false;
+#pragma unroll
+            for (int u = 0; u < kSub; u++) {
+                if (u >= nsub) break;
+                if (UPS == 2 || u == 0) {
+                    const bool got = ok && mbar_wait(wbar, wround & 1, abort_flag);
+                    wround++;
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(wrow + ((c ^ wsw) << 4));
+                        w[4 * c] = v.x; w[4 * c + 1] = v.y; w[4 * c + 2] = v.z; w[4 * c + 3] = v.w;
+                    }
+                    // The reads above are generic-proxy accesses, the refill is an async-proxy write: the proxy
+                    // fence orders the two (without it a read still in the load pipe could see the next unit).
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    // every thread of the group has its bytes: the slot may be refilled.  The same barrier makes
+                    // a failed wait a decision of the whole group, so nobody is left waiting at it.
+                    ok = group_all(bar_id, got);
+                    if (!ok) { group_fail = true; break; }
+                    if (leader) {
+                        if (UPS == 2 && u + 1 < nsub) issue(cur, u + 1);
+                        else if (nxt.tile < total_tiles) issue(nxt, 0);
+                    }
+                }
+                // scales of the two 32-weight halves of this sub-block
+                const int h0 = (2 * u * 32) >> p.gshift, h1 = ((2 * u + 1) * 32) >> p.gshift;
+                const uint32_t s0 = (sc[h0 >> 1] >> ((h0 & 1) * 16)) & 0xFFFFu, b0 = (bc[h0 >> 1] >> ((h0 & 1) * 16)) & 0xFFFFu;
+                const uint32_t s1 = (sc[h1 >> 1] >> ((h1 & 1) * 16)) & 0xFFFFu, b1 = (bc[h1 >> 1] >> ((h1 & 1) * 16)) & 0xFFFFu;
+                uint32_t out[32];
+                const uint32_t (&ws)[WPS] = *reinterpret_cast<const uint32_t (*)[WPS]>(&w[BITS == 4 ? 8 * u : 0]);
+                if (scale_fast_ok(s0) && scale_fast_ok(s1)) dequant_row_stage<BITS, true>(ws, s0, b0, s1, b1, out);
+                else dequant_row_stage<BITS, false>(ws, s0, b0, s1, b1, out);  // whole-block branch: not if-converted
+                if (u == 0) {
+                    const bool freed = ok && mbar_wait(&sl->empty[sa], ((it / kStagesP) & 1) ^ 1, abort_flag);
+                    ok = __all_sync(0xFFFFFFFFu, freed);  // tcgen05.st below is warp-collective
+                    tc_fence_after();
+                }
+                __syncwarp();
+                if (ok) tmem_st32(lane_addr + sa * kAColsPerSlot + u * kAColsPerSub, out);
+            }
+            if (ok) {
+                tmem_st_wait();  // once per stage: both sub-blocks are in tensor memory
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cta0(&sl->full[sa]);  // one arrival per warp, on the barrier the MMA issuer waits at
+            } else if (!*abort_flag) {
+                *abort_flag = 1;
+            }
+            if (group_fail) break;  // decided by the whole group at its barrier
+            cur = nxt;                // a warp that failed alone goes on to the next barrier, where the group ends
+        }
+    } else {
+        // ---------------- epilogue: warp w reads TMEM lanes 32*(w%4).., half w/4 of the column blocks ----------------
+        const int q = warp & 3, half = warp >> 2;
+        const int nblk = (p.bm + 31) / 32, blk_lo = half ? (nblk + 1) / 2 : 0, blk_hi = half ? nblk : (nblk + 1) / 2;
+        uint32_t tile_i = 0;
+        for (int tile = cl; tile < total_tiles; tile += ncl, tile_i++) {
+            const int n = n0_of(tile) + q * 32 + lane;
+            const int m0 = (tile % p.m_tiles) * p.bm;
+            if (!mbar_wait(&sl->tmem_full, tile_i & 1, abort_flag)) break;
+            tc_fence_after();
+            // this thread: column n of y, rows m0 + c (32 consecutive n per warp: 64-byte row segments)
+            const int m_end = min(p.bm, p.M - m0);
+            for (int blk = blk_lo; blk < blk_hi; blk++) {
+                const int c0 = blk * 32;
+                uint32_t v[32];
+                __syncwarp();
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
+                if (n < p.N) {
+                    // column-sharded layers: the tile goes into every rank's copy of y (peer stores over NVLink)
+                    const size_t idx0 = (size_t)(m0 + c0) * p.ld + p.col0 + n;
+                    for (int dst = 0; dst < p.world; dst++) {
+                        if (p.y_bf16) {
+                            __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(p.y_all[dst]) + idx0;
+                            if (c0 + 32 <= m_end) {
+#pragma unroll
+                                for (int j = 0; j < 32; j++) yp[(size_t)j * p.ld] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    if (c0 + j < m_end) yp[(size_t)j * p.ld] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                            }
+                        } else {
+                            float* yp = reinterpret_cast<float*>(p.y_all[dst]) + idx0;
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (c0 + j < m_end) yp[(size_t)j * p.ld] = __uint_as_float(v[j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cta0(&sl->tmem_empty);
+        }
+    }
+    // ---------------- teardown ----------------
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();  // neither CTA leaves (or frees tensor memory) while the other may still reach into it
+    if (tid == 0 && sl->abort_flag) *p.error = 1;
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
 // ---- host side -------------------------------------------------------------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -1028,7 +1352,7 @@ int* error_word() {
 }
 
 struct GemmPlan {
-    int bm, m_tiles, n_tiles, streamk;
+    int bm, m_tiles, n_tiles, streamk, pair;
     size_t smem;
 };
 
@@ -1063,7 +1387,29 @@ bool make_gemm_plan(const QmmArgs& a, int sm_count, GemmPlan* pl) {
         pl->streamk = sk < whole && T * nst >= G;
         if (const char* env = getenv("LUXCUDA_QMM_SCHEDULE")) pl->streamk = env[0] == 's';  // "streamk" | "tiles" (experiments)
     }
+    // whole tiles on CTA pairs
+    pl->pair = !pl->streamk && (sm_count & 1) == 0 && getenv("LUXCUDA_QMM_PAIR") != nullptr;
+    if (pl->pair)
+        pl->smem = 1024 + (size_t)kStagesP * kSub * kPairBBytes + (size_t)kDqGroups * kWUnitBytes + sizeof(PairSmemLayout) + 64;
     return encode_tiled_fn() != nullptr;
+}
+
+template <int BITS>
+cudaError_t launch_gemm_pair_t(const CUtensorMap& tmap, const CUtensorMap& tmap_w, const GemmParams& p, const GemmPlan& pl, int sm_count, cudaStream_t stream) {
+    auto kern = qmm_tc_pair_kernel<BITS>;
+    static std::atomic<size_t> attr_smem[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_smem[dev & 63].load() < pl.smem) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+        if (e != cudaSuccess) return e;
+        attr_smem[dev & 63].store(pl.smem);
+    }
+    // one pair of CTAs per pair of SMs (the kernel carries its cluster shape), unless there are fewer pair tiles
+    const int pairs = ((pl.n_tiles + 1) / 2) * pl.m_tiles;
+    const int grid = 2 * std::min(sm_count / 2, pairs);
+    kern<<<grid, kNumThreads, pl.smem, stream>>>(tmap, tmap_w, p);
+    return cudaGetLastError();
 }
 
 template <int BITS, bool SK>
@@ -1106,7 +1452,7 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, void* workspace, int sm_count, cudaS
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)a.M};
     const cuuint64_t strides[1] = {(cuuint64_t)a.K * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)pl.bm};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)(pl.pair ? pl.bm / 2 : pl.bm)};  // (a CTA of a pair stages half the rows)
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = encode_tiled_fn()(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.x), dims, strides, box,
                                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1155,6 +1501,11 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, void* workspace, int sm_count, cudaS
     p.bm = pl.bm; p.n_tiles = pl.n_tiles; p.m_tiles = pl.m_tiles;
     p.ws_flags = static_cast<uint32_t*>(workspace);
     p.ws = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kWsFlagBytes);
+    if (pl.pair) {
+        if (name) *name = a.bits == 4 ? "qmm_tc<4,pairs>" : "qmm_tc<8,pairs>";
+        return a.bits == 4 ? launch_gemm_pair_t<4>(tmap, tmap_w, p, pl, sm_count, stream)
+                           : launch_gemm_pair_t<8>(tmap, tmap_w, p, pl, sm_count, stream);
+    }
     if (a.bits == 4) {
         if (name) *name = pl.streamk ? "qmm_tc<4,stream-k>" : "qmm_tc<4>";
         return pl.streamk ? launch_gemm_t<4, true>(tmap, tmap_w, p, pl, sm_count, stream)
