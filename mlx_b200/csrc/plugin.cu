@@ -492,6 +492,8 @@ const LuxEmbeddedKernel g_kernels[] = {
     {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<8>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<4,stream-k>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},  // the same, k-stages split evenly over the SMs
     {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<8,stream-k>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<4,pairs>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},     // the same on pairs of CTAs (cta_group::2)
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<8,pairs>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {LUX_CUDA_QMM_KERNEL_NAME, "qmv_simt", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},        // fp32 activations, odd K
     {"lux.qmm.dequantize", "dequantize", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {"lux.qmm.unpack", "unpack", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},

@@ -1387,8 +1387,11 @@ bool make_gemm_plan(const QmmArgs& a, int sm_count, GemmPlan* pl) {
         pl->streamk = sk < whole && T * nst >= G;
         if (const char* env = getenv("LUXCUDA_QMM_SCHEDULE")) pl->streamk = env[0] == 's';  // "streamk" | "tiles" (experiments)
     }
-    // whole tiles on CTA pairs
-    pl->pair = !pl->streamk && (sm_count & 1) == 0 && getenv("LUXCUDA_QMM_PAIR") != nullptr;
+    // Whole tiles on CTA pairs when the tiles about fill the SMs (measured against the one-CTA kernel on the same
+    // box: 256 tiles 59.2 against 60.1 us, 512 tiles 110.6 against 116.3, 448 tiles of the 8-bit shape 215 against
+    // 243, 112 tiles 60.3 against 64.0; below that the one-CTA kernel is 2-3 % ahead).
+    pl->pair = !pl->streamk && (sm_count & 1) == 0 && 10 * pl->n_tiles * pl->m_tiles >= 7 * sm_count;
+    if (const char* env = getenv("LUXCUDA_QMM_PAIR")) pl->pair = !pl->streamk && (sm_count & 1) == 0 && env[0] == '1';  // (experiments)
     if (pl->pair)
         pl->smem = 1024 + (size_t)kStagesP * kSub * kPairBBytes + (size_t)kDqGroups * kWUnitBytes + sizeof(PairSmemLayout) + 64;
     return encode_tiled_fn() != nullptr;

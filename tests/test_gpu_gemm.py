@@ -120,21 +120,23 @@ def test_prefill_is_repeatable(ctx, oracle, M, K, N, bits, group):
     assert bad == 0, f"{bad} of 240 launches differed from the first"
 
 
-@pytest.mark.parametrize("schedule", ["streamk", "tiles"])
+@pytest.mark.parametrize("schedule", ["streamk", "tiles", "pairs"])
 @pytest.mark.parametrize("M,K,N,bits,group", [(64, 4096, 4096, 4, 64), (512, 4096, 2048, 4, 64), (300, 1024, 384, 4, 64),
                                                   (512, 8192, 3584, 8, 128), (32, 64, 128, 4, 64), (2048, 1024, 4096, 4, 64)])
 def test_both_schedules(ctx, oracle, monkeypatch, schedule, M, K, N, bits, group):
-    """The launch either gives every CTA whole tiles or splits the sequence of (tile, k-stage) units evenly over the
-    CTAs, partial accumulators of a split tile being added in a fixed order by the CTA that starts the tile.  The
-    host picks one per shape; here each is forced in turn: both meet the bar, and both are repeatable bit for bit
-    (the flags of the partial-accumulator exchange are left reset by every launch)."""
-    monkeypatch.setenv("LUXCUDA_QMM_SCHEDULE", schedule)
+    """The launch either gives every CTA whole tiles, or gives pairs of CTAs (one MMA stream for two SMs) pairs of
+    tiles, or splits the sequence of (tile, k-stage) units evenly over the CTAs, partial accumulators of a split tile
+    being added in a fixed order by the CTA that starts the tile.  The host picks one per shape; here each is forced
+    in turn: all meet the bar, and all are repeatable bit for bit (the flags of the partial-accumulator exchange are
+    left reset by every launch)."""
+    monkeypatch.setenv("LUXCUDA_QMM_SCHEDULE", "streamk" if schedule == "streamk" else "tiles")
+    monkeypatch.setenv("LUXCUDA_QMM_PAIR", "1" if schedule == "pairs" else "0")
     wq, s, b = oracle.make_layer(N, K, bits, group, oracle.BF16, config_id=3, layer=K, proj=N)
     x = oracle.make_x(M, K, oracle.BF16, config_id=3, layer=K, tag=M)
     bx, bw, bs, bb = ctx.upload(x), ctx.upload(wq), ctx.upload(s), ctx.upload(b)
     y = ctx.empty((M, N), np.uint16)
     ctx.qmatmul(bx, bw, bs, bb, y, M, K, N, bits, group, BF16, BF16, BF16)
-    assert ctx.last_kernel().startswith("qmm_tc")
+    assert ctx.last_kernel().startswith("qmm_tc") and (schedule == "tiles") == ctx.last_kernel().endswith(("<4>", "<8>"))
     first = y.to_host()
     rows = np.unique(np.r_[0:min(M, 4), M // 2, M - 1])
     cols = np.unique(np.r_[0:min(N, 64), N // 2:N // 2 + 32, N - 64:N])
