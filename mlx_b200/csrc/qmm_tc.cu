@@ -222,6 +222,7 @@ struct GemmParams {
     int bm;                  // rows of x per tile (multiple of 16, <= 256)
     int n_tiles, m_tiles;
     float* ws;               // partial accumulators of tiles shared between CTAs: [CTA][bm][128] fp32
+    int y_tma;               // pair kernel: y leaves through shared memory and a TMA store (bf16, one copy of y, N % 8 == 0)
     uint32_t* ws_flags;      // [CTA]: 1 while that CTA's partial waits to be added (zero between launches)
 };
 
@@ -998,8 +999,11 @@ qmm_tc_tiles_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
 // The MMA is 256 rows of W (128 from each CTA's tensor memory) x bm rows of x, of which each CTA stages half in
 // its shared memory; the thread that issues it (in CTA 0) issues for both tensor cores, so the instruction
 // stream that bounds a stage is halved per SM, and x takes half the shared memory per stage.
-constexpr int kStagesP = 4;                   // k-stages in flight: x halves in shared memory, A in TMEM
+constexpr int kStagesP = 3;                   // k-stages in flight: x halves in shared memory, A in TMEM.  (Four, with
+                                              // the 64 KB more of shared memory they take from L1, measured the same or slower.)
 constexpr int kPairBBytes = (kMaxBM / 2) * 128;  // one sub-block of this CTA's half of x
+constexpr int kPairYBytes = kMaxBM * kTileN * 2; // a finished tile of y as bf16
+constexpr int kPairEpiBar = 1 + kDqGroups;       // named barrier of the epilogue warps
 static_assert(kDqGroups <= kStagesP, "parity waits would alias");
 static_assert(kAColBase + kStagesP * kAColsPerSlot <= kTmemCols, "A ring does not fit");
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // a shared::cluster address with this bit cleared is CTA 0's copy
@@ -1035,6 +1039,13 @@ __device__ __forceinline__ void tc_mma_ts_pair(uint32_t d_tmem, uint32_t a_tmem,
         "  tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p; }"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z) : "memory");
 }
+// a finished tile of y from shared memory ([row of x][128 columns] bf16) to global memory; rows and columns past
+// the ends of y are clipped by the copy engine
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                 ::"l"(map), "r"(x), "r"(y), "r"(s32(src)) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
 // this CTA's half of an x tile into its own shared memory, completion counted on CTA 0's barrier (no multicast)
 __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile(
@@ -1045,14 +1056,17 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
 template <int BITS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 qmm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-              const __grid_constant__ GemmParams p) {
+                   const __grid_constant__ CUtensorMap tmap_y, const __grid_constant__ GemmParams p) {
     constexpr int WPS = kBK * BITS / 32;  // packed words per row per stage: 8 | 16
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* sB = smem;  // [kStagesP][kSub][bm/2 rows][128 B], swizzled (TMA): this CTA's half of the x tile
     const uint32_t b_bytes = (uint32_t)(p.bm >> 1) * 128;
     unsigned char* sW = sB + (size_t)kStagesP * kSub * kPairBBytes;  // [kDqGroups][128 rows][64 B], 64-byte swizzle (TMA)
-    PairSmemLayout* sl = reinterpret_cast<PairSmemLayout*>(sW + (size_t)kDqGroups * kWUnitBytes);
+    unsigned char* sY = sW + (size_t)kDqGroups * kWUnitBytes;  // [bm rows of x][128 columns] bf16: a finished tile on its way out
+    // (without the staging buffer the shared memory is that much smaller, and L1, which holds the rows' scales and
+    // biases over a tile, that much larger: worth 4 % on this kernel)
+    PairSmemLayout* sl = reinterpret_cast<PairSmemLayout*>(sY + (p.y_tma ? kPairYBytes : 0));
     uint32_t rank;  // of this CTA in its pair: 0 issues the MMAs of both
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
     const int cl = (int)(blockIdx.x >> 1), ncl = (int)(gridDim.x >> 1);
@@ -1270,8 +1284,33 @@ qmm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         for (int tile = cl; tile < total_tiles; tile += ncl, tile_i++) {
             const int n = n0_of(tile) + q * 32 + lane;
             const int m0 = (tile % p.m_tiles) * p.bm;
+            if (p.y_tma && tile_i > 0) {
+                // the copy engine has finished reading the previous tile out of the staging buffer
+                if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                asm volatile("bar.sync %0, %1;" ::"n"(kPairEpiBar), "n"(kEpiWarps * 32) : "memory");
+            }
             if (!mbar_wait(&sl->tmem_full, tile_i & 1, abort_flag)) break;
             tc_fence_after();
+            if (p.y_tma) {
+                // The accumulator goes to shared memory as bf16, [row of x][column], and is released at once; the
+                // copy engine takes the tile to y while the next tile's MMAs run.
+                for (int blk = blk_lo; blk < blk_hi; blk++) {
+                    const int c0 = blk * 32;
+                    uint32_t v[32];
+                    __syncwarp();
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, v);
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(sY + (size_t)c0 * 256) + q * 32 + lane;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) dst[j * 128] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cta0(&sl->tmem_empty);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these writes, then the copy engine's reads
+                asm volatile("bar.sync %0, %1;" ::"n"(kPairEpiBar), "n"(kEpiWarps * 32) : "memory");
+                if (tid == 0 && n0_of(tile) < p.N) tma_store_2d(&tmap_y, sY, n0_of(tile), m0);
+                continue;
+            }
             // this thread: column n of y, rows m0 + c (32 consecutive n per warp: 64-byte row segments)
             const int m_end = min(p.bm, p.M - m0);
             for (int blk = blk_lo; blk < blk_hi; blk++) {
@@ -1308,6 +1347,7 @@ qmm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
         }
     }
     // ---------------- teardown ----------------
+    if (tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // the last tile has left
     tc_fence_before();
     __syncthreads();
     cluster_sync();  // neither CTA leaves (or frees tensor memory) while the other may still reach into it
@@ -1393,12 +1433,12 @@ bool make_gemm_plan(const QmmArgs& a, int sm_count, GemmPlan* pl) {
     pl->pair = !pl->streamk && (sm_count & 1) == 0 && 10 * pl->n_tiles * pl->m_tiles >= 7 * sm_count;
     if (const char* env = getenv("LUXCUDA_QMM_PAIR")) pl->pair = !pl->streamk && (sm_count & 1) == 0 && env[0] == '1';  // (experiments)
     if (pl->pair)
-        pl->smem = 1024 + (size_t)kStagesP * kSub * kPairBBytes + (size_t)kDqGroups * kWUnitBytes + sizeof(PairSmemLayout) + 64;
+        pl->smem = 1024 + (size_t)kStagesP * kSub * kPairBBytes + (size_t)kDqGroups * kWUnitBytes + kPairYBytes + sizeof(PairSmemLayout) + 64;
     return encode_tiled_fn() != nullptr;
 }
 
 template <int BITS>
-cudaError_t launch_gemm_pair_t(const CUtensorMap& tmap, const CUtensorMap& tmap_w, const GemmParams& p, const GemmPlan& pl, int sm_count, cudaStream_t stream) {
+cudaError_t launch_gemm_pair_t(const CUtensorMap& tmap, const CUtensorMap& tmap_w, const CUtensorMap& tmap_y, const GemmParams& p, const GemmPlan& pl, int sm_count, cudaStream_t stream) {
     auto kern = qmm_tc_pair_kernel<BITS>;
     static std::atomic<size_t> attr_smem[64];
     int dev = 0;
@@ -1411,7 +1451,7 @@ cudaError_t launch_gemm_pair_t(const CUtensorMap& tmap, const CUtensorMap& tmap_
     // one pair of CTAs per pair of SMs (the kernel carries its cluster shape), unless there are fewer pair tiles
     const int pairs = ((pl.n_tiles + 1) / 2) * pl.m_tiles;
     const int grid = 2 * std::min(sm_count / 2, pairs);
-    kern<<<grid, kNumThreads, pl.smem, stream>>>(tmap, tmap_w, p);
+    kern<<<grid, kNumThreads, pl.smem, stream>>>(tmap, tmap_w, tmap_y, p);
     return cudaGetLastError();
 }
 
@@ -1504,10 +1544,23 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, void* workspace, int sm_count, cudaS
     p.bm = pl.bm; p.n_tiles = pl.n_tiles; p.m_tiles = pl.m_tiles;
     p.ws_flags = static_cast<uint32_t*>(workspace);
     p.ws = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + kWsFlagBytes);
+    p.y_tma = 0;
     if (pl.pair) {
+        // y as a 2-D tensor [M rows][N] of bf16, boxes of 128 columns x bm rows, for the epilogue's TMA store
+        CUtensorMap tmap_y = tmap;
+        if (p.y_bf16 && p.world == 1 && (a.N & 7) == 0 && !getenv("LUXCUDA_QMM_NO_YTMA")) {
+            const cuuint64_t ydims[2] = {(cuuint64_t)a.N, (cuuint64_t)a.M};
+            const cuuint64_t ystrides[1] = {(cuuint64_t)a.N * 2};
+            const cuuint32_t ybox[2] = {(cuuint32_t)kTileN, (cuuint32_t)pl.bm};
+            r = encode_tiled_fn()(&tmap_y, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.y, ydims, ystrides, ybox, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            p.y_tma = r == CUDA_SUCCESS ? 1 : 0;
+        }
+        if (!p.y_tma) pl.smem -= kPairYBytes;
         if (name) *name = a.bits == 4 ? "qmm_tc<4,pairs>" : "qmm_tc<8,pairs>";
-        return a.bits == 4 ? launch_gemm_pair_t<4>(tmap, tmap_w, p, pl, sm_count, stream)
-                           : launch_gemm_pair_t<8>(tmap, tmap_w, p, pl, sm_count, stream);
+        return a.bits == 4 ? launch_gemm_pair_t<4>(tmap, tmap_w, tmap_y, p, pl, sm_count, stream)
+                           : launch_gemm_pair_t<8>(tmap, tmap_w, tmap_y, p, pl, sm_count, stream);
     }
     if (a.bits == 4) {
         if (name) *name = pl.streamk ? "qmm_tc<4,stream-k>" : "qmm_tc<4>";
