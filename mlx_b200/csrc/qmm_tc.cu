@@ -222,7 +222,8 @@ struct GemmParams {
     int bm;                  // rows of x per tile (multiple of 16, <= 256)
     int n_tiles, m_tiles;
     float* ws;               // partial accumulators of tiles shared between CTAs: [CTA][bm][128] fp32
-    int y_tma;               // pair kernel: y leaves through shared memory and a TMA store (bf16, one copy of y, N % 8 == 0)
+    int y_tma;               // pair kernel: y leaves through shared memory; 1: by a TMA store (bf16, one copy of y, N % 8 == 0),
+                             // 2: by 16-byte stores into every rank's copy (column-sharded, ld and col0 multiples of 8)
     uint32_t* ws_flags;      // [CTA]: 1 while that CTA's partial waits to be added (zero between launches)
 };
 
@@ -1308,7 +1309,31 @@ qmm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_cons
                 if (lane == 0) mbar_arrive_cta0(&sl->tmem_empty);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // these writes, then the copy engine's reads
                 asm volatile("bar.sync %0, %1;" ::"n"(kPairEpiBar), "n"(kEpiWarps * 32) : "memory");
-                if (tid == 0 && n0_of(tile) < p.N) tma_store_2d(&tmap_y, sY, n0_of(tile), m0);
+                if (p.y_tma == 1) {
+                    if (tid == 0 && n0_of(tile) < p.N) tma_store_2d(&tmap_y, sY, n0_of(tile), m0);
+                } else {
+                    // column-sharded layers: the tile goes into every rank's copy of y, 16 bytes per store (plain
+                    // stores: no TMA on a peer's memory), a row of the tile = 16 lanes
+                    const int m_end = min(p.bm, p.M - m0);
+                    const int ncol = n0_of(tile) + (tid & 15) * 8;
+                    for (int row = tid >> 4; row < m_end; row += (kEpiWarps * 32) >> 4) {
+                        const uint4 val = *reinterpret_cast<const uint4*>(sY + (size_t)row * 256 + (tid & 15) * 16);
+                        if (ncol >= p.N) continue;
+                        const size_t idx = (size_t)(m0 + row) * p.ld + p.col0 + ncol;
+                        if (ncol + 8 <= p.N) {
+                            for (int dst = 0; dst < p.world; dst++)
+                                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y_all[dst]) + idx) = val;
+                        } else {  // the last columns of y: one by one
+                            const uint32_t w4[4] = {val.x, val.y, val.z, val.w};
+                            for (int dst = 0; dst < p.world; dst++) {
+                                uint16_t* yp = reinterpret_cast<uint16_t*>(p.y_all[dst]) + idx;
+#pragma unroll
+                                for (int e = 0; e < 8; e++)
+                                    if (ncol + e < p.N) yp[e] = (uint16_t)(w4[e >> 1] >> ((e & 1) * 16));
+                            }
+                        }
+                    }
+                }
                 continue;
             }
             // this thread: column n of y, rows m0 + c (32 consecutive n per warp: 64-byte row segments)
@@ -1556,6 +1581,8 @@ cudaError_t launch_qmm_tc(const QmmArgs& a, void* workspace, int sm_count, cudaS
                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             p.y_tma = r == CUDA_SUCCESS ? 1 : 0;
+        } else if (p.y_bf16 && p.world > 1 && ((p.ld | p.col0) & 7) == 0 && !getenv("LUXCUDA_QMM_NO_YTMA")) {
+            p.y_tma = 2;
         }
         if (!p.y_tma) pl.smem -= kPairYBytes;
         if (name) *name = a.bits == 4 ? "qmm_tc<4,pairs>" : "qmm_tc<8,pairs>";
