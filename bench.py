@@ -53,6 +53,16 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 
 
+def e2e_driver_path():
+    """The C host loop of the end-to-end leg (bench_e2e.c), built on demand with the host compiler."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    src, lib = os.path.join(here, "bench_e2e.c"), os.path.join(here, "mlx_b200", "lib", "libbench_e2e.so")
+    if not os.path.exists(lib) or os.path.getmtime(lib) < os.path.getmtime(src):
+        cc = "/usr/bin/gcc" if os.path.exists("/usr/bin/gcc") else "gcc"
+        subprocess.run([cc, "-O2", "-shared", "-fPIC", "-fvisibility=hidden", "-o", lib, src], check=True)
+    return lib
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -781,8 +791,47 @@ def run_ours(args, rank, world):
     xp = {M: (C.c_void_p(x_pin[M].ctypes.data), x_pin[M].nbytes) for M in M_SWEEP}
     yp = {M: (C.c_void_p(y_pin[M].ctypes.data), y_pin[M].nbytes) for M in M_SWEEP}
 
+    # The loop over the calls runs in C (bench_e2e.c), as a host of the plugin would run it: per call the plugin's
+    # own buffer_copy_from_host_async, qmatmul (or qmatmul_sharded_push) and blocking buffer_copy_to_host, taken as
+    # function pointers from the tables the plugin publishes.  (The same loop in Python, which --e2e-python runs
+    # instead, costs about 2 us of interpreter and ctypes time per call on top.)
+    e2e_native = None
+    if not args.e2e_python and world > 1 and not use_push:
+        args.e2e_python = True  # (the NCCL fallback takes a staging buffer and a communicator: not wired into the C loop)
+    if not args.e2e_python:
+        drv = C.CDLL(e2e_driver_path())
+
+        class Call(C.Structure):
+            _fields_ = [("x_dev", C.c_void_p), ("wq", C.c_void_p), ("scales", C.c_void_p), ("biases", C.c_void_p),
+                        ("y_dev", C.c_void_p), ("y_symm", C.c_void_p), ("x_host", C.c_void_p), ("y_host", C.c_void_p),
+                        ("x_bytes", C.c_size_t), ("y_bytes", C.c_size_t), ("M", C.c_int32), ("K", C.c_int32), ("N", C.c_int32),
+                        ("bits", C.c_int32), ("group", C.c_int32), ("dtype", C.c_int32)]
+
+        def _h(obj):  # a handle as an integer
+            v = obj.handle if hasattr(obj, "handle") else obj
+            return v.value if isinstance(v, C.c_void_p) else C.cast(v, C.c_void_p).value
+
+        order = [(M, r) for M in M_SWEEP for r in range(R_SETS)]
+        calls = (Call * len(order))()
+        for i, (M, r) in enumerate(order):
+            w, s_, b_ = layers[r]
+            calls[i] = Call(_h(x_dev[M]), _h(w), _h(s_), _h(b_), _h(y_dev[M]), _h(symm[M]) if use_push else None,
+                            xp[M][0].value, yp[M][0].value, xp[M][1], yp[M][1], M, K_DEC, N_DEC, BITS, GROUP, BF16)
+        fn = lambda f: C.cast(f, C.c_void_p)
+        drv.lux_bench_e2e.restype = C.c_int
+        drv.lux_bench_e2e.argtypes = [C.c_void_p] * 5 + [C.POINTER(Call), C.c_int, C.c_int, C.POINTER(C.c_longlong)]
+        e2e_native = (drv, calls, len(order), fn(q.buffer_copy_from_host_async), fn(q.qmatmul), fn(q.qmatmul_sharded_push),
+                      fn(plugin.vtbl.buffer_copy_to_host))
+
     def e2e_step():
         nonlocal e2e_calls
+        if e2e_native is not None:
+            drv, calls, n, f_in, f_mm, f_push, f_out = e2e_native
+            done = C.c_longlong(0)
+            rc = drv.lux_bench_e2e(f_in, f_mm, f_push, f_out, ctx.handle, calls, n, e2e_reps, C.byref(done))
+            plugin.check(rc, "e2e loop")
+            e2e_calls += done.value
+            return
         for _ in range(e2e_reps):
             for M in M_SWEEP:
                 for r in range(R_SETS):
@@ -860,6 +909,7 @@ def run_ours(args, rank, world):
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "calls": e2e_calls, "us_per_call": ms_e2e * 1e3 / max(1, e2e_calls),
+                "driver": "python" if e2e_native is None else "C host loop (bench_e2e.c) over the plugin's entry points",
                 "note": "per call, pinned host buffers: buffer_copy_from_host_async(x) + qmatmul + buffer_copy_to_host(y, blocking); weights stay resident "
                         "like the core's tensors (src/gpu_core.cpp:47-76)"},
         "gpu_launches": int(launches),
@@ -880,6 +930,8 @@ def main():
                     help="skip the e2e and CPU-baseline legs (for short runs under a profiler)")
     ap.add_argument("--nccl-allgather", action="store_true",
                     help="N>1: gather the column slices with NCCL + an interleave pass instead of peer stores from the kernel")
+    ap.add_argument("--e2e-python", action="store_true",
+                    help="run the end-to-end leg's loop over the calls in Python instead of in C (bench_e2e.c)")
     ap.add_argument("--no-sharded-legs", action="store_true",
                     help="N>1: skip the column-sharded 8-bit GEMM and chain legs that follow the sweep by default")
     ap.add_argument("--gemm-sharded", action="store_true",

@@ -1,0 +1,49 @@
+/* Host loop of bench.py's end-to-end leg, in C: what a C or C++ host of the plugin does per call --
+ *   copy the call's activations from page-locked host memory to the device   (buffer_copy_from_host_async),
+ *   the quantized matmul                                                      (qmatmul | qmatmul_sharded_push),
+ *   read the result back into page-locked host memory, blocking               (buffer_copy_to_host)
+ * -- through the plugin's own entry points, which bench.py hands over as function pointers taken from the
+ * tables the plugin publishes.  Only the loop lives here (from Python every call costs about two microseconds
+ * of interpreter and ctypes time that no such host pays); bench.py brackets it with the plugin's timers.
+ * Built by __graft_entry__.build() with the host compiler; no CUDA, no plugin header needed. */
+#include <stddef.h>
+#include <stdint.h>
+
+typedef int (*copy_in_fn)(void* ctx, void* buf, const void* src, size_t bytes);
+typedef int (*copy_out_fn)(void* ctx, void* buf, void* dst, size_t bytes);
+typedef int (*qmatmul_fn)(void* ctx, void* x, void* wq, void* scales, void* biases, void* y, int M, int K, int N, int bits,
+                          int group, int x_dtype, int sb_dtype, int y_dtype);
+typedef int (*push_fn)(void* y_symm, void* x, void* wq, void* scales, void* biases, int M, int K, int N_local, int bits,
+                       int group, int y_dtype);
+
+typedef struct {
+    void *x_dev, *wq, *scales, *biases;
+    void* y_dev;   /* the buffer read back (for a sharded call: the symmetric buffer seen as a buffer) */
+    void* y_symm;  /* sharded calls: the symmetric buffer handle; else NULL */
+    const void* x_host;
+    void* y_host;
+    size_t x_bytes, y_bytes;
+    int32_t M, K, N, bits, group, dtype;
+} lux_bench_call;
+
+__attribute__((visibility("default")))
+int lux_bench_e2e(copy_in_fn copy_in, qmatmul_fn qmatmul, push_fn push, copy_out_fn copy_out, void* ctx,
+                  const lux_bench_call* calls, int n_calls, int reps, long long* calls_done) {
+    long long done = 0;
+    for (int r = 0; r < reps; r++) {
+        for (int i = 0; i < n_calls; i++) {
+            const lux_bench_call* c = &calls[i];
+            int rc = copy_in(ctx, c->x_dev, c->x_host, c->x_bytes);
+            if (rc) return rc;
+            rc = c->y_symm ? push(c->y_symm, c->x_dev, c->wq, c->scales, c->biases, c->M, c->K, c->N, c->bits, c->group, c->dtype)
+                           : qmatmul(ctx, c->x_dev, c->wq, c->scales, c->biases, c->y_dev, c->M, c->K, c->N, c->bits, c->group,
+                                     c->dtype, c->dtype, c->dtype);
+            if (rc) return rc;
+            rc = copy_out(ctx, c->y_dev, c->y_host, c->y_bytes);
+            if (rc) return rc;
+            done++;
+        }
+    }
+    if (calls_done) *calls_done = done;
+    return 0;
+}
