@@ -708,7 +708,41 @@ def run_ours(args, rank, world):
                     launch(M, r)
         graph_sweeps = ctx.graph_end()
 
+    # One GPU: the matmuls of a sweep are independent, so the timed step hands each sweep to the plugin as ONE call
+    # (qmatmul_batch: a persistent launch for the items with M <= 8, one for those with M = 16) instead of 48 calls.
+    # Every item has its own output buffer; three of them are checked against the single calls, bit for bit.
+    use_batch = world == 1 and not args.single_calls
+    batch_graph, batch_verified = None, None
+    if use_batch:
+        b_items = [(M, r) for M in M_SWEEP for r in range(R_SETS)]
+        b_y = {it: ctx.empty((it[0], N_DEC), np.uint16) for it in b_items}
+
+        def batch_call(items):
+            ctx.qmatmul_batch([x_dev[M] for M, r in items], [layers[r][0] for M, r in items], [layers[r][1] for M, r in items],
+                              [layers[r][2] for M, r in items], [b_y[it] for it in items], [M for M, r in items],
+                              K_DEC, N_DEC, BITS, GROUP, BF16)
+        batch_call(b_items)
+        batch_kernel = ctx.last_kernel()
+        ctx.sync()
+        bad = []
+        for it in ((1, 0), (8, R_SETS - 1), (16, R_SETS // 2)):
+            launch(*it)
+            if not np.array_equal(b_y[it].to_host(), y_dev[it[0]].to_host()[:, :N_DEC]):
+                bad.append(it)
+        batch_verified = (f"FAILED: items {bad} differ from single calls" if bad else
+                          "items (M=1, set 0), (M=8, last set), (M=16, middle set) of a batched sweep bit-identical to single qmatmul calls")
+        if bad:
+            print(batch_verified, file=sys.stderr, flush=True)
+        if use_graph:
+            ctx.graph_begin()
+            for _ in range(SWEEPS_PER_GRAPH):
+                batch_call(b_items)
+            batch_graph = ctx.graph_end()
+
     def sweep():
+        if use_batch:
+            batch_call(b_items)
+            return
         for M in M_SWEEP:
             if use_graph:
                 ctx.graph_launch(graphs[M])
@@ -739,7 +773,7 @@ def run_ours(args, rank, world):
     def step():
         done = 0
         while use_graph and done + SWEEPS_PER_GRAPH <= args.reps:
-            ctx.graph_launch(graph_sweeps)
+            ctx.graph_launch(batch_graph if use_batch else graph_sweeps)
             done += SWEEPS_PER_GRAPH
         for _ in range(args.reps - done):
             sweep()
@@ -753,6 +787,26 @@ def run_ours(args, rank, world):
     ms_total = timed(lambda: [step() for _ in range(args.steps)])
     launches = ctx.launch_count() - lc0
     clocks = sampler.stop() if rank == 0 else None
+
+    # the same sweeps as single calls (one launch per matmul, 48 per sweep), for comparison
+    single = None
+    if use_batch:
+        def step_single():
+            done = 0
+            while use_graph and done + SWEEPS_PER_GRAPH <= args.reps:
+                ctx.graph_launch(graph_sweeps)
+                done += SWEEPS_PER_GRAPH
+            for _ in range(args.reps - done):
+                for M in M_SWEEP:
+                    for r in range(R_SETS):
+                        launch(M, r)
+        n_s = max(1, min(args.steps, 5))
+        step_single()
+        ms_s = timed(lambda: [step_single() for _ in range(n_s)], 10, 11)
+        single = {"GBps": sum(alg_bytes(M) for M in M_SWEEP) * R_SETS * args.reps * n_s / ms_s / 1e6, "steps": n_s,
+                  "us_per_matmul": ms_s * 1e3 / (len(M_SWEEP) * R_SETS * args.reps * n_s),
+                  "how": "one qmatmul call (one launch) per matmul, the same sweeps replayed from CUDA graphs"}
+        single["frac_of_peak"] = single["GBps"] / float(measured_peaks()[0]["hbm_gbs"])
 
     # per-M timing (same graphs, one M at a time) for the roofline of the dominant kernel
     per_m = {}
@@ -773,6 +827,18 @@ def run_ours(args, rank, world):
         per_m[M] = {"us_per_launch": ms * 1e3 / n_launch, "GBps": alg_bytes(M) * world * n_launch / ms / 1e6,
                     "kernel": kernel_name}
 
+    per_m_batched = None
+    if use_batch:
+        per_m_batched = {}
+        for M in M_SWEEP:
+            its = [it for it in b_items if it[0] == M]
+            def run_b(its=its):
+                for _ in range(reps_m):
+                    batch_call(its)
+            run_b()
+            ms = timed(run_b, 2, 3)
+            per_m_batched[str(M)] = {"us_per_matmul": ms * 1e3 / (reps_m * len(its)), "GBps": alg_bytes(M) * reps_m * len(its) / ms / 1e6,
+                                     "kernel": batch_kernel if M > 8 else batch_kernel.replace("m16", "m8")}
     sweep_bytes = sum(alg_bytes(M) for M in M_SWEEP) * R_SETS * world
     total_bytes = sweep_bytes * args.reps * args.steps
     value = total_bytes / ms_total / 1e6  # GB/s
@@ -888,7 +954,10 @@ def run_ours(args, rank, world):
         "run": {"layout": "one GPU" if world == 1 else f"weak scaling: each of {world} ranks holds its own {N_DEC}-column slice of a "
                           f"{n_total}-column layer and every rank ends with the whole y (all-gather of output slices)",
                    "N_total": n_total, "weight_sets": R_SETS, "sweeps_per_step": args.reps, "cuda_graph": use_graph,
-                   "launches_per_graph": SWEEPS_PER_GRAPH * len(M_SWEEP) * R_SETS if use_graph else None,
+                   "calls": ("one qmatmul_batch call per sweep: its 48 independent matmuls run as two persistent launches (36 with M <= 8, "
+                             "12 with M = 16)" if use_batch else "one call (one launch) per matmul"),
+                   "batch_verified": batch_verified,
+                   "launches_per_graph": (SWEEPS_PER_GRAPH * (2 if use_batch else len(M_SWEEP) * R_SETS)) if use_graph else None,
                    "allgather": None if world == 1 else ("peer stores from the decode kernel (one launch per call)" if use_push
                                                          else "NCCL all-gather + interleave pass"),
                    "verified": verified,
@@ -896,11 +965,14 @@ def run_ours(args, rank, world):
                          "each launch reads a set last touched 11 launches earlier"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": which, "frac_of_nominal_8TBps": achieved / NOMINAL_HBM_GBS,
-                     "kernel": "qmv_mma<4,m8|m16>", "avg_us_per_launch": avg_us,
+                     "kernel": "qmv_batch<4,m8|m16>" if use_batch else "qmv_mma<4,m8|m16>",
+                     ("avg_us_per_matmul" if use_batch else "avg_us_per_launch"): avg_us,
                      "alg_bytes_per_launch": {str(M): alg_bytes(M) for M in M_SWEEP},
                      "traffic": args.traffic_bytes, "traffic_unit": "bytes per launch (ncu dram read+write, M=1 launch)",
                      "traffic_over_algorithmic": args.traffic_bytes / alg_bytes(1) if args.traffic_bytes else None},
         "per_M": {str(M): per_m[M] for M in M_SWEEP},
+        "per_M_batched": per_m_batched,
+        "single_calls": single,
         "cpu_reference_config": cpu_ref_config,
         "prefill": prefill,
         "chain": chain,
@@ -930,6 +1002,8 @@ def main():
                     help="skip the e2e and CPU-baseline legs (for short runs under a profiler)")
     ap.add_argument("--nccl-allgather", action="store_true",
                     help="N>1: gather the column slices with NCCL + an interleave pass instead of peer stores from the kernel")
+    ap.add_argument("--single-calls", action="store_true",
+                    help="N=1: time the sweep as one call per matmul (the default hands each sweep to qmatmul_batch)")
     ap.add_argument("--e2e-python", action="store_true",
                     help="run the end-to-end leg's loop over the calls in Python instead of in C (bench_e2e.c)")
     ap.add_argument("--no-sharded-legs", action="store_true",

@@ -51,7 +51,7 @@ extern "C" {
 #define LUX_CUDA_QUANT_MAGIC 0x4C515854u /* "LQXT" */
 #define LUX_CUDA_PRO_RMS_NORM 1
 #define LUX_CUDA_PRO_SUM3 2
-#define LUX_CUDA_QUANT_VERSION 4u /* 2: symm_* and qmatmul_sharded_push appended; 3: sum3, mul_rms_norm; 4: qmatmul_pro */
+#define LUX_CUDA_QUANT_VERSION 5u /* 2: symm_* and qmatmul_sharded_push appended; 3: sum3, mul_rms_norm; 4: qmatmul_pro; 5: qmatmul_batch */
 #define LUX_CUDA_QMM_KERNEL_NAME "lux.qmm.affine"
 #define LUX_CUDA_NCCL_UID_BYTES 128
 
@@ -226,6 +226,19 @@ typedef struct lux_gpu_quant_vtbl {
     LuxBackendError (*qmatmul_pro)(LuxBackendContext* ctx, LuxBackendBuffer* x, LuxBackendBuffer* wq, LuxBackendBuffer* scales,
                                    LuxBackendBuffer* biases, LuxBackendBuffer* y, int M, int K, int N, int bits, int group,
                                    LuxBackendDtype y_dtype, int prologue, size_t x_ld, float eps);
+
+    /* --- several independent decode matmuls of one shape in one call (version >= 5) ---
+     * y[i] = x[i] . dequant(wq[i], scales[i], biases[i])^T for i < n: n layers (or n requests on one layer) of the
+     * same K, N, bits, group, bf16, each with its own M[i] <= 16.  The same bits as n calls of qmatmul.  The matmuls
+     * run in as few launches as their shapes allow (those with M <= 8 together, those with M > 8 together, up to 48
+     * per launch), each launch a persistent kernel that goes from one matmul to the next without draining: what a
+     * single decode launch spends on starting and on finishing is paid once per launch.  Nothing orders the
+     * matmuls of a call among themselves: no y[i] may be an x[j] of the same call.  Shapes the decode kernel
+     * does not take whole (K split over CTAs, fp32, M > 16) run as n calls of qmatmul. */
+    LuxBackendError (*qmatmul_batch)(LuxBackendContext* ctx, int n, LuxBackendBuffer* const* x, LuxBackendBuffer* const* wq,
+                                     LuxBackendBuffer* const* scales, LuxBackendBuffer* const* biases,
+                                     LuxBackendBuffer* const* y, const int* M, int K, int N, int bits, int group,
+                                     LuxBackendDtype y_dtype);
 } lux_gpu_quant_vtbl;
 
 /* Entry points exported with default visibility. */

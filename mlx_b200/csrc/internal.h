@@ -203,6 +203,9 @@ void note_chain_launch(Context* c, const void* out, size_t out_bytes);  // right
 void note_decode_launch(Context* c, const QmmArgs& a);  // call right after a decode launch, before counting it
 // decode / small-M, any supported dtype combination: CUDA cores + warp shuffles
 cudaError_t launch_qmv_simt(const QmmArgs& a, cudaStream_t stream, const char** name);
+// several decode matmuls of one shape (M on one side of 8) as one persistent launch; at most qmv_batch_max() items
+int qmv_batch_max();
+cudaError_t launch_qmv_batch(const QmmArgs* items, int n, int sm_count, cudaStream_t stream, const char** name);
 // prefill GEMM, bf16 activations: TMA + tcgen05 + TMEM
 bool qmm_tc_supported(const QmmArgs& a);
 size_t qmm_tc_workspace_bytes(int sm_count);  // scratch of a launch (flags at its head: zero between launches)

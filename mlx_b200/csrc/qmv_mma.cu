@@ -727,6 +727,239 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_mma_kernel(const __grid_const
     }
 }
 
+// ---- several matmuls of one shape per launch ------------------------------------------------------------
+constexpr int kMaxBatch = 48;
+struct BatchItem {
+    const __nv_bfloat16* x;
+    const uint32_t* wq;
+    const __nv_bfloat16* scales;
+    const __nv_bfloat16* biases;
+    void* y;
+    int M, pad;
+};
+struct BatchParams {
+    int n_items;
+    int K, N, gshift, y_bf16;
+    int nkb, n_rt, chunks, tb, sb_bytes, xs_off;
+    BatchItem items[kMaxBatch];
+};
+template <int BITS, int MT>
+__device__ __forceinline__ void load_x_item(const __nv_bfloat16* x, int M, int K, int kb, int g, int t, uint4 (&xr)[MT][BITS == 4 ? 8 : 4]) {
+    constexpr int XV = BITS == 4 ? 8 : 4;
+    constexpr int KB = 1024 / BITS;
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+        const int m = mt * 8 + g;
+        const __nv_bfloat16* row = x + (size_t)m * K + kb * KB + t * (KB / 8);
+#pragma unroll
+        for (int j = 0; j < XV; j++) {
+            const int h = j / (XV / 2), i = j % (XV / 2);
+            xr[mt][j] = make_uint4(0, 0, 0, 0);
+            if (m < M) xr[mt][j] = ldg_nc_v4(reinterpret_cast<const uint4*>(row + h * (KB / 2) + i * 8));
+        }
+    }
+}
+template <int MT>
+__device__ __forceinline__ void store_tile_item(void* y, int M, int N, int y_bf16, int rt, int e, float sum) {
+    const int mt = e >> 7, rem = e & 127, ln = rem >> 2, ci = rem & 3;
+    const int r16 = (ln >> 2) + 8 * (ci >> 1);
+    const int row = rt * 16 + r16;
+    const int m = mt * 8 + 2 * (ln & 3) + (ci & 1);
+    if (row < N && m < M) {
+        const size_t idx = (size_t)m * N + row;
+        if (y_bf16) reinterpret_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(sum);
+        else reinterpret_cast<float*>(y)[idx] = sum;
+    }
+}
+
+// Several decode matmuls of one shape (K, N, bits, group; M <= 8*MT each) in ONE launch: qmv_mma_kernel's roles and
+// arithmetic with a loop over the matmuls around them.  A CTA keeps its range of row tiles through all of them and
+// its warps' rings never drain in between: the fetch iterator walks from the last task of one matmul into the
+// first of the next, so the start of a launch (first reads of parameters, x and weights) and its tail (the
+// ordered sum and the store of y), which are half of a single decode launch, are paid once per launch instead of
+// once per matmul -- the sum and the store of a matmul run while the next one's weights are already arriving.
+// No K split, no peers, no prologue (the host sends such calls one by one).
+template <int BITS, int MT>
+__global__ void __launch_bounds__(kThreads, 1) qmv_batch_kernel(const __grid_constant__ BatchParams p) {
+    constexpr int XV = BITS == 4 ? 8 : 4;  // x fragments (uint4) per lane per k-block per 8-row block
+    constexpr int KB = 1024 / BITS;        // weights per k-block (128 bytes per row)
+    constexpr int E4 = MT * 32;            // float4 per partial
+    constexpr int D = ring_depth(MT);      // ring stages of a warp
+    extern __shared__ __align__(16) unsigned char smem[];
+    float4* part = reinterpret_cast<float4*>(smem + ring_bytes(MT));   // [tb][nkl][MT][32]; ring: [kWarps][D][kStageBytes]
+    // after the partials (MT == 2): the x fragments of rows 8..15, [warp][fragment][lane]
+    uint4* xs = reinterpret_cast<uint4*>(smem + p.xs_off) + (threadIdx.x >> 5) * (XV * 32) + (threadIdx.x & 31);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int ci = blockIdx.x;
+    const int rt_lo = (int)((long long)p.n_rt * ci / p.chunks), rt_hi = (int)((long long)p.n_rt * (ci + 1) / p.chunks);
+    const int kb_lo = 0, kb_hi = p.nkb;
+    const int nkl = kb_hi - kb_lo;
+    const int tb = p.tb;
+    const size_t row_bytes = (size_t)p.K * BITS / 8;
+    const int gpr = p.K >> p.gshift;   // groups per row
+    const int gpk = KB >> p.gshift;    // groups per k-block
+    // the matmul whose weights are being fetched (f_pi) runs ahead of the one being computed (pi)
+    int f_pi = 0;
+    const unsigned char* wbase = reinterpret_cast<const unsigned char*>(p.items[0].wq) + t * 16;
+    const __nv_bfloat16* sb_src = lane < 16 ? p.items[0].scales : p.items[0].biases;
+    const uint32_t ring_lo = smem_u32(smem) + warp * (D * kStageBytes) + lane * 16;  // this lane's slot, stage 0
+    const int tail_tile = (p.N & 15) ? p.n_rt - 1 : -1;  // the tile whose rows must be clamped to N-1
+    const bool has_work = kb_lo + warp < kb_hi && rt_lo < rt_hi;
+
+    // The warp's tasks, in order: for each batch of tb tiles, for each of its k-blocks, the tiles of the
+    // batch ("run": they share the x fragments of that k-block).  D-1 tasks are in flight while one is
+    // computed; the fetch runs that far ahead of the computation, one commit group per task (empty past the end).
+    const size_t half_tile = 8 * row_bytes, tile_stride = 16 * row_bytes;
+    int f_b0 = rt_lo, f_kb = kb_lo + warp, f_rt = rt_lo;  // the task fetched next
+    uint32_t f_dst = ring_lo;                             // and the stage it goes to
+    // this lane's sources of that task: rows g and g+8 of the tile (its 16-byte pieces t and t+4 of the k-block),
+    // the scales (lanes 0-15) or biases (16-31) of row lane%16.  Inside a run they move by constant strides.
+    const unsigned char* f_p0 = nullptr;
+    const unsigned char* f_p1 = nullptr;
+    const __nv_bfloat16* f_sb = nullptr;
+    auto fetch_point = [&]() {
+        if (f_rt != tail_tile) {
+            f_p0 = wbase + (size_t)(f_rt * 16 + g) * row_bytes + f_kb * 128;
+            f_p1 = f_p0 + half_tile;
+            f_sb = sb_src + ((f_rt * 16 + (lane & 15)) * gpr + f_kb * gpk);
+        } else {  // rows past N read row N-1 (their results are never stored)
+            const int n0 = f_rt * 16;
+            f_p0 = wbase + (size_t)min(n0 + g, p.N - 1) * row_bytes + f_kb * 128;
+            f_p1 = wbase + (size_t)min(n0 + g + 8, p.N - 1) * row_bytes + f_kb * 128;
+            f_sb = sb_src + (min(n0 + (lane & 15), p.N - 1) * gpr + f_kb * gpk);
+        }
+    };
+    if (has_work) fetch_point();
+    auto fetch_next = [&]() {
+        if (has_work && f_pi < p.n_items) {
+            cp_async16(f_dst, f_p0);
+            cp_async16(f_dst + 512, f_p0 + 64);
+            cp_async16(f_dst + 1024, f_p1);
+            cp_async16(f_dst + 1536, f_p1 + 64);
+            if (p.sb_bytes == 16) cp_async16(f_dst + 2048, f_sb);
+            else if (p.sb_bytes == 8) cp_async8(f_dst + 2048, f_sb);
+            else cp_async4(f_dst + 2048, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(f_sb) & ~uintptr_t(3)));  // a lone scale travels with its neighbour
+            // on to the task after it
+            f_dst = f_dst + kStageBytes == ring_lo + D * kStageBytes ? ring_lo : f_dst + kStageBytes;
+            if (++f_rt == min(f_b0 + tb, rt_hi)) {  // next run: next k-block of the batch, else first k-block of the next batch
+                f_kb += kWarps;
+                if (f_kb >= kb_hi) {
+                    f_kb = kb_lo + warp;
+                    f_b0 += tb;
+                }
+                if (f_b0 >= rt_hi && ++f_pi < p.n_items) {  // on to the next matmul: same tiles, its weights
+                    f_b0 = rt_lo;
+                    wbase = reinterpret_cast<const unsigned char*>(p.items[f_pi].wq) + t * 16;
+                    sb_src = lane < 16 ? p.items[f_pi].scales : p.items[f_pi].biases;
+                }
+                f_rt = f_b0;
+                if (f_pi < p.n_items) fetch_point();
+            } else if (f_rt == tail_tile) {
+                fetch_point();
+            } else {
+                f_p0 += tile_stride;
+                f_p1 += tile_stride;
+                f_sb += 16 * gpr;
+            }
+        }
+        cp_async_commit();
+    };
+
+    uint4 xr[MT][XV];
+    bool x_ahead = false;  // xr already holds the fragments of the run about to start
+#pragma unroll
+    for (int i = 0; i < D - 1; i++) fetch_next();
+    uint32_t src_c = ring_lo;  // stage of the task computed next (this lane's slot)
+    uint32_t sboff[2][2];      // byte offsets of this lane's scales inside a stage, by row half r and piece h
+#pragma unroll 1
+    for (int pi = 0; pi < p.n_items; pi++) {
+    const __nv_bfloat16* x_cur = p.items[pi].x;
+    void* y_cur = p.items[pi].y;
+    const int M_cur = p.items[pi].M;
+#pragma unroll 1
+    for (int b0 = rt_lo; b0 < rt_hi; b0 += tb) {
+        const int nt = min(tb, rt_hi - b0);
+        if (has_work) {
+#pragma unroll 1
+            for (int kb = kb_lo + warp; kb < kb_hi; kb += kWarps) {
+                fetch_next();  // (the run's first fetch goes out ahead of the x loads)
+                if (!x_ahead) load_x_item<BITS, MT>(x_cur, M_cur, p.K, kb, g, t, xr);
+                x_ahead = false;
+                permute_x<BITS, MT>(xr);
+                if (MT == 2 && kX1Shared) {
+                    __syncwarp();  // (the previous run's reads of xs)
+#pragma unroll
+                    for (int j = 0; j < XV; j++) xs[j * 32] = xr[MT - 1][j];
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    const int slot = g + 8 * r;
+                    const int par = p.sb_bytes == 2 ? ((slot * gpr + kb) & 1) : 0;
+#pragma unroll
+                    for (int h = 0; h < 2; h++)
+                        sboff[r][h] = 2048 - lane * 16 + slot * 16 + ((((h * (KB / 2) + t * (KB / 8)) >> p.gshift) + par) << 1);
+                }
+                float4* dstp = part + (kb - kb_lo) * E4 + lane;
+#pragma unroll 1
+                for (int rt = b0; rt < b0 + nt; rt++) {
+                    if (rt != b0) fetch_next();
+                    cp_async_wait<D - 1>();
+                    __syncwarp();
+                    uint4 w[2][2];
+                    uint32_t s[2][2], b[2][2];
+#pragma unroll
+                    for (int r = 0; r < 2; r++)
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                         : "=r"(w[r][h].x), "=r"(w[r][h].y), "=r"(w[r][h].z), "=r"(w[r][h].w)
+                                         : "r"(src_c + (r * 2 + h) * 512));
+                            asm volatile("ld.shared.u16 %0, [%1];" : "=r"(s[r][h]) : "r"(src_c + sboff[r][h]));
+                            asm volatile("ld.shared.u16 %0, [%1+256];" : "=r"(b[r][h]) : "r"(src_c + sboff[r][h]));
+                        }
+                    const bool fast = scales_fast_ok4(s[0][0], s[0][1], s[1][0], s[1][1]);
+                    float acc[MT][2][4];  // two independent accumulation chains per 8-row block of x
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                        for (int c = 0; c < 2; c++) acc[mt][c][0] = acc[mt][c][1] = acc[mt][c][2] = acc[mt][c][3] = 0.0f;
+                    if (__all_sync(0xffffffffu, fast)) task_mma<BITS, MT, true>(w, s, b, xr, xs, acc);
+                    else task_mma<BITS, MT, false>(w, s, b, xr, xs, acc);
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++)
+                        dstp[mt * 32] = make_float4(acc[mt][0][0] + acc[mt][1][0], acc[mt][0][1] + acc[mt][1][1],
+                                                    acc[mt][0][2] + acc[mt][1][2], acc[mt][0][3] + acc[mt][1][3]);
+                    dstp += nkl * E4;
+                    __syncwarp();  // every lane is done with the stage before it is refilled
+                    src_c = src_c + kStageBytes == ring_lo + D * kStageBytes ? ring_lo : src_c + kStageBytes;
+                }
+            }
+        }
+        // When a matmul is one run of one batch for this warp (K of at most 16 k-blocks, the CTA's tiles in one
+        // batch), the x fragments of the NEXT matmul are requested here, before the block meets: their latency is
+        // spent in the sum and the store below instead of in front of the next matmul's first task.
+        // (With 16 rows of x the fragments held across the block barrier spill: measured 16.5 against 11.2 us.)
+        if (MT == 1 && has_work && kb_hi - kb_lo <= kWarps && rt_hi - rt_lo <= tb && pi + 1 < p.n_items) {
+            load_x_item<BITS, MT>(p.items[pi + 1].x, p.items[pi + 1].M, p.K, kb_lo + warp, g, t, xr);
+            x_ahead = true;
+        }
+        // End of the batch: sum the per-k-block partials of every tile in k-block order and write y.
+        {
+            constexpr int E = 128 * MT;
+            __syncthreads();
+            for (int ti = tid / E; ti < nt; ti += kThreads / E)
+                store_tile_item<MT>(y_cur, M_cur, p.N, p.y_bf16, b0 + ti, tid % E,
+                                    ordered_sum<false>(reinterpret_cast<const float*>(part) + ti * nkl * E + tid % E, nkl, E, 0.0f));
+            __syncthreads();  // the partial buffer is reused by the next batch (of this matmul or the next)
+        }
+    }
+    }
+    cp_async_wait<0>();
+}
+
 struct Plan {
     int nkb, n_rt, mt, chunks, ks, tb, gshift, sb_bytes, xs_off, yt_off;
     size_t smem, scratch_bytes;
@@ -892,6 +1125,52 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
          : a.pro == 2 ? launch_t<8, 1, 2>(p, pl, stream, overlap_prev) : launch_t<8, 1, 0>(p, pl, stream, overlap_prev);
 }
 
+
+// Several matmuls of one shape in one launch (qmv_batch_kernel).  All items: the shape of items[0] but for M, with
+// M on the same side of 8; bf16; no K split for that shape.  cudaErrorNotSupported otherwise.
+template <int BITS, int MT>
+cudaError_t launch_batch_t(const BatchParams& p, const Plan& pl, cudaStream_t stream) {
+    auto kern = qmv_batch_kernel<BITS, MT>;
+    static std::atomic<size_t> attr_smem[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_smem[dev & 63].load() < pl.smem) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem);
+        if (e != cudaSuccess) return e;
+        attr_smem[dev & 63].store(pl.smem);
+    }
+    kern<<<pl.chunks, kThreads, pl.smem, stream>>>(p);
+    return cudaGetLastError();
+}
+int qmv_batch_max() { return kMaxBatch; }
+cudaError_t launch_qmv_batch(const QmmArgs* items, int n, int sm_count, cudaStream_t stream, const char** name) {
+    if (n < 1 || n > kMaxBatch) return cudaErrorInvalidValue;
+    Plan pl;
+    QmmArgs a0 = items[0];
+    int mmax = 0;
+    for (int i = 0; i < n; i++) mmax = std::max(mmax, items[i].M);
+    a0.M = mmax;
+    if (!make_plan(a0, sm_count, &pl) || pl.ks != 1) return cudaErrorNotSupported;
+    BatchParams p;
+    p.n_items = n;
+    p.K = a0.K; p.N = a0.N; p.gshift = pl.gshift;
+    p.y_bf16 = a0.y_dtype == LUX_DTYPE_BFLOAT16;
+    p.nkb = pl.nkb; p.n_rt = pl.n_rt; p.chunks = pl.chunks; p.tb = pl.tb; p.sb_bytes = pl.sb_bytes; p.xs_off = pl.xs_off;
+    for (int i = 0; i < n; i++) {
+        const QmmArgs& a = items[i];
+        if (a.K != a0.K || a.N != a0.N || a.bits != a0.bits || a.group != a0.group || a.y_dtype != a0.y_dtype ||
+            a.x_dtype != LUX_DTYPE_BFLOAT16 || a.sb_dtype != LUX_DTYPE_BFLOAT16 || a.M < 1 || (a.M <= 8) != (mmax <= 8) || a.pro)
+            return cudaErrorNotSupported;
+        if (((uintptr_t)a.wq | (uintptr_t)a.x | (uintptr_t)a.scales | (uintptr_t)a.biases) & 15) return cudaErrorInvalidValue;
+        p.items[i] = BatchItem{(const __nv_bfloat16*)a.x, a.wq, (const __nv_bfloat16*)a.scales, (const __nv_bfloat16*)a.biases, a.y, a.M, 0};
+    }
+    if (a0.bits == 4) {
+        if (name) *name = pl.mt == 1 ? "qmv_batch<4,m8>" : "qmv_batch<4,m16>";
+        return pl.mt == 1 ? launch_batch_t<4, 1>(p, pl, stream) : launch_batch_t<4, 2>(p, pl, stream);
+    }
+    if (name) *name = pl.mt == 1 ? "qmv_batch<8,m8>" : "qmv_batch<8,m16>";
+    return pl.mt == 1 ? launch_batch_t<8, 1>(p, pl, stream) : launch_batch_t<8, 2>(p, pl, stream);
+}
 
 // ---------------------------------------------------------------------------------
 // Decode GEMV without any allocation: the scratch lives in the library image.

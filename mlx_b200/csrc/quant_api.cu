@@ -363,6 +363,75 @@ LuxBackendError qmatmul_pro(LuxBackendContext* ctx, LuxBackendBuffer* x, LuxBack
     return LUX_BACKEND_OK;
 }
 
+LuxBackendError qmatmul_batch(LuxBackendContext* ctx, int n, LuxBackendBuffer* const* x, LuxBackendBuffer* const* wq,
+                              LuxBackendBuffer* const* scales, LuxBackendBuffer* const* biases, LuxBackendBuffer* const* y,
+                              const int* M, int K, int N, int bits, int group, LuxBackendDtype y_dtype) {
+    Context* c = as_ctx(ctx);
+    if (!c || n < 0 || (n && (!x || !wq || !scales || !biases || !y || !M)) || N < 0) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    LuxBackendError fe = check_format(K, bits, group);
+    if (fe != LUX_BACKEND_OK) return fe;
+    const size_t ys = dtype_size(y_dtype);
+    if (!ys) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (n == 0 || N == 0) return LUX_BACKEND_OK;
+    std::vector<QmmArgs> items((size_t)n);
+    bool decode = true;
+    for (int i = 0; i < n; i++) {
+        Buffer *bx = as_buf(x[i]), *bw = as_buf(wq[i]), *bs = as_buf(scales[i]), *bb = as_buf(biases[i]), *by = as_buf(y[i]);
+        if (!bx || !bw || !bs || !bb || !by || M[i] < 1) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+        if ((size_t)M[i] * K * 2 > bx->bytes || (size_t)N * K * bits / 8 > bw->bytes || (size_t)N * (K / group) * 2 > bs->bytes ||
+            (size_t)N * (K / group) * 2 > bb->bytes || (size_t)M[i] * N * ys > by->bytes) {
+            set_last_error("qmatmul_batch: a buffer of item %d is smaller than its shape needs", i);
+            return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+        }
+        if (((uintptr_t)bx->ptr | (uintptr_t)bw->ptr | (uintptr_t)bs->ptr | (uintptr_t)bb->ptr | (uintptr_t)by->ptr) & 15) {
+            set_last_error("qmatmul_batch: buffers must be 16-byte aligned");
+            return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+        }
+        items[i] = QmmArgs{bx->ptr, (const uint32_t*)bw->ptr, bs->ptr, bb->ptr, by->ptr, M[i], K, N, bits, group,
+                           (int)LUX_DTYPE_BFLOAT16, (int)LUX_DTYPE_BFLOAT16, (int)y_dtype};
+        items[i].error = c->err_dev;
+        decode = decode && M[i] <= 16;
+    }
+    std::lock_guard<std::mutex> lk(c->mu);
+    DeviceGuard g(c->dev->device());
+    const char* name = "";
+    bool batched = false;
+    if (decode) {
+        // the items with M <= 8 and those with M > 8, each kind in launches of at most qmv_batch_max()
+        batched = true;
+        std::vector<QmmArgs> kind;
+        for (int hi = 0; hi < 2 && batched; hi++) {
+            kind.clear();
+            for (const QmmArgs& a : items)
+                if ((a.M > 8) == (hi == 1)) kind.push_back(a);
+            for (size_t i0 = 0; i0 < kind.size() && batched; i0 += (size_t)qmv_batch_max()) {
+                const int cnt = (int)std::min(kind.size() - i0, (size_t)qmv_batch_max());
+                cudaError_t e = launch_qmv_batch(kind.data() + i0, cnt, c->dev->sm_count, c->stream, &name);
+                if (e == cudaErrorNotSupported && hi == 0 && i0 == 0) {
+                    cudaGetLastError();
+                    batched = false;  // nothing launched yet: one by one below
+                } else if (e != cudaSuccess) {
+                    return map_cuda_error(e, name);
+                } else {
+                    c->launches++;
+                }
+            }
+        }
+    }
+    if (!batched) {
+        for (const QmmArgs& a : items) {
+            LuxBackendError r = qmatmul_on_stream(c, a);
+            if (r != LUX_BACKEND_OK) return r;
+        }
+    } else {
+        c->last_kernel = name;
+    }
+    for (int i = 0; i < n; i++)
+        as_buf(x[i])->last_stream = as_buf(wq[i])->last_stream = as_buf(scales[i])->last_stream = as_buf(biases[i])->last_stream =
+            as_buf(y[i])->last_stream = c->stream;
+    return LUX_BACKEND_OK;
+}
+
 // --- buffer interop ---------------------------------------------------------
 void* buffer_device_ptr(LuxBackendContext*, LuxBackendBuffer* buf) {
     Buffer* b = as_buf(buf);
@@ -560,6 +629,7 @@ void fill_quant() {
     g_quant.sum3 = sum3;
     g_quant.mul_rms_norm = mul_rms_norm;
     g_quant.qmatmul_pro = qmatmul_pro;
+    g_quant.qmatmul_batch = qmatmul_batch;
 }
 
 }  // namespace

@@ -139,6 +139,8 @@ class QuantVtbl(C.Structure):  # include/lux_cuda_quant.h: lux_gpu_quant_vtbl
         ("mul_rms_norm", _fn(_i, _vp, _vp, _vp, _sz, _sz, _sz, C.c_float)),
         # version >= 4
         ("qmatmul_pro", _fn(_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _sz, C.c_float)),
+        # version >= 5
+        ("qmatmul_batch", _fn(_i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i)),
     ]
 
 
@@ -378,6 +380,14 @@ class Context:
         """y = prologue(x) . dequant(Wq)^T in one decode launch (M <= 8, bf16): PRO_RMS_NORM | PRO_SUM3."""
         self.plugin.check(self.plugin.quant.qmatmul_pro(self.handle, x.handle, wq.handle, scales.handle, biases.handle, y.handle,
                                                         M, K, N, bits, group, y_dtype, prologue, x_ld, eps), "qmatmul_pro")
+
+    def qmatmul_batch(self, xs, wqs, scales, biases, ys, Ms, K, N, bits, group, y_dtype):
+        """Independent decode matmuls of one shape (lists of buffers, one M per item) in one call."""
+        n = len(xs)
+        arr = lambda bufs: (C.c_void_p * n)(*[b.handle.value if isinstance(b.handle, C.c_void_p) else C.cast(b.handle, C.c_void_p).value for b in bufs])
+        keep = [arr(xs), arr(wqs), arr(scales), arr(biases), arr(ys), (C.c_int * n)(*Ms)]
+        self.plugin.check(self.plugin.quant.qmatmul_batch(self.handle, n, *[C.cast(a, C.c_void_p) for a in keep], K, N, bits, group, y_dtype),
+                          "qmatmul_batch")
 
     def timer_record(self, slot):
         self.plugin.check(self.plugin.quant.timer_record(self.handle, slot), "timer_record")

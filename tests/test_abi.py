@@ -61,7 +61,7 @@ def test_descriptor_and_layout():
 def test_quant_table():
     p = mlx_b200.Plugin(require_gpu=False)
     q = p.quant
-    assert q.magic == P.QUANT_MAGIC and q.version == 4 and q.size == C.sizeof(P.QuantVtbl)
+    assert q.magic == P.QUANT_MAGIC and q.version == 5 and q.size == C.sizeof(P.QuantVtbl)
     getter = p.lib.lux_gpu_cuda_quant_vtbl()
     assert C.addressof(getter.contents) == p.vtbl._reserved[0]
     for name, _ in P.QuantVtbl._fields_[4:]:
@@ -117,6 +117,7 @@ def test_tensor_op_slots_are_filled_and_reject_null():
     assert p.quant.sum3(None, None, None, 1, 4, 12) == P.ERR_INVALID
     assert p.quant.mul_rms_norm(None, None, None, 1, 4, 8, 1e-6) == P.ERR_INVALID
     assert p.quant.qmatmul_pro(None, None, None, None, None, None, 1, 64, 1, 4, 64, 0, P.PRO_SUM3, 192, 0.0) == P.ERR_INVALID
+    assert p.quant.qmatmul_batch(None, 1, None, None, None, None, None, None, 64, 1, 4, 64, 0) == P.ERR_INVALID
 
 
 STUB_SRC = r"""

@@ -265,3 +265,51 @@ def test_scale_extremes_bit_exact(ctx, oracle, bits, group):
     y, kern = run_qmatmul(ctx, x, wq, s, b, bits, group, F32)
     assert kern.startswith("qmv_mma")
     check(oracle, y, x, wq, s, b, bits, group, oracle.BF16)
+
+
+@pytest.mark.parametrize("K,N,bits,group,Ms", [(4096, 1200, 4, 64, [1, 4, 8, 16, 3, 12, 8, 1]), (2048, 528, 8, 128, [2, 16, 16, 7]),
+                                                  (1024, 100, 4, 32, [5]), (8192, 64, 4, 64, [8, 1, 16])])
+def test_batch_equals_single_calls(ctx, oracle, K, N, bits, group, Ms):
+    """qmatmul_batch runs independent decode matmuls of one shape in as few persistent launches as their M allow (the
+    last shape is one whose K the decode kernel splits over CTAs: the call then runs them one by one).  Either way
+    every result must be the bits of a qmatmul call of its own, and within the bar of the oracle."""
+    layers, xs, want = [], [], []
+    for i, M in enumerate(Ms):
+        wq, s, b = oracle.make_layer(N, K, bits, group, oracle.BF16, config_id=7, layer=i, proj=N)
+        x = oracle.make_x(M, K, oracle.BF16, config_id=7, layer=i, tag=M)
+        bw, bs, bb, bx = ctx.upload(wq), ctx.upload(s), ctx.upload(b), ctx.upload(x)
+        y = ctx.empty((M, N), np.uint16)
+        ctx.qmatmul(bx, bw, bs, bb, y, M, K, N, bits, group, BF16, BF16, BF16)
+        got = y.to_host()
+        check(oracle, got, x, wq, s, b, bits, group, oracle.BF16)
+        layers.append((bw, bs, bb)); xs.append(bx); want.append(got)
+        y.free()
+    ys = [ctx.empty((M, N), np.uint16) for M in Ms]
+    for rep in range(3):
+        for y, M in zip(ys, Ms):
+            y.from_host(np.zeros((M, N), np.uint16))
+        ctx.qmatmul_batch(xs, [l[0] for l in layers], [l[1] for l in layers], [l[2] for l in layers], ys, Ms, K, N, bits, group, BF16)
+        for i, (y, w) in enumerate(zip(ys, want)):
+            assert np.array_equal(y.to_host(), w), (rep, i, Ms[i], ctx.last_kernel())
+    if K <= 4096:
+        assert ctx.last_kernel().startswith("qmv_batch"), ctx.last_kernel()
+    for h in xs + ys + [b for l in layers for b in l]:
+        h.free()
+
+
+def test_batch_of_many_items_and_fp32_output(ctx, oracle):
+    """More items than one launch takes (48), and fp32 results."""
+    K, N, bits, group, n = 1024, 256, 4, 64, 60
+    wq, s, b = oracle.make_layer(N, K, bits, group, oracle.BF16, config_id=7, layer=99)
+    bw, bs, bb = ctx.upload(wq), ctx.upload(s), ctx.upload(b)
+    Ms = [1 + (i % 8) for i in range(n)]
+    xh = [oracle.make_x(M, K, oracle.BF16, config_id=7, layer=i, tag=M) for i, M in enumerate(Ms)]
+    xs = [ctx.upload(x) for x in xh]
+    ys = [ctx.empty((M, N), np.float32) for M in Ms]
+    ctx.qmatmul_batch(xs, [bw] * n, [bs] * n, [bb] * n, ys, Ms, K, N, bits, group, F32)
+    ref = ctx.empty((8, N), np.float32)
+    for i in (0, 7, 47, 48, 59):
+        ctx.qmatmul(xs[i], bw, bs, bb, ref, Ms[i], K, N, bits, group, BF16, BF16, F32)
+        assert np.array_equal(ys[i].to_host(), ref.to_host((Ms[i], N), np.float32)), i
+    for h in xs + ys + [bw, bs, bb, ref]:
+        h.free()
