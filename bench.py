@@ -40,6 +40,7 @@ import numpy as np
 # dram__bytes_read.sum + dram__bytes_write.sum of one qmv_mma launch (M=1) of this workload, from an ncu capture
 # of `bench.py --kernel-only --no-graph` (counters cannot be read inside the timed run)
 NCU_TRAFFIC_BYTES = 25461632.0
+NCU_TRAFFIC_BYTES_BATCH = 920277760.0  # one qmv_batch<4,m8> launch of the sweep (profiles/qmv_batch_decode_sweep_...md)
 SWEEPS_PER_GRAPH = 5  # sweeps (of 4 x 12 launches) recorded in the CUDA graph the timed step replays
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -968,8 +969,12 @@ def run_ours(args, rank, world):
                      "kernel": "qmv_batch<4,m8|m16>" if use_batch else "qmv_mma<4,m8|m16>",
                      ("avg_us_per_matmul" if use_batch else "avg_us_per_launch"): avg_us,
                      "alg_bytes_per_launch": {str(M): alg_bytes(M) for M in M_SWEEP},
-                     "traffic": args.traffic_bytes, "traffic_unit": "bytes per launch (ncu dram read+write, M=1 launch)",
-                     "traffic_over_algorithmic": args.traffic_bytes / alg_bytes(1) if args.traffic_bytes else None},
+                     **({"traffic": NCU_TRAFFIC_BYTES_BATCH, "alg_bytes_of_that_launch": R_SETS * sum(alg_bytes(M) for M in M_SWEEP if M <= 8),
+                         "traffic_unit": "bytes per launch (ncu dram read+write of one qmv_batch<4,m8> launch: the 36 matmuls with M <= 8)",
+                         "traffic_over_algorithmic": NCU_TRAFFIC_BYTES_BATCH / (R_SETS * sum(alg_bytes(M) for M in M_SWEEP if M <= 8))}
+                        if use_batch else
+                        {"traffic": args.traffic_bytes, "traffic_unit": "bytes per launch (ncu dram read+write, M=1 launch)",
+                         "traffic_over_algorithmic": args.traffic_bytes / alg_bytes(1) if args.traffic_bytes else None})},
         "per_M": {str(M): per_m[M] for M in M_SWEEP},
         "per_M_batched": per_m_batched,
         "single_calls": single,
