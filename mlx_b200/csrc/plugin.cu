@@ -488,6 +488,10 @@ const LuxEmbeddedKernel g_kernels[] = {
     {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<8,m8,rms>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<8,m8,sum3>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {LUX_CUDA_QMM_KERNEL_NAME, "qmv_mma<8,m16>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_batch<4,m8>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},  // several decode matmuls of one shape per launch
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_batch<4,m16>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_batch<8,m8>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_batch<8,m16>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<4>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},       // prefill GEMM (tcgen05), M > 16
     {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<8>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<4,stream-k>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},  // the same, k-stages split evenly over the SMs
