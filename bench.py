@@ -709,29 +709,62 @@ def run_ours(args, rank, world):
                     launch(M, r)
         graph_sweeps = ctx.graph_end()
 
-    # One GPU: the matmuls of a sweep are independent, so the timed step hands each sweep to the plugin as ONE call
-    # (qmatmul_batch: a persistent launch for the items with M <= 8, one for those with M = 16) instead of 48 calls.
-    # Every item has its own output buffer; three of them are checked against the single calls, bit for bit.
-    use_batch = world == 1 and not args.single_calls
-    batch_graph, batch_verified = None, None
+    # The matmuls of a sweep are independent, so the timed step hands each sweep to the plugin as ONE call
+    # (qmatmul_batch, on several GPUs qmatmul_sharded_push_batch: a persistent launch for the items with M <= 8, one
+    # for those with M = 16) instead of 48 calls.  Every item has its own output (on several GPUs: its own place in
+    # one symmetric buffer, whole on every rank when the call ends); three of them are checked against the single
+    # calls, bit for bit (on several GPUs: all ranks' columns, on every rank).
+    use_batch = (world == 1 or use_push) and not args.single_calls
+    batch_graph, batch_verified, symm_all = None, None, None
     if use_batch:
         b_items = [(M, r) for M in M_SWEEP for r in range(R_SETS)]
-        b_y = {it: ctx.empty((it[0], N_DEC), np.uint16) for it in b_items}
+        if world == 1:
+            b_y = {it: ctx.empty((it[0], N_DEC), np.uint16) for it in b_items}
 
-        def batch_call(items):
-            ctx.qmatmul_batch([x_dev[M] for M, r in items], [layers[r][0] for M, r in items], [layers[r][1] for M, r in items],
-                              [layers[r][2] for M, r in items], [b_y[it] for it in items], [M for M, r in items],
-                              K_DEC, N_DEC, BITS, GROUP, BF16)
+            def batch_call(items):
+                ctx.qmatmul_batch([x_dev[M] for M, r in items], [layers[r][0] for M, r in items], [layers[r][1] for M, r in items],
+                                  [layers[r][2] for M, r in items], [b_y[it] for it in items], [M for M, r in items],
+                                  K_DEC, N_DEC, BITS, GROUP, BF16)
+
+            def item_host(it):
+                return b_y[it].to_host()
+        else:
+            import torch
+            b_off, rows = {}, 0
+            for it in b_items:
+                b_off[it] = rows * n_total * 2
+                rows += it[0]
+            symm_all = mlx_b200.plugin.SymmBuffer(ctx, rank, world, (rows, n_total), np.uint16)
+            mine = torch.tensor(list(symm_all.export()), dtype=torch.uint8, device="cuda")
+            every = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(every, mine)
+            symm_all.attach([bytes(t.cpu().tolist()) for t in every])
+            dist.barrier()
+
+            def batch_call(items):
+                symm_all.qmatmul_batch([x_dev[M] for M, r in items], [layers[r][0] for M, r in items], [layers[r][1] for M, r in items],
+                                       [layers[r][2] for M, r in items], [b_off[it] for it in items], [M for M, r in items],
+                                       K_DEC, N_DEC, BITS, GROUP, BF16)
+
+            def item_host(it):
+                return symm_all.item_to_host(b_off[it], (it[0], n_total), np.uint16)
         batch_call(b_items)
         batch_kernel = ctx.last_kernel()
         ctx.sync()
         bad = []
         for it in ((1, 0), (8, R_SETS - 1), (16, R_SETS // 2)):
             launch(*it)
-            if not np.array_equal(b_y[it].to_host(), y_dev[it[0]].to_host()[:, :N_DEC]):
+            if not np.array_equal(item_host(it), y_dev[it[0]].to_host((it[0], n_total), np.uint16)):
                 bad.append(it)
+        if dist is not None:
+            import torch
+            t = torch.tensor([len(bad)], dtype=torch.int64, device="cuda")
+            dist.all_reduce(t)
+            if int(t.item()) and not bad:
+                bad = ["(on another rank)"]
         batch_verified = (f"FAILED: items {bad} differ from single calls" if bad else
-                          "items (M=1, set 0), (M=8, last set), (M=16, middle set) of a batched sweep bit-identical to single qmatmul calls")
+                          "items (M=1, set 0), (M=8, last set), (M=16, middle set) of a batched sweep bit-identical to single "
+                          + ("qmatmul calls" if world == 1 else "sharded calls: every rank's columns, compared on every rank"))
         if bad:
             print(batch_verified, file=sys.stderr, flush=True)
         if use_graph:
@@ -838,7 +871,7 @@ def run_ours(args, rank, world):
                     batch_call(its)
             run_b()
             ms = timed(run_b, 2, 3)
-            per_m_batched[str(M)] = {"us_per_matmul": ms * 1e3 / (reps_m * len(its)), "GBps": alg_bytes(M) * reps_m * len(its) / ms / 1e6,
+            per_m_batched[str(M)] = {"us_per_matmul": ms * 1e3 / (reps_m * len(its)), "GBps": alg_bytes(M) * world * reps_m * len(its) / ms / 1e6,
                                      "kernel": batch_kernel if M > 8 else batch_kernel.replace("m16", "m8")}
     sweep_bytes = sum(alg_bytes(M) for M in M_SWEEP) * R_SETS * world
     total_bytes = sweep_bytes * args.reps * args.steps
@@ -938,6 +971,8 @@ def run_ours(args, rank, world):
             q.shard_comm_destroy(comm)
         for sb in symm.values():
             sb.free()
+        if symm_all is not None:
+            symm_all.free()
         dist.destroy_process_group()
     if rank != 0:
         return
@@ -955,18 +990,19 @@ def run_ours(args, rank, world):
         "run": {"layout": "one GPU" if world == 1 else f"weak scaling: each of {world} ranks holds its own {N_DEC}-column slice of a "
                           f"{n_total}-column layer and every rank ends with the whole y (all-gather of output slices)",
                    "N_total": n_total, "weight_sets": R_SETS, "sweeps_per_step": args.reps, "cuda_graph": use_graph,
-                   "calls": ("one qmatmul_batch call per sweep: its 48 independent matmuls run as two persistent launches (36 with M <= 8, "
+                   "calls": (("one qmatmul_batch" if world == 1 else "one qmatmul_sharded_push_batch") + " call per sweep: its 48 independent matmuls run as two persistent launches (36 with M <= 8, "
                              "12 with M = 16)" if use_batch else "one call (one launch) per matmul"),
                    "batch_verified": batch_verified,
                    "launches_per_graph": (SWEEPS_PER_GRAPH * (2 if use_batch else len(M_SWEEP) * R_SETS)) if use_graph else None,
-                   "allgather": None if world == 1 else ("peer stores from the decode kernel (one launch per call)" if use_push
+                   "allgather": None if world == 1 else (("peer stores from the batched decode kernel, the ranks meet once per launch" if use_batch else
+                                                          "peer stores from the decode kernel (one launch per call)") if use_push
                                                          else "NCCL all-gather + interleave pass"),
                    "verified": verified,
                    "l2": f"inputs larger than L2: {R_SETS} rotating weight sets = {R_SETS * alg_bytes(1) / 1e6:.0f} MB, "
                          "each launch reads a set last touched 11 launches earlier"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": which, "frac_of_nominal_8TBps": achieved / NOMINAL_HBM_GBS,
-                     "kernel": "qmv_batch<4,m8|m16>" if use_batch else "qmv_mma<4,m8|m16>",
+                     "kernel": ("qmv_batch<4,m8|m16>" if world == 1 else "qmv_batch<4,m8|m16,push>") if use_batch else "qmv_mma<4,m8|m16>",
                      ("avg_us_per_matmul" if use_batch else "avg_us_per_launch"): avg_us,
                      "alg_bytes_per_launch": {str(M): alg_bytes(M) for M in M_SWEEP},
                      **({"traffic": NCU_TRAFFIC_BYTES_BATCH, "alg_bytes_of_that_launch": R_SETS * sum(alg_bytes(M) for M in M_SWEEP if M <= 8),

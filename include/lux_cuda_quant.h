@@ -51,7 +51,7 @@ extern "C" {
 #define LUX_CUDA_QUANT_MAGIC 0x4C515854u /* "LQXT" */
 #define LUX_CUDA_PRO_RMS_NORM 1
 #define LUX_CUDA_PRO_SUM3 2
-#define LUX_CUDA_QUANT_VERSION 5u /* 2: symm_* and qmatmul_sharded_push appended; 3: sum3, mul_rms_norm; 4: qmatmul_pro; 5: qmatmul_batch */
+#define LUX_CUDA_QUANT_VERSION 6u /* 2: symm_* and qmatmul_sharded_push appended; 3: sum3, mul_rms_norm; 4: qmatmul_pro; 5: qmatmul_batch; 6: qmatmul_sharded_push_batch */
 #define LUX_CUDA_QMM_KERNEL_NAME "lux.qmm.affine"
 #define LUX_CUDA_NCCL_UID_BYTES 128
 
@@ -239,6 +239,21 @@ typedef struct lux_gpu_quant_vtbl {
                                      LuxBackendBuffer* const* scales, LuxBackendBuffer* const* biases,
                                      LuxBackendBuffer* const* y, const int* M, int K, int N, int bits, int group,
                                      LuxBackendDtype y_dtype);
+
+    /* --- several independent column-sharded decode matmuls of one shape in one call (version >= 6) ---
+     * qmatmul_batch for a layer whose columns are sharded over ranks: item i's full output y_i[M[i], world*Nl]
+     * lies at byte offset y_offset[i] (a multiple of 16; the outputs do not overlap) of the symmetric buffer, on
+     * every rank; this rank computes columns [rank*Nl, (rank+1)*Nl) of every item and the kernel stores them
+     * into all ranks' copies as it goes from one matmul to the next.  The ranks meet once per launch, not once per
+     * matmul (up to 48 matmuls per launch; items with M <= 8 and with M > 8 in separate launches): when the
+     * call's work on the stream ends, every y_i is whole on this rank.  The same rules as qmatmul_sharded_push
+     * (same calls in the same order on all ranks, bf16, Nl a multiple of 16, M[i] <= 16); results are the bits
+     * of qmatmul_sharded_push item by item.  Shapes the batched kernel does not take (K split over CTAs) run as n
+     * single pushes inside the call. */
+    LuxBackendError (*qmatmul_sharded_push_batch)(LuxCudaSymmBuffer* y_all, int n, LuxBackendBuffer* const* x,
+                                                  LuxBackendBuffer* const* wq_local, LuxBackendBuffer* const* scales_local,
+                                                  LuxBackendBuffer* const* biases_local, const size_t* y_offset, const int* M,
+                                                  int K, int N_local, int bits, int group, LuxBackendDtype y_dtype);
 } lux_gpu_quant_vtbl;
 
 /* Entry points exported with default visibility. */

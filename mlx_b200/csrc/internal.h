@@ -205,7 +205,10 @@ void note_decode_launch(Context* c, const QmmArgs& a);  // call right after a de
 cudaError_t launch_qmv_simt(const QmmArgs& a, cudaStream_t stream, const char** name);
 // several decode matmuls of one shape (M on one side of 8) as one persistent launch; at most qmv_batch_max() items
 int qmv_batch_max();
-cudaError_t launch_qmv_batch(const QmmArgs* items, int n, int sm_count, cudaStream_t stream, const char** name);
+// push (column-sharded layer, world > 1): every item's y lies inside this rank's symmetric buffer and the launch
+// delivers its columns to the same place of every peer's
+cudaError_t launch_qmv_batch(const QmmArgs* items, int n, int sm_count, cudaStream_t stream, const char** name,
+                             const ShardPush* push = nullptr);
 // prefill GEMM, bf16 activations: TMA + tcgen05 + TMEM
 bool qmm_tc_supported(const QmmArgs& a);
 size_t qmm_tc_workspace_bytes(int sm_count);  // scratch of a launch (flags at its head: zero between launches)

@@ -113,7 +113,9 @@ struct Params {
 // of that call has started -- everything it enqueued before has then finished with its y and inbox -- and a
 // sender waits for it before its first remote store.  Waits are bounded (Params::peer_wait_ns): on a time-out the
 // kernel raises the host-visible error word, stops waiting (in every later launch too) and returns.
-constexpr int kFlagEpoch = 0, kFlagCtaDone = 1, kFlagReady = 8;
+// (kFlagDone + q: the number of the last call of which rank q has delivered ALL its columns here -- the batched
+// kernel stores straight into the peers' y and announces once per launch, see qmv_batch_kernel)
+constexpr int kFlagEpoch = 0, kFlagCtaDone = 1, kFlagReady = 8, kFlagDone = 16;
 
 __device__ __forceinline__ long long now_ns() {
     long long t;
@@ -735,13 +737,19 @@ struct BatchItem {
     const __nv_bfloat16* scales;
     const __nv_bfloat16* biases;
     void* y;
-    int M, pad;
+    int M;
+    uint32_t yoff;  // column-sharded: byte offset of this y inside every rank's symmetric buffer
 };
 struct BatchParams {
     int n_items;
     int K, N, gshift, y_bf16;
     int nkb, n_rt, chunks, tb, sb_bytes, xs_off;
     BatchItem items[kMaxBatch];
+    // column-sharded launches only (SH): N is this rank's share of the columns
+    int ld, col0, yt_off;
+    int* error;
+    long long peer_wait_ns;
+    ShardPush sp;
 };
 template <int BITS, int MT>
 __device__ __forceinline__ void load_x_item(const __nv_bfloat16* x, int M, int K, int kb, int g, int t, uint4 (&xr)[MT][BITS == 4 ? 8 : 4]) {
@@ -759,16 +767,24 @@ __device__ __forceinline__ void load_x_item(const __nv_bfloat16* x, int M, int K
         }
     }
 }
+// ytile (column-sharded launches): the tile's values once more in shared memory, [row of x][16 columns]
 template <int MT>
-__device__ __forceinline__ void store_tile_item(void* y, int M, int N, int y_bf16, int rt, int e, float sum) {
+__device__ __forceinline__ void store_tile_item(void* y, int M, int N, int ld, int col0, int y_bf16, int rt, int e, float sum,
+                                                unsigned char* ytile) {
     const int mt = e >> 7, rem = e & 127, ln = rem >> 2, ci = rem & 3;
     const int r16 = (ln >> 2) + 8 * (ci >> 1);
     const int row = rt * 16 + r16;
     const int m = mt * 8 + 2 * (ln & 3) + (ci & 1);
     if (row < N && m < M) {
-        const size_t idx = (size_t)m * N + row;
-        if (y_bf16) reinterpret_cast<__nv_bfloat16*>(y)[idx] = __float2bfloat16_rn(sum);
-        else reinterpret_cast<float*>(y)[idx] = sum;
+        const size_t idx = (size_t)m * ld + col0 + row;
+        if (y_bf16) {
+            const __nv_bfloat16 v = __float2bfloat16_rn(sum);
+            reinterpret_cast<__nv_bfloat16*>(y)[idx] = v;
+            if (ytile) reinterpret_cast<__nv_bfloat16*>(ytile + m * 32)[r16] = v;
+        } else {
+            reinterpret_cast<float*>(y)[idx] = sum;
+            if (ytile) reinterpret_cast<float*>(ytile + m * 64)[r16] = sum;
+        }
     }
 }
 
@@ -778,8 +794,17 @@ __device__ __forceinline__ void store_tile_item(void* y, int M, int N, int y_bf1
 // first of the next, so the start of a launch (first reads of parameters, x and weights) and its tail (the
 // ordered sum and the store of y), which are half of a single decode launch, are paid once per launch instead of
 // once per matmul -- the sum and the store of a matmul run while the next one's weights are already arriving.
-// No K split, no peers, no prologue (the host sends such calls one by one).
-template <int BITS, int MT>
+// No K split, no prologue (the host sends such calls one by one).
+//
+// SH: the layer is column-sharded over ranks and every y lives at the same offset of every rank's symmetric buffer.
+// The finished tiles of a matmul (staged in shared memory as they are stored locally) go straight into the peers'
+// copies of y, 16 bytes a store, while the warps are already in the next matmul.  The hand-shakes are paid once
+// per launch instead of once per matmul: ready[q] as in qmv_mma_kernel (before the first remote store: has every
+// peer started this call, i.e. is it done with its y of earlier calls?), and at the end done[q] = call number,
+// written by a rank's last CTA to finish -- behind a system-wide fence, every CTA having fenced its own stores
+// before it counted itself in -- into every peer's flag words; that CTA then waits (bounded) for the peers' done
+// words, so that the launch ends with y whole on this rank and stream order is all a consumer needs.
+template <int BITS, int MT, bool SH>
 __global__ void __launch_bounds__(kThreads, 1) qmv_batch_kernel(const __grid_constant__ BatchParams p) {
     constexpr int XV = BITS == 4 ? 8 : 4;  // x fragments (uint4) per lane per k-block per 8-row block
     constexpr int KB = 1024 / BITS;        // weights per k-block (128 bytes per row)
@@ -871,6 +896,16 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_batch_kernel(const __grid_con
     bool x_ahead = false;  // xr already holds the fragments of the run about to start
 #pragma unroll
     for (int i = 0; i < D - 1; i++) fetch_next();
+    // column-sharded: this call's number, and the word to the peers that our copies of y may be overwritten
+    // (the launch is an ordinary one: whatever this rank enqueued before has finished with them)
+    uint32_t epoch = 0;
+    bool peers_ready = true, ready_checked = !SH;
+    if (SH) {
+        epoch = *reinterpret_cast<volatile uint32_t*>(p.sp.flags[p.sp.me] + kFlagEpoch) + 1;
+        if (blockIdx.x == 0 && tid < p.sp.world && tid != p.sp.me) st_relaxed_sys(p.sp.flags[tid] + kFlagReady + p.sp.me, epoch);
+    }
+    unsigned char* const ytiles = SH ? smem + p.yt_off : nullptr;
+    const int yt_bytes = p.y_bf16 ? 512 : 1024;  // of a staged tile
     uint32_t src_c = ring_lo;  // stage of the task computed next (this lane's slot)
     uint32_t sboff[2][2];      // byte offsets of this lane's scales inside a stage, by row half r and piece h
 #pragma unroll 1
@@ -946,18 +981,65 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_batch_kernel(const __grid_con
             load_x_item<BITS, MT>(p.items[pi + 1].x, p.items[pi + 1].M, p.K, kb_lo + warp, g, t, xr);
             x_ahead = true;
         }
+        if (SH && !ready_checked) {  // before the first remote store: has every peer started this call?
+            ready_checked = true;
+            int ok = 1;
+            if (tid < p.sp.world && tid != p.sp.me) ok = wait_flag(p.sp.flags[p.sp.me] + kFlagReady + tid, epoch, p.peer_wait_ns);
+            peers_ready = __syncthreads_and(ok);
+            if (!peers_ready && tid == 0 && p.error) *p.error = 2;  // nothing is sent; the host learns of it at its next sync
+        }
         // End of the batch: sum the per-k-block partials of every tile in k-block order and write y.
         {
             constexpr int E = 128 * MT;
             __syncthreads();
             for (int ti = tid / E; ti < nt; ti += kThreads / E)
-                store_tile_item<MT>(y_cur, M_cur, p.N, p.y_bf16, b0 + ti, tid % E,
-                                    ordered_sum<false>(reinterpret_cast<const float*>(part) + ti * nkl * E + tid % E, nkl, E, 0.0f));
+                store_tile_item<MT>(y_cur, M_cur, p.N, SH ? p.ld : p.N, SH ? p.col0 : 0, p.y_bf16, b0 + ti, tid % E,
+                                    ordered_sum<false>(reinterpret_cast<const float*>(part) + ti * nkl * E + tid % E, nkl, E, 0.0f),
+                                    SH ? ytiles + ti * yt_bytes : nullptr);
             __syncthreads();  // the partial buffer is reused by the next batch (of this matmul or the next)
+        }
+        if (SH && peers_ready) {
+            // The staged tiles go to the peers, a 16-byte piece of a row per store.  (The staging area is written
+            // again only behind the first barrier of the next batch end, which a thread reaches after these reads.)
+            const int esz = p.y_bf16 ? 2 : 4;            // also the number of 16-byte pieces of a tile row
+            const int per_tile = M_cur * esz, per_peer = nt * per_tile;
+            const int total = per_peer * (p.sp.world - 1);
+            const uint32_t yoff = p.items[pi].yoff;
+            for (int i = tid; i < total; i += kThreads) {
+                int q = i / per_peer;
+                const int j = i - q * per_peer;
+                q += q >= p.sp.me;
+                const int ti = j / per_tile, r = j - ti * per_tile, m = r / esz, k = r - m * esz;
+                const uint4 v = *reinterpret_cast<const uint4*>(ytiles + ti * yt_bytes + m * (16 * esz) + k * 16);
+                char* dst = static_cast<char*>(p.sp.y[q]) + yoff + ((size_t)m * p.ld + p.col0 + (size_t)(b0 + ti) * 16) * esz + k * 16;
+                *reinterpret_cast<uint4*>(dst) = v;
+            }
         }
     }
     }
     cp_async_wait<0>();
+    if (SH) {
+        __syncthreads();  // every remote store of this CTA has been issued
+        if (tid == 0) {
+            __threadfence_system();  // ... and is ordered before the count below, for every observer
+            uint32_t* lf = p.sp.flags[p.sp.me];
+            if (atomicAdd(lf + kFlagCtaDone, 1u) == gridDim.x - 1) {  // the last CTA of this rank
+                lf[kFlagCtaDone] = 0;
+                bool ok = peers_ready;
+                if (ok) {
+                    __threadfence_system();
+                    for (int q = 0; q < p.sp.world; q++)
+                        if (q != p.sp.me) st_relaxed_sys(p.sp.flags[q] + kFlagDone + p.sp.me, epoch);
+                    for (int q = 0; q < p.sp.world; q++)
+                        if (q != p.sp.me) ok = wait_flag(lf + kFlagDone + q, epoch, p.peer_wait_ns) && ok;
+                    __threadfence_system();
+                }
+                if (!ok && p.error) *p.error = 2;
+                // (a plain store: the next launch reads the call number only after this one has completed)
+                *reinterpret_cast<volatile uint32_t*>(lf + kFlagEpoch) = epoch;
+            }
+        }
+    }
 }
 
 struct Plan {
@@ -1128,9 +1210,9 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
 
 // Several matmuls of one shape in one launch (qmv_batch_kernel).  All items: the shape of items[0] but for M, with
 // M on the same side of 8; bf16; no K split for that shape.  cudaErrorNotSupported otherwise.
-template <int BITS, int MT>
+template <int BITS, int MT, bool SH>
 cudaError_t launch_batch_t(const BatchParams& p, const Plan& pl, cudaStream_t stream) {
-    auto kern = qmv_batch_kernel<BITS, MT>;
+    auto kern = qmv_batch_kernel<BITS, MT, SH>;
     static std::atomic<size_t> attr_smem[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1143,15 +1225,27 @@ cudaError_t launch_batch_t(const BatchParams& p, const Plan& pl, cudaStream_t st
     return cudaGetLastError();
 }
 int qmv_batch_max() { return kMaxBatch; }
-cudaError_t launch_qmv_batch(const QmmArgs* items, int n, int sm_count, cudaStream_t stream, const char** name) {
+cudaError_t launch_qmv_batch(const QmmArgs* items, int n, int sm_count, cudaStream_t stream, const char** name,
+                             const ShardPush* push) {
     if (n < 1 || n > kMaxBatch) return cudaErrorInvalidValue;
+    const bool sh = push && push->world > 1;
     Plan pl;
     QmmArgs a0 = items[0];
     int mmax = 0;
     for (int i = 0; i < n; i++) mmax = std::max(mmax, items[i].M);
     a0.M = mmax;
-    if (!make_plan(a0, sm_count, &pl) || pl.ks != 1) return cudaErrorNotSupported;
+    if (!make_plan(a0, sm_count, &pl, sh) || pl.ks != 1) return cudaErrorNotSupported;
     BatchParams p;
+    p.ld = a0.N; p.col0 = 0; p.yt_off = pl.yt_off;
+    p.error = nullptr;
+    p.peer_wait_ns = peer_wait_limit_ns();
+    if (sh) {
+        if (push->world > kMaxShardWorld || (a0.N & 15)) return cudaErrorInvalidValue;  // whole 16-column tiles only
+        p.sp = *push;
+        p.ld = push->ld; p.col0 = push->col0;
+        p.error = a0.error ? a0.error : device_error_word();
+        if (!p.error) return cudaErrorMemoryAllocation;
+    }
     p.n_items = n;
     p.K = a0.K; p.N = a0.N; p.gshift = pl.gshift;
     p.y_bf16 = a0.y_dtype == LUX_DTYPE_BFLOAT16;
@@ -1162,14 +1256,22 @@ cudaError_t launch_qmv_batch(const QmmArgs* items, int n, int sm_count, cudaStre
             a.x_dtype != LUX_DTYPE_BFLOAT16 || a.sb_dtype != LUX_DTYPE_BFLOAT16 || a.M < 1 || (a.M <= 8) != (mmax <= 8) || a.pro)
             return cudaErrorNotSupported;
         if (((uintptr_t)a.wq | (uintptr_t)a.x | (uintptr_t)a.scales | (uintptr_t)a.biases) & 15) return cudaErrorInvalidValue;
-        p.items[i] = BatchItem{(const __nv_bfloat16*)a.x, a.wq, (const __nv_bfloat16*)a.scales, (const __nv_bfloat16*)a.biases, a.y, a.M, 0};
+        uint32_t yoff = 0;
+        if (sh) {  // the item's y lies inside this rank's symmetric buffer: the peers' copies are at the same offset
+            const ptrdiff_t d = static_cast<const char*>(a.y) - static_cast<const char*>(push->y[push->me]);
+            if (d < 0 || d > (ptrdiff_t)0xFFFFFFF0ll || (d & 15)) return cudaErrorInvalidValue;
+            yoff = (uint32_t)d;
+        }
+        p.items[i] = BatchItem{(const __nv_bfloat16*)a.x, a.wq, (const __nv_bfloat16*)a.scales, (const __nv_bfloat16*)a.biases, a.y, a.M, yoff};
     }
     if (a0.bits == 4) {
-        if (name) *name = pl.mt == 1 ? "qmv_batch<4,m8>" : "qmv_batch<4,m16>";
-        return pl.mt == 1 ? launch_batch_t<4, 1>(p, pl, stream) : launch_batch_t<4, 2>(p, pl, stream);
+        if (name) *name = sh ? (pl.mt == 1 ? "qmv_batch<4,m8,push>" : "qmv_batch<4,m16,push>") : (pl.mt == 1 ? "qmv_batch<4,m8>" : "qmv_batch<4,m16>");
+        if (sh) return pl.mt == 1 ? launch_batch_t<4, 1, true>(p, pl, stream) : launch_batch_t<4, 2, true>(p, pl, stream);
+        return pl.mt == 1 ? launch_batch_t<4, 1, false>(p, pl, stream) : launch_batch_t<4, 2, false>(p, pl, stream);
     }
-    if (name) *name = pl.mt == 1 ? "qmv_batch<8,m8>" : "qmv_batch<8,m16>";
-    return pl.mt == 1 ? launch_batch_t<8, 1>(p, pl, stream) : launch_batch_t<8, 2>(p, pl, stream);
+    if (name) *name = sh ? (pl.mt == 1 ? "qmv_batch<8,m8,push>" : "qmv_batch<8,m16,push>") : (pl.mt == 1 ? "qmv_batch<8,m8>" : "qmv_batch<8,m16>");
+    if (sh) return pl.mt == 1 ? launch_batch_t<8, 1, true>(p, pl, stream) : launch_batch_t<8, 2, true>(p, pl, stream);
+    return pl.mt == 1 ? launch_batch_t<8, 1, false>(p, pl, stream) : launch_batch_t<8, 2, false>(p, pl, stream);
 }
 
 // ---------------------------------------------------------------------------------

@@ -9,8 +9,11 @@
 // (include/lux/gpu/backend_plugin.h:84).
 #include <unistd.h>
 
+#include <algorithm>
 #include <cstring>
 #include <new>
+#include <utility>
+#include <vector>
 
 #include "internal.h"
 
@@ -176,6 +179,40 @@ void symm_free(LuxCudaSymmBuffer* sb) {
     delete sb;
 }
 
+// One decode launch that delivers this rank's columns of the y at byte offset `yoff` of the symmetric buffer into
+// every rank's copy (the caller holds the context's lock and has checked the buffers).  The inbox of a y lies at
+// twice its offset in the inbox area, so outputs that do not overlap have inboxes that do not overlap.
+LuxBackendError push_decode_at(LuxCudaSymmBuffer* sb, const QmmArgs& a, size_t yoff) {
+    Context* c = sb->ctx;
+    if (!qmv_mma_supported(a)) {
+        set_last_error("qmatmul_sharded_push: shape not taken by the decode kernel (K must be a multiple of %d)", 1024 / a.bits);
+        return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    }
+    LuxBackendError le = ensure_qmv_workspace(c, qmv_mma_workspace_bytes(a, c->dev->sm_count));
+    if (le != LUX_BACKEND_OK) return le;
+    ShardPush sp;
+    sp.world = sb->world;
+    sp.me = sb->rank;
+    sp.ld = a.N * sb->world;
+    sp.col0 = sb->rank * a.N;
+    sp.inbox_off = ((sb->bytes + 255) & ~size_t(255)) + yoff;  // from the y at yoff: (inbox area - yoff) + 2 * yoff
+    for (int r = 0; r < sb->world; r++) {
+        sp.flags[r] = static_cast<uint32_t*>(sb->peer_base[r]);
+        sp.y[r] = static_cast<char*>(sb->peer_base[r]) + kHeader + yoff;
+    }
+    QmmArgs local = a;
+    local.y = static_cast<char*>(sb->view.ptr) + yoff;
+    QmmArgs whole = local;  // what the launch writes, for the chain bookkeeping: every column of the local copy
+    whole.N = sp.ld;
+    const char* name = "";
+    cudaError_t e = launch_qmv_mma(local, c->qmv_ws->ptr, c->dev->sm_count, c->stream, &name, decode_may_overlap(c, local), &sp);
+    if (e != cudaSuccess) return map_cuda_error(e, name);
+    c->last_kernel = name;
+    c->launches++;
+    note_decode_launch(c, whole);
+    return LUX_BACKEND_OK;
+}
+
 LuxBackendError qmatmul_sharded_push(LuxCudaSymmBuffer* sb, LuxBackendBuffer* x, LuxBackendBuffer* wq, LuxBackendBuffer* scales,
                                      LuxBackendBuffer* biases, int M, int K, int Nl, int bits, int group,
                                      LuxBackendDtype y_dtype) {
@@ -246,12 +283,61 @@ LuxBackendError qmatmul_sharded_push(LuxCudaSymmBuffer* sb, LuxBackendBuffer* x,
         bx->last_stream = bw->last_stream = bs->last_stream = bb->last_stream = sb->view.last_stream = c->stream;
         return LUX_BACKEND_OK;
     }
-    if (!qmv_mma_supported(a)) {
-        set_last_error("qmatmul_sharded_push: shape not taken by the decode kernel (K must be a multiple of %d)", 1024 / bits);
+    LuxBackendError le = push_decode_at(sb, a, 0);
+    if (le == LUX_BACKEND_OK) bx->last_stream = bw->last_stream = bs->last_stream = bb->last_stream = sb->view.last_stream = c->stream;
+    return le;
+}
+
+// n independent decode matmuls of one column-sharded shape, their outputs at given offsets of the symmetric buffer
+LuxBackendError qmatmul_sharded_push_batch(LuxCudaSymmBuffer* sb, int n, LuxBackendBuffer* const* x, LuxBackendBuffer* const* wq,
+                                           LuxBackendBuffer* const* scales, LuxBackendBuffer* const* biases, const size_t* y_offset,
+                                           const int* M, int K, int Nl, int bits, int group, LuxBackendDtype y_dtype) {
+    if (!sb || n < 0 || (n > 0 && (!x || !wq || !scales || !biases || !y_offset || !M))) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (n == 0) return LUX_BACKEND_OK;
+    Context* c = sb->ctx;
+    if (y_dtype != LUX_DTYPE_BFLOAT16 && y_dtype != LUX_DTYPE_FLOAT32) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (!sb->attached) {
+        set_last_error("qmatmul_sharded_push_batch: symm_attach has not been called");
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    }
+    if (Nl < 1 || (Nl & 15) || K < 1 || (bits != 4 && bits != 8) || (group != 32 && group != 64 && group != 128) || K % group) {
+        set_last_error("qmatmul_sharded_push_batch: needs N_local a multiple of 16, bits 4|8, group 32|64|128");
         return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     }
-    LuxBackendError le = ensure_qmv_workspace(c, qmv_mma_workspace_bytes(a, c->dev->sm_count));
-    if (le != LUX_BACKEND_OK) return le;
+    const size_t ys = y_dtype == LUX_DTYPE_BFLOAT16 ? 2 : 4;
+    const size_t ld = (size_t)Nl * sb->world;
+    std::vector<QmmArgs> items((size_t)n);
+    std::vector<std::pair<size_t, size_t>> spans((size_t)n);  // [offset, end) of every output
+    for (int i = 0; i < n; i++) {
+        Buffer *bx = as_buf(x[i]), *bw = as_buf(wq[i]), *bs = as_buf(scales[i]), *bb = as_buf(biases[i]);
+        if (!bx || !bw || !bs || !bb) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+        if (M[i] < 1 || M[i] > 16) {
+            set_last_error("qmatmul_sharded_push_batch: item %d has M = %d (1..16 rows of x per item)", i, M[i]);
+            return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+        }
+        const size_t ybytes = (size_t)M[i] * ld * ys;
+        if ((size_t)M[i] * K * 2 > bx->bytes || (size_t)Nl * K * bits / 8 > bw->bytes || (size_t)Nl * (K / group) * 2 > bs->bytes ||
+            (size_t)Nl * (K / group) * 2 > bb->bytes || (y_offset[i] & 15) || y_offset[i] > sb->bytes || ybytes > sb->bytes - y_offset[i]) {
+            set_last_error("qmatmul_sharded_push_batch: item %d: a buffer is smaller than its shape needs, or its output "
+                           "does not lie inside the symmetric buffer at a multiple of 16 bytes", i);
+            return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+        }
+        spans[i] = {y_offset[i], y_offset[i] + ybytes};
+        items[i] = QmmArgs{bx->ptr, (const uint32_t*)bw->ptr, bs->ptr, bb->ptr, static_cast<char*>(sb->view.ptr) + y_offset[i],
+                           M[i], K, Nl, bits, group, LUX_DTYPE_BFLOAT16, LUX_DTYPE_BFLOAT16, (int)y_dtype};
+        items[i].error = c->err_dev;
+    }
+    {
+        std::vector<std::pair<size_t, size_t>> sorted = spans;
+        std::sort(sorted.begin(), sorted.end());
+        for (int i = 1; i < n; i++)
+            if (sorted[i].first < sorted[i - 1].second) {
+                set_last_error("qmatmul_sharded_push_batch: two outputs overlap");
+                return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+            }
+    }
+    std::lock_guard<std::mutex> lk(c->mu);
+    DeviceGuard g(c->dev->device());
     ShardPush sp;
     sp.world = sb->world;
     sp.me = sb->rank;
@@ -262,15 +348,35 @@ LuxBackendError qmatmul_sharded_push(LuxCudaSymmBuffer* sb, LuxBackendBuffer* x,
         sp.flags[r] = static_cast<uint32_t*>(sb->peer_base[r]);
         sp.y[r] = static_cast<char*>(sb->peer_base[r]) + kHeader;
     }
-    QmmArgs whole = a;  // what the launch writes, for the chain bookkeeping: every column of the local copy
-    whole.N = (int)ld;
-    const char* name = "";
-    cudaError_t e = launch_qmv_mma(a, c->qmv_ws->ptr, c->dev->sm_count, c->stream, &name, decode_may_overlap(c, a), &sp);
-    if (e != cudaSuccess) return map_cuda_error(e, name);
-    c->last_kernel = name;
-    c->launches++;
-    note_decode_launch(c, whole);
-    bx->last_stream = bw->last_stream = bs->last_stream = bb->last_stream = sb->view.last_stream = c->stream;
+    // items with M <= 8 and with M > 8 are different instantiations: one sequence of launches each, in item order
+    for (int side = 0; side < 2; side++) {
+        std::vector<QmmArgs> part;
+        std::vector<int> idx;
+        for (int i = 0; i < n; i++)
+            if ((M[i] > 8) == (side == 1)) {
+                part.push_back(items[i]);
+                idx.push_back(i);
+            }
+        for (size_t lo = 0; lo < part.size(); lo += (size_t)qmv_batch_max()) {
+            const int cnt = (int)std::min(part.size() - lo, (size_t)qmv_batch_max());
+            const char* name = "";
+            cudaError_t e = launch_qmv_batch(part.data() + lo, cnt, c->dev->sm_count, c->stream, &name, &sp);
+            if (e == cudaErrorNotSupported) {  // K split over CTAs, ...: one push per item
+                cudaGetLastError();
+                for (int j = 0; j < cnt; j++) {
+                    LuxBackendError le = push_decode_at(sb, part[lo + j], y_offset[idx[lo + j]]);
+                    if (le != LUX_BACKEND_OK) return le;
+                }
+                continue;
+            }
+            if (e != cudaSuccess) return map_cuda_error(e, name);
+            c->last_kernel = name;
+            c->launches++;  // (not noted as a decode launch: the next decode kernel does not start under it)
+        }
+    }
+    for (int i = 0; i < n; i++)
+        as_buf(x[i])->last_stream = as_buf(wq[i])->last_stream = as_buf(scales[i])->last_stream = as_buf(biases[i])->last_stream = c->stream;
+    sb->view.last_stream = c->stream;
     return LUX_BACKEND_OK;
 }
 
@@ -283,6 +389,7 @@ void fill_symm_entries(lux_gpu_quant_vtbl* t) {
     t->symm_buffer = symm_buffer;
     t->symm_free = symm_free;
     t->qmatmul_sharded_push = qmatmul_sharded_push;
+    t->qmatmul_sharded_push_batch = qmatmul_sharded_push_batch;
 }
 
 }  // namespace luxcuda

@@ -141,6 +141,7 @@ class QuantVtbl(C.Structure):  # include/lux_cuda_quant.h: lux_gpu_quant_vtbl
         ("qmatmul_pro", _fn(_i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _sz, C.c_float)),
         # version >= 5
         ("qmatmul_batch", _fn(_i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i)),
+        ("qmatmul_sharded_push_batch", _fn(_i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i)),
     ]
 
 
@@ -482,8 +483,29 @@ class SymmBuffer:
             self.ctx.plugin.quant.qmatmul_sharded_push(self.handle, x.handle, wq.handle, scales.handle, biases.handle,
                                                        M, K, N_local, bits, group, y_dtype), "qmatmul_sharded_push")
 
+    def qmatmul_batch(self, xs, wqs, scales, biases, y_offsets, Ms, K, N_local, bits, group, y_dtype):
+        """n independent matmuls of one column-sharded shape; item i's y[M_i, world*N_local] lies at byte offset
+        y_offsets[i] of this buffer on every rank (qmatmul_sharded_push_batch)."""
+        n = len(xs)
+        assert all(len(a) == n for a in (wqs, scales, biases, y_offsets, Ms))
+        keep = [(C.c_void_p * n)(*[b.handle.value if isinstance(b.handle, C.c_void_p) else C.cast(b.handle, C.c_void_p).value for b in arr])
+                for arr in (xs, wqs, scales, biases)]
+        offs = (C.c_size_t * n)(*[int(o) for o in y_offsets])
+        ms = (C.c_int * n)(*[int(m) for m in Ms])
+        self.ctx.plugin.check(
+            self.ctx.plugin.quant.qmatmul_sharded_push_batch(self.handle, n, *[C.cast(a, C.c_void_p) for a in keep],
+                                                             C.cast(offs, C.c_void_p), C.cast(ms, C.c_void_p),
+                                                             K, N_local, bits, group, y_dtype), "qmatmul_sharded_push_batch")
+
     def to_host(self):
         return self.buffer.to_host(self.shape, self.dtype)
+
+    def item_to_host(self, offset, shape, dtype):
+        """The output at byte `offset` of the buffer as an array of `shape`."""
+        dtype = np.dtype(dtype)
+        flat = self.buffer.to_host((self.buffer.nbytes,), np.uint8)
+        n = int(np.prod(shape)) * dtype.itemsize
+        return flat[offset:offset + n].view(dtype).reshape(shape).copy()
 
     def free(self):
         if self.handle:

@@ -1,7 +1,7 @@
 """Helper of test_gpu_symm.py (not collected by pytest): run under torchrun with one rank per GPU.
 
 Every rank keeps a column slice of a few layers, runs the decode matmul that delivers its columns to all ranks
-(qmatmul_sharded_push), and rank 0 compares the gathered result with the unsharded matmul, bit for bit.  The
+(qmatmul_sharded_push, then several per call with qmatmul_sharded_push_batch), and rank 0 compares the gathered result with the unsharded matmul, bit for bit.  The
 shapes include few rows of W with a long K, where the decode kernel splits K over CTAs and the tiles are
 finished -- and sent to the peers -- by whichever CTA arrives last.
 """
@@ -26,6 +26,12 @@ SHAPES = [  # (M, K, N_local, bits, group)
     (16, 4096, 11008, 4, 64),
     (300, 2048, 384, 8, 32),   # prefill GEMM: tiles stored into every rank's copy from the epilogue
     (64, 1024, 144, 4, 64),
+]
+
+BATCHES = [  # (K, N_local, bits, group, [M of every item])
+    (4096, 1376, 4, 64, [1, 4, 8, 16, 3, 16, 8, 1, 12, 5]),
+    (11008, 512, 4, 64, [8, 2, 16]),   # split-K: single pushes at the items' offsets
+    (2048, 2752, 8, 128, [7, 9, 16, 1]),
 ]
 
 
@@ -68,10 +74,51 @@ def main():
         sb.free()
         for h in (bx, bw, bs, bb):
             h.free()
+    # Several matmuls per call (qmatmul_sharded_push_batch): the outputs one after another in one buffer, the call
+    # repeated into the same buffer; the second shape is one whose K the decode kernel splits over CTAs, which
+    # runs as single pushes at the items' offsets inside the call.
+    for case, (K, nl, bits, group, Ms) in enumerate(BATCHES):
+        N = nl * world
+        layers = [O.make_layer(N, K, bits, group, O.BF16, config_id=9, layer=10 * case + i) for i in range(len(Ms))]
+        xs = [O.make_x(M, K, O.BF16, config_id=9, tag=10 * case + i) for i, M in enumerate(Ms)]
+        sl = slice(rank * nl, (rank + 1) * nl)
+        up = [(ctx.upload(x), ctx.upload(l[0][sl]), ctx.upload(l[1][sl]), ctx.upload(l[2][sl])) for x, l in zip(xs, layers)]
+        offs, total = [], 0
+        for M in Ms:
+            offs.append(total)
+            total += M * N * 2
+        sb = SymmBuffer(ctx, rank, world, (total // 2,), np.uint16)
+        mine = torch.tensor(list(sb.export()), dtype=torch.uint8, device="cuda")
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        sb.attach([bytes(t.cpu().tolist()) for t in every])
+        dist.barrier()
+        for rep in range(10):
+            sb.qmatmul_batch([u[0] for u in up], [u[1] for u in up], [u[2] for u in up], [u[3] for u in up], offs, Ms,
+                             K, nl, bits, group, BF16)
+        ctx.sync()
+        got = [sb.item_to_host(offs[i], (M, N), np.uint16) for i, M in enumerate(Ms)]
+        dist.barrier()
+        if rank == 0:
+            for i, M in enumerate(Ms):
+                fw, fs, fb = ctx.upload(layers[i][0]), ctx.upload(layers[i][1]), ctx.upload(layers[i][2])
+                ref = ctx.empty((M, N), np.uint16)
+                ctx.qmatmul(up[i][0], fw, fs, fb, ref, M, K, N, bits, group, BF16, BF16, BF16)
+                if not np.array_equal(got[i], ref.to_host()):
+                    bad = np.argwhere(got[i] != ref.to_host())
+                    print(f"MISMATCH batch {case} item {i} (M={M}): {len(bad)} elements, first {bad[:4].tolist()}", flush=True)
+                    os._exit(3)
+                for h in (fw, fs, fb, ref):
+                    h.free()
+        dist.barrier()
+        sb.free()
+        for u in up:
+            for h in u:
+                h.free()
     ctx.sync()
     dist.barrier()
     if rank == 0:
-        print(f"SYMM_RANKS_OK world={world} cases={len(SHAPES)}", flush=True)
+        print(f"SYMM_RANKS_OK world={world} cases={len(SHAPES)} batches={len(BATCHES)}", flush=True)
     dist.destroy_process_group()
 
 
