@@ -2,7 +2,7 @@
 
 The plugin is compiled against the reference's UNCHANGED ABI header
 (include/lux/gpu/backend_plugin.h), taken where it lies in the reference tree
-(``LUX_REFERENCE_INCLUDE``, else the default location below); the header is not
+(``LUX_REFERENCE_INCLUDE``, else a directory ``reference`` beside this repository); the header is not
 copied into this repository.  On a machine without the reference tree the
 prebuilt library is used as is.
 """
@@ -25,7 +25,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 
 
 def reference_include():
-    for cand in (os.environ.get("LUX_REFERENCE_INCLUDE"), "/root/reference/include"):
+    for cand in (os.environ.get("LUX_REFERENCE_INCLUDE"), os.path.join(os.path.dirname(os.path.realpath(ROOT)), "reference", "include")):
         if cand and os.path.exists(os.path.join(cand, "lux", "gpu", "backend_plugin.h")):
             return cand
     return None

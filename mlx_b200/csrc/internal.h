@@ -181,6 +181,10 @@ struct QmmArgs {
 // Column-sharded decode launch: where the finished output tiles go besides this rank's own copy of y.
 // world == 1 (the default) means "not sharded".
 constexpr int kMaxShardWorld = 8;
+// Grid-stride helper kernels cap their grids at a few CTAs per SM of a B200 (2 x 74 SMs); they are correct for any
+// count.  The matmul kernels size their grids from the device's own SM count.
+constexpr int kGridCapSMs = 148;
+
 struct ShardPush {
     int world = 1, me = 0;
     int ld = 0, col0 = 0;                   // row stride of the full y and this rank's first column (elements)
@@ -190,7 +194,7 @@ struct ShardPush {
 };
 
 // decode GEMV, bf16 activations: mma.sync m16n8k16 with in-register dequant
-bool qmv_mma_supported(const QmmArgs& a);
+bool qmv_mma_supported(const QmmArgs& a, int sm_count);
 size_t qmv_mma_workspace_bytes(const QmmArgs& a, int sm_count);
 // overlap_prev: launch as a programmatic dependent of the previous kernel in the stream (see Context);
 // x_stable: that previous kernel does not write x, which may then be read before the wait for it
@@ -210,7 +214,7 @@ int qmv_batch_max();
 cudaError_t launch_qmv_batch(const QmmArgs* items, int n, int sm_count, cudaStream_t stream, const char** name,
                              const ShardPush* push = nullptr);
 // prefill GEMM, bf16 activations: TMA + tcgen05 + TMEM
-bool qmm_tc_supported(const QmmArgs& a);
+bool qmm_tc_supported(const QmmArgs& a, int sm_count);
 size_t qmm_tc_workspace_bytes(int sm_count);  // scratch of a launch (flags at its head: zero between launches)
 cudaError_t launch_qmm_tc(const QmmArgs& a, void* workspace, int sm_count, cudaStream_t stream, const char** name,
                           const ShardPush* push = nullptr);

@@ -26,7 +26,7 @@ __global__ void binary_f32_kernel(const float* __restrict__ a, const float* __re
 cudaError_t launch_binary_f32(BinOp op, const float* a, const float* b, float* out, size_t n, cudaStream_t stream) {
     const int threads = 256;
     size_t blocks = (n + threads - 1) / threads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > kGridCapSMs * 16) blocks = kGridCapSMs * 16;
     switch (op) {
         case BinOp::Add: binary_f32_kernel<0><<<(unsigned)blocks, threads, 0, stream>>>(a, b, out, n); break;
         case BinOp::Sub: binary_f32_kernel<1><<<(unsigned)blocks, threads, 0, stream>>>(a, b, out, n); break;
@@ -175,7 +175,7 @@ __global__ void flush_kernel(uint4* p, size_t n, unsigned v) {
 }
 cudaError_t launch_flush(void* buf, size_t bytes, cudaStream_t stream) {
     static unsigned ctr = 0;
-    flush_kernel<<<148 * 8, 256, 0, stream>>>((uint4*)buf, bytes / 16, ++ctr);
+    flush_kernel<<<kGridCapSMs * 8, 256, 0, stream>>>((uint4*)buf, bytes / 16, ++ctr);
     return cudaGetLastError();
 }
 
@@ -201,7 +201,7 @@ cudaError_t launch_gather_columns(const void* staging, void* y_full, int world, 
     // widen to 16-byte elements when the slice width allows it
     const int per16 = 16 / elem_size;
     unsigned blocks;
-    auto nblocks = [](size_t n) { size_t b = (n + 255) / 256; return (unsigned)(b > 148 * 8 ? 148 * 8 : b); };
+    auto nblocks = [](size_t n) { size_t b = (n + 255) / 256; return (unsigned)(b > kGridCapSMs * 8 ? kGridCapSMs * 8 : b); };
     if (n_local % per16 == 0 && ((uintptr_t)staging % 16) == 0 && ((uintptr_t)y_full % 16) == 0) {
         blocks = nblocks(total / per16);
         gather_columns_kernel<uint4><<<blocks, 256, 0, stream>>>((const uint4*)staging, (uint4*)y_full, world, M, n_local / per16);

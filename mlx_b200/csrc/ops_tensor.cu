@@ -121,7 +121,7 @@ __global__ void layer_norm_f32_kernel(const float* __restrict__ in, float* __res
 cudaError_t launch_unary_f32(int op, const float* in, float* out, size_t n, cudaStream_t stream) {
     if (!n) return cudaSuccess;
     size_t blocks = (n + kThreads - 1) / kThreads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > kGridCapSMs * 16) blocks = kGridCapSMs * 16;
     unary_f32_kernel<<<(unsigned)blocks, kThreads, 0, stream>>>(in, out, n, op);
     return cudaGetLastError();
 }

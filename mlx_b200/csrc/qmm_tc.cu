@@ -1500,9 +1500,9 @@ cudaError_t launch_gemm_t(const CUtensorMap& tmap, const CUtensorMap& tmap_w, co
 
 }  // namespace
 
-bool qmm_tc_supported(const QmmArgs& a) {
+bool qmm_tc_supported(const QmmArgs& a, int sm_count) {
     GemmPlan pl;
-    return make_gemm_plan(a, 148, &pl);
+    return make_gemm_plan(a, sm_count, &pl);
 }
 
 // Scratch of a launch: one partial accumulator and one flag word per CTA (see SegIter).  The flags must be zero

@@ -1142,9 +1142,9 @@ long long peer_wait_limit_ns() {
     return ns;
 }
 
-bool qmv_mma_supported(const QmmArgs& a) {
+bool qmv_mma_supported(const QmmArgs& a, int sm_count) {
     Plan pl;
-    return make_plan(a, 148, &pl);
+    return make_plan(a, sm_count, &pl);
 }
 
 // Scratch memory (global memory beyond inputs and outputs): arrival counters

@@ -121,7 +121,7 @@ LuxBackendError qmatmul_on_stream(Context* c, const QmmArgs& a) {
     cudaError_t e = cudaSuccess;
     int launches = 1;
     if (a.x_dtype == LUX_DTYPE_BFLOAT16) {
-        if (a.M > 16 && qmm_tc_supported(a)) {
+        if (a.M > 16 && qmm_tc_supported(a, c->dev->sm_count)) {
             LuxBackendError le = ensure_qmm_workspace(c);
             if (le != LUX_BACKEND_OK) return le;
             e = launch_qmm_tc(a, c->qmm_ws->ptr, c->dev->sm_count, c->stream, &name);
@@ -129,7 +129,7 @@ LuxBackendError qmatmul_on_stream(Context* c, const QmmArgs& a) {
             // decode kernel, 16 rows of x per launch
             QmmArgs chunk = a;
             chunk.M = a.M < 16 ? a.M : 16;
-            if (qmv_mma_supported(chunk)) {
+            if (qmv_mma_supported(chunk, c->dev->sm_count)) {
                 const size_t ws = qmv_mma_workspace_bytes(chunk, c->dev->sm_count);
                 LuxBackendError le = ensure_qmv_workspace(c, ws);
                 if (le != LUX_BACKEND_OK) return le;
@@ -341,7 +341,7 @@ LuxBackendError qmatmul_pro(LuxBackendContext* ctx, LuxBackendBuffer* x, LuxBack
     a.error = c->err_dev;
     a.x_ld = (int)x_ld;
     a.eps = eps;
-    if (M > 8 || !qmv_mma_supported(a)) {
+    if (M > 8 || !qmv_mma_supported(a, c->dev->sm_count)) {
         set_last_error("qmatmul_pro: shape not taken by the decode kernel with a prologue (M <= 8, K as qmatmul's decode path)");
         return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     }

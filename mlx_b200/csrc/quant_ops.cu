@@ -37,7 +37,7 @@ cudaError_t launch_unpack(const uint32_t* wq, uint8_t* q, int N, int K, int bits
     size_t words = (size_t)N * (K * bits / 32);
     if (!words) return cudaSuccess;
     size_t blocks = (words + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > kGridCapSMs * 16) blocks = kGridCapSMs * 16;
     unpack_kernel<<<(unsigned)blocks, 256, 0, stream>>>(wq, q, words, bits);
     return cudaGetLastError();
 }
@@ -94,7 +94,7 @@ cudaError_t launch_dequantize(const uint32_t* wq, const void* scales, const void
     size_t words = (size_t)N * (K * bits / 32);
     if (!words) return cudaSuccess;
     size_t blocks = (words + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > kGridCapSMs * 16) blocks = kGridCapSMs * 16;
     if (out_dtype == LUX_DTYPE_BFLOAT16)
         dequantize_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(wq, scales, biases, out, N, K, bits, group, sb_dtype);
     else

@@ -184,7 +184,7 @@ void symm_free(LuxCudaSymmBuffer* sb) {
 // twice its offset in the inbox area, so outputs that do not overlap have inboxes that do not overlap.
 LuxBackendError push_decode_at(LuxCudaSymmBuffer* sb, const QmmArgs& a, size_t yoff) {
     Context* c = sb->ctx;
-    if (!qmv_mma_supported(a)) {
+    if (!qmv_mma_supported(a, c->dev->sm_count)) {
         set_last_error("qmatmul_sharded_push: shape not taken by the decode kernel (K must be a multiple of %d)", 1024 / a.bits);
         return LUX_BACKEND_ERROR_NOT_SUPPORTED;
     }
@@ -246,7 +246,7 @@ LuxBackendError qmatmul_sharded_push(LuxCudaSymmBuffer* sb, LuxBackendBuffer* x,
         // Prefill: the tcgen05 GEMM stores every tile into all ranks' copies of y from its epilogue, so the
         // transfer runs under the remaining tiles.  A device-side barrier over the ranks before it (every rank
         // is done reading its y of the previous call) and one after it (every rank's tiles have landed).
-        if (!qmm_tc_supported(a)) {
+        if (!qmm_tc_supported(a, c->dev->sm_count)) {
             set_last_error("qmatmul_sharded_push: shape not taken by the prefill kernel (K must be a multiple of 64)");
             return LUX_BACKEND_ERROR_NOT_SUPPORTED;
         }

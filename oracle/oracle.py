@@ -31,7 +31,7 @@ def build(force=False):
     """Compile the oracle (and the reference core when its tree is present)."""
     src = os.path.join(_HERE, "qmm_oracle.c")
     stale = (not os.path.exists(_LIB_PATH)) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
-    if force or stale or (os.path.isdir("/root/reference") and not os.path.exists(os.path.join(_HERE, "_ref", "test_gpu_core"))):
+    if force or stale or (os.path.isdir(os.environ.get("REF", os.path.join(os.path.dirname(os.path.dirname(os.path.realpath(_HERE))), "reference"))) and not os.path.exists(os.path.join(_HERE, "_ref", "test_gpu_core"))):
         subprocess.run(["make", "-C", _HERE, "all"], check=True, stdout=subprocess.DEVNULL)
     return _LIB_PATH
 

@@ -17,7 +17,7 @@
  *     kernels/cpu/tensor_ops.c:546-566;
  *   - dtype enum values (FLOAT32 = 0, BFLOAT16 = 2, UINT32 = 5) --
  *     include/lux/gpu/backend_plugin.h:38-47.
- *   tests/test_oracle_vs_reference.py checks that orc_qmatmul_ref() on a
+ *   tests/test_oracle.py checks that orc_qmatmul_ref() on a
  *   layer equals, bit for bit, the reference's own cpu_op_matmul_f32 applied
  *   to the dequantised dense weights.
  *
