@@ -122,13 +122,37 @@ struct Context {
     std::mutex mu;  // one thread at a time per context
 };
 
+// The stream a buffer was last used on.  Every entry point assigns it for each buffer it reads or writes (the
+// allocator orders the reuse of a freed block behind it), so the number of assignments doubles as a change
+// counter: as long as it stands still, nothing has been enqueued that could have written the buffer.
+struct LastStream {
+    cudaStream_t stream = nullptr;
+    uint64_t uses = 0;
+    LastStream& operator=(cudaStream_t s) {
+        stream = s;
+        ++uses;
+        return *this;
+    }
+    LastStream& operator=(const LastStream& o) {
+        stream = o.stream;
+        ++uses;
+        return *this;
+    }
+    operator cudaStream_t() const { return stream; }
+};
+
 struct Buffer {
     uint32_t magic = kBufMagic;
     std::shared_ptr<DeviceState> dev;
     Block* block = nullptr;  // null for wrapped (non-owning) buffers
     void* ptr = nullptr;
     size_t bytes = 0;
-    cudaStream_t last_stream = nullptr;
+    LastStream last_stream;
+    // kernel_dispatch's parameter block as last read back from this buffer, valid while last_stream.uses stands
+    // at params_uses (the dispatch itself does not count as a use of the parameter buffer)
+    unsigned char params_copy[64] = {};
+    uint64_t params_uses = ~0ull;
+    bool exposed = false;  // the host holds the raw device pointer: it may write the buffer behind the plugin's back
 };
 
 struct Kernel {

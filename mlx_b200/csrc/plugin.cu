@@ -265,13 +265,19 @@ LuxBackendError kernel_dispatch(LuxBackendContext* ctx, LuxBackendKernel* kernel
     }
     Buffer* pb = as_buf(buffers[5]);
     if (!pb || pb->bytes < sizeof(lux_qmm_params)) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    // The dispatch ABI carries no scalars, so the shape travels in a device buffer and has to be read back:
+    // once per content -- while nothing has touched the buffer since (LastStream), the copy kept with it is used
+    // and the dispatch enqueues without waiting for the stream.
+    static_assert(sizeof(lux_qmm_params) <= sizeof(pb->params_copy), "parameter block larger than its host copy");
     lux_qmm_params p;
-    {
+    if (pb->params_uses != pb->last_stream.uses || pb->exposed || !pb->block) {  // (wrapped memory is the host's)
         DeviceGuard g(c->dev->device());
         c->copies++;
-        LUX_CUDA_TRY(cudaMemcpyAsync(&p, pb->ptr, sizeof(p), cudaMemcpyDeviceToHost, c->stream));
+        LUX_CUDA_TRY(cudaMemcpyAsync(pb->params_copy, pb->ptr, sizeof(p), cudaMemcpyDeviceToHost, c->stream));
         LUX_CUDA_TRY(cudaStreamSynchronize(c->stream));
+        pb->params_uses = pb->last_stream.uses;
     }
+    memcpy(&p, pb->params_copy, sizeof(p));
     return quant_vtbl()->qmatmul(ctx, buffers[0], buffers[1], buffers[2], buffers[3], buffers[4], p.M, p.K, p.N,
                                  p.bits, p.group, (LuxBackendDtype)p.x_dtype, (LuxBackendDtype)p.sb_dtype,
                                  (LuxBackendDtype)p.y_dtype);
@@ -492,6 +498,10 @@ const LuxEmbeddedKernel g_kernels[] = {
     {LUX_CUDA_QMM_KERNEL_NAME, "qmv_batch<4,m16>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {LUX_CUDA_QMM_KERNEL_NAME, "qmv_batch<8,m8>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {LUX_CUDA_QMM_KERNEL_NAME, "qmv_batch<8,m16>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_batch<4,m8,push>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},  // the same, column-sharded: tiles stored into every rank's y
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_batch<4,m16,push>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_batch<8,m8,push>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
+    {LUX_CUDA_QMM_KERNEL_NAME, "qmv_batch<8,m16,push>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<4>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},       // prefill GEMM (tcgen05), M > 16
     {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<8>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},
     {LUX_CUDA_QMM_KERNEL_NAME, "qmm_tc<4,stream-k>", LUX_KERNEL_LANG_CUDA, nullptr, 0, nullptr, 0},  // the same, k-stages split evenly over the SMs

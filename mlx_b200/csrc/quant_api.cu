@@ -435,6 +435,7 @@ LuxBackendError qmatmul_batch(LuxBackendContext* ctx, int n, LuxBackendBuffer* c
 // --- buffer interop ---------------------------------------------------------
 void* buffer_device_ptr(LuxBackendContext*, LuxBackendBuffer* buf) {
     Buffer* b = as_buf(buf);
+    if (b) b->exposed = true;
     return b ? b->ptr : nullptr;
 }
 size_t buffer_size(LuxBackendContext*, LuxBackendBuffer* buf) {

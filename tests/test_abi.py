@@ -180,7 +180,7 @@ def test_kernel_registry_hook():
     variants = {e for n, e, _ in entries if n == "lux.qmm.affine"}
     assert {"qmv_mma<4,m8>", "qmv_mma<4,m16>", "qmv_mma<8,m8>", "qmv_mma<8,m16>", "qmm_tc<4>", "qmm_tc<8>", "qmm_tc<4,stream-k>",
             "qmm_tc<8,stream-k>", "qmm_tc<4,pairs>", "qmm_tc<8,pairs>", "qmv_mma<4,m8,rms>", "qmv_mma<4,m8,sum3>", "qmv_batch<4,m8>", "qmv_batch<4,m16>", "qmv_batch<8,m8>",
-            "qmv_batch<8,m16>", "qmv_simt"} <= variants
+            "qmv_batch<8,m16>", "qmv_batch<4,m8,push>", "qmv_batch<4,m16,push>", "qmv_simt"} <= variants
     assert all(lang == 1 for _, _, lang in entries)  # LUX_KERNEL_LANG_CUDA
 
 

@@ -313,3 +313,39 @@ def test_batch_of_many_items_and_fp32_output(ctx, oracle):
         assert np.array_equal(ys[i].to_host(), ref.to_host((Ms[i], N), np.float32)), i
     for h in xs + ys + [bw, bs, bb, ref]:
         h.free()
+
+
+def test_dispatch_rereads_its_parameter_buffer_only_when_it_changed(ctx, plugin, oracle):
+    """kernel_dispatch takes the shape from a device buffer (the dispatch ABI has no scalars).  The same parameter
+    buffer dispatched again is not read back again, and a buffer rewritten in between is: the second shape must
+    be the one that runs."""
+    import ctypes as C
+    from mlx_b200 import plugin as P
+    K, N, bits, group = 1024, 256, 4, 64
+    wq, s, b = oracle.make_layer(N, K, bits, group, oracle.BF16, config_id=7, layer=1)
+    x = oracle.make_x(8, K, oracle.BF16, config_id=7, tag=1)
+    bx, bw, bs, bb = ctx.upload(x), ctx.upload(wq), ctx.upload(s), ctx.upload(b)
+    y = ctx.empty((8, N), np.uint16)
+    v = plugin.vtbl
+    k = v.kernel_load(ctx.handle, None, P.QMM_KERNEL_NAME)
+    assert k
+    prm = P.QmmParams(8, K, N, bits, group, BF16, BF16, BF16)
+    pb = v.buffer_alloc_with_data(ctx.handle, C.addressof(prm), C.sizeof(prm))
+    bufs = (C.c_void_p * 6)(bx.handle, bw.handle, bs.handle, bb.handle, y.handle, pb)
+    want8 = ctx.empty((8, N), np.uint16)
+    ctx.qmatmul(bx, bw, bs, bb, want8, 8, K, N, bits, group, BF16, BF16, BF16)
+    for _ in range(3):
+        plugin.check(v.kernel_dispatch(ctx.handle, k, 0, 0, 0, 0, 0, 0, bufs, 6), "kernel_dispatch")
+    assert np.array_equal(y.to_host(), want8.to_host())
+    # rewrite the parameters in place: 3 rows of x now; rows 3..7 of y must stay as they are
+    prm3 = P.QmmParams(3, K, N, bits, group, BF16, BF16, BF16)
+    plugin.check(v.buffer_copy_from_host(ctx.handle, pb, C.addressof(prm3), C.sizeof(prm3)), "copy_from_host")
+    marker = np.full((8, N), 0x7FC0, np.uint16)
+    y.from_host(marker)
+    plugin.check(v.kernel_dispatch(ctx.handle, k, 0, 0, 0, 0, 0, 0, bufs, 6), "kernel_dispatch")
+    got = y.to_host()
+    assert np.array_equal(got[:3], want8.to_host()[:3]) and np.array_equal(got[3:], marker[3:])
+    v.buffer_free(ctx.handle, pb)
+    v.kernel_destroy(ctx.handle, k)
+    for h in (bx, bw, bs, bb, y, want8):
+        h.free()
