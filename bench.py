@@ -923,6 +923,62 @@ def run_ours(args, rank, world):
         e2e_native = (drv, calls, len(order), fn(q.buffer_copy_from_host_async), fn(q.qmatmul), fn(q.qmatmul_sharded_push),
                       fn(plugin.vtbl.buffer_copy_to_host))
 
+    # The batched sweep end to end: every item's activations in one device buffer and one pinned host buffer (the
+    # items' x are views into it), every item's output in one device buffer (several GPUs: the symmetric buffer), so
+    # that a sweep is one host->device copy, one batched call and one blocking device->host copy of all outputs.
+    e2e_batch = None
+    if use_batch and e2e_native is not None:
+        class Batch(C.Structure):
+            _fields_ = [("x_all_dev", C.c_void_p), ("x_all_host", C.c_void_p), ("x_bytes", C.c_size_t),
+                        ("y_all_dev", C.c_void_p), ("y_all_host", C.c_void_p), ("y_bytes", C.c_size_t), ("n", C.c_int32),
+                        ("x", C.c_void_p), ("wq", C.c_void_p), ("scales", C.c_void_p), ("biases", C.c_void_p), ("y", C.c_void_p),
+                        ("y_offset", C.c_void_p), ("M", C.c_void_p), ("y_symm", C.c_void_p),
+                        ("K", C.c_int32), ("N", C.c_int32), ("bits", C.c_int32), ("group", C.c_int32), ("dtype", C.c_int32)]
+        nb = len(b_items)
+        x_off, y_off, xo, yo = [], [], 0, 0
+        for M, r in b_items:
+            x_off.append(xo)
+            y_off.append(yo)
+            xo += M * K_DEC * 2
+            yo += M * n_total * 2
+        x_all = ctx.empty((xo // 2,), np.uint16)
+        x_all_pin = ctx.pinned_array((xo // 2,), np.uint16)
+        for (M, r), o in zip(b_items, x_off):
+            x_all_pin[o // 2:o // 2 + M * K_DEC] = x_host[M].reshape(-1)
+        y_all_pin = ctx.pinned_array((yo // 2,), np.uint16)
+        x_base = x_all.device_ptr
+        x_views = [ctx.wrap(x_base + o, M * K_DEC * 2) for (M, r), o in zip(b_items, x_off)]
+        if world == 1:
+            y_all = ctx.empty((yo // 2,), np.uint16)
+            y_base = y_all.device_ptr
+            y_views = [ctx.wrap(y_base + o, M * n_total * 2) for (M, r), o in zip(b_items, y_off)]
+            y_all_handle, y_symm_handle = _h(y_all), None
+        else:
+            assert [b_off[it] for it in b_items] == y_off
+            y_all, y_views = None, []
+            y_all_handle, y_symm_handle = _h(symm_all.buffer), _h(symm_all)
+        arr = lambda hs: (C.c_void_p * nb)(*hs)
+        keep = {"x": arr([_h(v) for v in x_views]), "wq": arr([_h(layers[r][0]) for M, r in b_items]),
+                "scales": arr([_h(layers[r][1]) for M, r in b_items]), "biases": arr([_h(layers[r][2]) for M, r in b_items]),
+                "y": arr([_h(v) for v in y_views]) if y_views else None, "y_offset": (C.c_size_t * nb)(*y_off),
+                "M": (C.c_int * nb)(*[M for M, r in b_items])}
+        adr = lambda a: C.cast(a, C.c_void_p).value if a is not None else None
+        bt = Batch(_h(x_all), x_all_pin.ctypes.data, xo, y_all_handle, y_all_pin.ctypes.data, yo, nb, adr(keep["x"]), adr(keep["wq"]),
+                   adr(keep["scales"]), adr(keep["biases"]), adr(keep["y"]), adr(keep["y_offset"]), adr(keep["M"]), y_symm_handle,
+                   K_DEC, N_DEC, BITS, GROUP, BF16)
+        drv.lux_bench_e2e_batch.restype = C.c_int
+        drv.lux_bench_e2e_batch.argtypes = [C.c_void_p] * 5 + [C.POINTER(Batch), C.c_int, C.POINTER(C.c_longlong)]
+        e2e_batch = (bt, keep, x_views, y_views, x_all, y_all, x_all_pin, y_all_pin, fn(q.qmatmul_batch), fn(q.qmatmul_sharded_push_batch))
+
+    def e2e_batch_step():
+        nonlocal e2e_calls
+        bt = e2e_batch[0]
+        done = C.c_longlong(0)
+        rc = drv.lux_bench_e2e_batch(e2e_native[3], e2e_batch[8], e2e_batch[9], e2e_native[6], ctx.handle, C.byref(bt), e2e_reps,
+                                     C.byref(done))
+        plugin.check(rc, "e2e batch loop")
+        e2e_calls += done.value
+
     def e2e_step():
         nonlocal e2e_calls
         if e2e_native is not None:
@@ -945,6 +1001,25 @@ def run_ours(args, rank, world):
     e2e_calls = 0
     ms_e2e = timed(lambda: [e2e_step() for _ in range(e2e_steps)], 4, 5) if e2e_steps else float("nan")
     e2e_value = sweep_bytes * e2e_reps * e2e_steps / ms_e2e / 1e6
+    e2e_single = None
+    if e2e_batch is not None and e2e_steps:
+        # the headline's own route end to end: keep the per-call figures beside it, then check what came back
+        e2e_single = {"value": e2e_value, "unit": "GB/s", "calls": e2e_calls, "us_per_call": ms_e2e * 1e3 / max(1, e2e_calls),
+                      "how": "one copy in, one qmatmul" + ("_sharded_push" if world > 1 else "") + ", one blocking copy out per matmul"}
+        e2e_batch_step()
+        y_back = e2e_batch[7]
+        bad = []
+        for it in ((1, 0), (8, R_SETS - 1), (16, R_SETS // 2)):
+            i = b_items.index(it)
+            o, cnt = e2e_batch[1]["y_offset"][i] // 2, it[0] * n_total
+            if not np.array_equal(np.asarray(y_back[o:o + cnt]).reshape(it[0], n_total), item_host(it)):
+                bad.append(it)
+        e2e_checked = f"FAILED: outputs {bad} read back differ" if bad else "three outputs as read back to the host bit-identical to the batched sweep's"
+        if bad:
+            print(e2e_checked, file=sys.stderr, flush=True)
+        e2e_calls = 0
+        ms_e2e = timed(lambda: [e2e_batch_step() for _ in range(e2e_steps)], 4, 5)
+        e2e_value = sweep_bytes * e2e_reps * e2e_steps / ms_e2e / 1e6
     h2d = sum(M * K_DEC * 2 for M in M_SWEEP) * R_SETS * e2e_reps
     d2h = sum(M * n_total * 2 for M in M_SWEEP) * R_SETS * e2e_reps
 
@@ -1021,10 +1096,15 @@ def run_ours(args, rank, world):
         "gemm_sharded": gemm_sharded,
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "calls": e2e_calls, "us_per_call": ms_e2e * 1e3 / max(1, e2e_calls),
+                **({"matmuls": e2e_calls, "us_per_matmul": ms_e2e * 1e3 / max(1, e2e_calls)} if e2e_single else
+                   {"calls": e2e_calls, "us_per_call": ms_e2e * 1e3 / max(1, e2e_calls)}),
                 "driver": "python" if e2e_native is None else "C host loop (bench_e2e.c) over the plugin's entry points",
-                "note": "per call, pinned host buffers: buffer_copy_from_host_async(x) + qmatmul + buffer_copy_to_host(y, blocking); weights stay resident "
-                        "like the core's tensors (src/gpu_core.cpp:47-76)"},
+                "note": ("per sweep of 48 independent matmuls, pinned host buffers: ONE buffer_copy_from_host_async of every item's x, ONE "
+                         + ("qmatmul_batch" if world == 1 else "qmatmul_sharded_push_batch") + " call, ONE blocking buffer_copy_to_host of "
+                         "every item's y; weights stay resident like the core's tensors (src/gpu_core.cpp:47-76)") if e2e_single else
+                        "per call, pinned host buffers: buffer_copy_from_host_async(x) + qmatmul + buffer_copy_to_host(y, blocking); weights stay resident "
+                        "like the core's tensors (src/gpu_core.cpp:47-76)",
+                **({"checked": e2e_checked, "single_calls": e2e_single} if e2e_single else {})},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }

@@ -47,3 +47,52 @@ int lux_bench_e2e(copy_in_fn copy_in, qmatmul_fn qmatmul, push_fn push, copy_out
     if (calls_done) *calls_done = done;
     return 0;
 }
+
+/* The same for a whole sweep of independent matmuls handed to the plugin as ONE call (qmatmul_batch |
+ * qmatmul_sharded_push_batch): the activations of all items lie one after another in one device buffer and
+ * one page-locked host buffer (the items' x are views into it), and so do the outputs, so that a sweep is
+ *   one host->device copy of every item's activations,
+ *   one batched call,
+ *   one blocking device->host copy of every item's output. */
+typedef int (*batch_fn)(void* ctx, int n, void* const* x, void* const* wq, void* const* scales, void* const* biases,
+                        void* const* y, const int* M, int K, int N, int bits, int group, int y_dtype);
+typedef int (*push_batch_fn)(void* y_symm, int n, void* const* x, void* const* wq, void* const* scales, void* const* biases,
+                             const size_t* y_offset, const int* M, int K, int N_local, int bits, int group, int y_dtype);
+
+typedef struct {
+    void* x_all_dev;
+    const void* x_all_host;
+    size_t x_bytes;
+    void* y_all_dev; /* for a sharded call: the symmetric buffer seen as a buffer */
+    void* y_all_host;
+    size_t y_bytes;
+    int32_t n;
+    void* const* x;
+    void* const* wq;
+    void* const* scales;
+    void* const* biases;
+    void* const* y;         /* unsharded: the items' outputs, views into y_all_dev */
+    const size_t* y_offset; /* sharded: the items' byte offsets inside the symmetric buffer */
+    const int* M;
+    void* y_symm; /* sharded: the symmetric buffer handle; else NULL */
+    int32_t K, N, bits, group, dtype;
+} lux_bench_batch;
+
+__attribute__((visibility("default")))
+int lux_bench_e2e_batch(copy_in_fn copy_in, batch_fn batch, push_batch_fn push_batch, copy_out_fn copy_out, void* ctx,
+                        const lux_bench_batch* b, int reps, long long* matmuls_done) {
+    long long done = 0;
+    for (int r = 0; r < reps; r++) {
+        int rc = copy_in(ctx, b->x_all_dev, b->x_all_host, b->x_bytes);
+        if (rc) return rc;
+        rc = b->y_symm ? push_batch(b->y_symm, b->n, b->x, b->wq, b->scales, b->biases, b->y_offset, b->M, b->K, b->N, b->bits,
+                                    b->group, b->dtype)
+                       : batch(ctx, b->n, b->x, b->wq, b->scales, b->biases, b->y, b->M, b->K, b->N, b->bits, b->group, b->dtype);
+        if (rc) return rc;
+        rc = copy_out(ctx, b->y_all_dev, b->y_all_host, b->y_bytes);
+        if (rc) return rc;
+        done += b->n;
+    }
+    if (matmuls_done) *matmuls_done = done;
+    return 0;
+}
