@@ -926,7 +926,7 @@ def run_ours(args, rank, world):
     # The batched sweep end to end: every item's activations in one device buffer and one pinned host buffer (the
     # items' x are views into it), every item's output in one device buffer (several GPUs: the symmetric buffer), so
     # that a sweep is one host->device copy, one batched call and one blocking device->host copy of all outputs.
-    e2e_batch = None
+    e2e_batch = e2e_two = None
     if use_batch and e2e_native is not None:
         class Batch(C.Structure):
             _fields_ = [("x_all_dev", C.c_void_p), ("x_all_host", C.c_void_p), ("x_bytes", C.c_size_t),
@@ -969,11 +969,33 @@ def run_ours(args, rank, world):
         drv.lux_bench_e2e_batch.restype = C.c_int
         drv.lux_bench_e2e_batch.argtypes = [C.c_void_p] * 5 + [C.POINTER(Batch), C.c_int, C.POINTER(C.c_longlong)]
         e2e_batch = (bt, keep, x_views, y_views, x_all, y_all, x_all_pin, y_all_pin, fn(q.qmatmul_batch), fn(q.qmatmul_sharded_push_batch))
+        if world == 1 and not args.e2e_one_context:
+            # a second context (stream) with its own activations and outputs: sweep r computes while sweep r-1 is read back
+            ctx2 = plugin.context(local_rank)
+            x_all2, y_all2 = ctx2.empty((xo // 2,), np.uint16), ctx2.empty((yo // 2,), np.uint16)
+            y_all_pin2 = ctx2.pinned_array((yo // 2,), np.uint16)
+            x_views2 = [ctx2.wrap(x_all2.device_ptr + o, M * K_DEC * 2) for (M, r), o in zip(b_items, x_off)]
+            y_views2 = [ctx2.wrap(y_all2.device_ptr + o, M * n_total * 2) for (M, r), o in zip(b_items, y_off)]
+            keep2 = {"x": arr([_h(v) for v in x_views2]), "y": arr([_h(v) for v in y_views2])}
+            bt2 = Batch(_h(x_all2), x_all_pin.ctypes.data, xo, _h(y_all2), y_all_pin2.ctypes.data, yo, nb, adr(keep2["x"]), adr(keep["wq"]),
+                        adr(keep["scales"]), adr(keep["biases"]), adr(keep2["y"]), adr(keep["y_offset"]), adr(keep["M"]), None,
+                        K_DEC, N_DEC, BITS, GROUP, BF16)
+            drv.lux_bench_e2e_batch2.restype = C.c_int
+            drv.lux_bench_e2e_batch2.argtypes = [C.c_void_p] * 3 + [C.POINTER(C.c_void_p), C.POINTER(C.POINTER(Batch)), C.c_int,
+                                                                    C.POINTER(C.c_longlong)]
+            e2e_two = (ctx2, bt2, keep2, x_views2, y_views2, x_all2, y_all2, y_all_pin2, (C.c_void_p * 2)(_h(ctx), _h(ctx2)),
+                       (C.POINTER(Batch) * 2)(C.pointer(bt), C.pointer(bt2)))
 
-    def e2e_batch_step():
+    def e2e_batch_step(two=True):
         nonlocal e2e_calls
         bt = e2e_batch[0]
         done = C.c_longlong(0)
+        if two and e2e_two is not None:
+            rc = drv.lux_bench_e2e_batch2(e2e_native[3], e2e_batch[8], e2e_native[6], e2e_two[8], e2e_two[9], e2e_reps, C.byref(done))
+            plugin.check(rc, "e2e batch loop (two contexts)")
+            e2e_two[0].sync()
+            e2e_calls += done.value
+            return
         rc = drv.lux_bench_e2e_batch(e2e_native[3], e2e_batch[8], e2e_batch[9], e2e_native[6], ctx.handle, C.byref(bt), e2e_reps,
                                      C.byref(done))
         plugin.check(rc, "e2e batch loop")
@@ -1007,16 +1029,23 @@ def run_ours(args, rank, world):
         e2e_single = {"value": e2e_value, "unit": "GB/s", "calls": e2e_calls, "us_per_call": ms_e2e * 1e3 / max(1, e2e_calls),
                       "how": "one copy in, one qmatmul" + ("_sharded_push" if world > 1 else "") + ", one blocking copy out per matmul"}
         e2e_batch_step()
-        y_back = e2e_batch[7]
         bad = []
-        for it in ((1, 0), (8, R_SETS - 1), (16, R_SETS // 2)):
-            i = b_items.index(it)
-            o, cnt = e2e_batch[1]["y_offset"][i] // 2, it[0] * n_total
-            if not np.array_equal(np.asarray(y_back[o:o + cnt]).reshape(it[0], n_total), item_host(it)):
-                bad.append(it)
+        for y_back in [e2e_batch[7]] + ([e2e_two[7]] if e2e_two is not None else []):
+            for it in ((1, 0), (8, R_SETS - 1), (16, R_SETS // 2)):
+                i = b_items.index(it)
+                o, cnt = e2e_batch[1]["y_offset"][i] // 2, it[0] * n_total
+                if not np.array_equal(np.asarray(y_back[o:o + cnt]).reshape(it[0], n_total), item_host(it)):
+                    bad.append(it)
         e2e_checked = f"FAILED: outputs {bad} read back differ" if bad else "three outputs as read back to the host bit-identical to the batched sweep's"
         if bad:
             print(e2e_checked, file=sys.stderr, flush=True)
+        e2e_one = None
+        if e2e_two is not None:
+            e2e_batch_step(False)
+            e2e_calls = 0
+            ms_one = timed(lambda: [e2e_batch_step(False) for _ in range(e2e_steps)], 4, 5)
+            e2e_one = {"value": sweep_bytes * e2e_reps * e2e_steps / ms_one / 1e6, "unit": "GB/s", "us_per_matmul": ms_one * 1e3 / max(1, e2e_calls),
+                       "how": "the same with one context: copy in, batched call, blocking copy out, strictly one after the other"}
         e2e_calls = 0
         ms_e2e = timed(lambda: [e2e_batch_step() for _ in range(e2e_steps)], 4, 5)
         e2e_value = sweep_bytes * e2e_reps * e2e_steps / ms_e2e / 1e6
@@ -1101,10 +1130,12 @@ def run_ours(args, rank, world):
                 "driver": "python" if e2e_native is None else "C host loop (bench_e2e.c) over the plugin's entry points",
                 "note": ("per sweep of 48 independent matmuls, pinned host buffers: ONE buffer_copy_from_host_async of every item's x, ONE "
                          + ("qmatmul_batch" if world == 1 else "qmatmul_sharded_push_batch") + " call, ONE blocking buffer_copy_to_host of "
-                         "every item's y; weights stay resident like the core's tensors (src/gpu_core.cpp:47-76)") if e2e_single else
+                         "every item's y; weights stay resident like the core's tensors (src/gpu_core.cpp:47-76)"
+                         + ("; the host keeps two contexts (streams) and reads sweep r-1 back while sweep r computes" if e2e_two is not None else ""))
+                        if e2e_single else
                         "per call, pinned host buffers: buffer_copy_from_host_async(x) + qmatmul + buffer_copy_to_host(y, blocking); weights stay resident "
                         "like the core's tensors (src/gpu_core.cpp:47-76)",
-                **({"checked": e2e_checked, "single_calls": e2e_single} if e2e_single else {})},
+                **({"checked": e2e_checked, "one_context": e2e_one, "single_calls": e2e_single} if e2e_single else {})},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
@@ -1123,6 +1154,8 @@ def main():
                     help="skip the e2e and CPU-baseline legs (for short runs under a profiler)")
     ap.add_argument("--nccl-allgather", action="store_true",
                     help="N>1: gather the column slices with NCCL + an interleave pass instead of peer stores from the kernel")
+    ap.add_argument("--e2e-one-context", action="store_true",
+                    help="end-to-end leg: one context (copy in, batched call, blocking copy out, strictly one after the other)")
     ap.add_argument("--single-calls", action="store_true",
                     help="N=1: time the sweep as one call per matmul (the default hands each sweep to qmatmul_batch)")
     ap.add_argument("--e2e-python", action="store_true",

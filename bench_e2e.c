@@ -96,3 +96,30 @@ int lux_bench_e2e_batch(copy_in_fn copy_in, batch_fn batch, push_batch_fn push_b
     if (matmuls_done) *matmuls_done = done;
     return 0;
 }
+
+/* Two sweeps in flight: the host keeps two contexts (two streams), each with its own activations and outputs,
+ * and reads sweep r-1 back (blocking) while sweep r computes -- the copies of one context run under the kernels
+ * of the other.  One GPU only: the batched sharded kernels of two contexts would wait for their peers from two
+ * streams of one GPU.  Every sweep is still one copy in, one qmatmul_batch call, one blocking copy out. */
+__attribute__((visibility("default")))
+int lux_bench_e2e_batch2(copy_in_fn copy_in, batch_fn batch, copy_out_fn copy_out, void* const ctx[2],
+                         const lux_bench_batch* const b[2], int reps, long long* matmuls_done) {
+    long long done = 0;
+    for (int r = 0; r <= reps; r++) {
+        if (r < reps) {
+            const lux_bench_batch* c = b[r & 1];
+            int rc = copy_in(ctx[r & 1], c->x_all_dev, c->x_all_host, c->x_bytes);
+            if (rc) return rc;
+            rc = batch(ctx[r & 1], c->n, c->x, c->wq, c->scales, c->biases, c->y, c->M, c->K, c->N, c->bits, c->group, c->dtype);
+            if (rc) return rc;
+        }
+        if (r > 0) {
+            const lux_bench_batch* p = b[(r - 1) & 1];
+            int rc = copy_out(ctx[(r - 1) & 1], p->y_all_dev, p->y_all_host, p->y_bytes);
+            if (rc) return rc;
+            done += p->n;
+        }
+    }
+    if (matmuls_done) *matmuls_done = done;
+    return 0;
+}
