@@ -51,7 +51,7 @@ extern "C" {
 #define LUX_CUDA_QUANT_MAGIC 0x4C515854u /* "LQXT" */
 #define LUX_CUDA_PRO_RMS_NORM 1
 #define LUX_CUDA_PRO_SUM3 2
-#define LUX_CUDA_QUANT_VERSION 6u /* 2: symm_* and qmatmul_sharded_push appended; 3: sum3, mul_rms_norm; 4: qmatmul_pro; 5: qmatmul_batch; 6: qmatmul_sharded_push_batch */
+#define LUX_CUDA_QUANT_VERSION 7u /* 2: symm_* and qmatmul_sharded_push appended; 3: sum3, mul_rms_norm; 4: qmatmul_pro; 5: qmatmul_batch; 6: qmatmul_sharded_push_batch; 7: qmatmul_sharded_push_pro */
 #define LUX_CUDA_QMM_KERNEL_NAME "lux.qmm.affine"
 #define LUX_CUDA_NCCL_UID_BYTES 128
 
@@ -254,6 +254,18 @@ typedef struct lux_gpu_quant_vtbl {
                                                   LuxBackendBuffer* const* wq_local, LuxBackendBuffer* const* scales_local,
                                                   LuxBackendBuffer* const* biases_local, const size_t* y_offset, const int* M,
                                                   int K, int N_local, int bits, int group, LuxBackendDtype y_dtype);
+
+    /* --- qmatmul_pro for a column-sharded layer (version >= 7) ---
+     * qmatmul_sharded_push with one of qmatmul_pro's prologues applied to x as the kernel loads it: x is the whole
+     * (gathered) activation buffer [M][x_ld] on this rank, e.g. the symmetric buffer of the previous projection;
+     * M <= 8.  Same results as the step on every rank followed by qmatmul_sharded_push, in one launch per rank.
+     * NOT_SUPPORTED as for qmatmul_pro (M > 8, a K the decode kernel does not take or splits over CTAs on this
+     * rank's share of the columns, for RMS_NORM a K longer than 16 k-blocks): call the step and
+     * qmatmul_sharded_push instead -- the same decision on every rank, since it depends on the shape only. */
+    LuxBackendError (*qmatmul_sharded_push_pro)(LuxCudaSymmBuffer* y_full, LuxBackendBuffer* x, LuxBackendBuffer* wq_local,
+                                                LuxBackendBuffer* scales_local, LuxBackendBuffer* biases_local,
+                                                int M, int K, int N_local, int bits, int group, LuxBackendDtype y_dtype,
+                                                int prologue, size_t x_ld, float eps);
 } lux_gpu_quant_vtbl;
 
 /* Entry points exported with default visibility. */

@@ -206,6 +206,11 @@ LuxBackendError push_decode_at(LuxCudaSymmBuffer* sb, const QmmArgs& a, size_t y
     whole.N = sp.ld;
     const char* name = "";
     cudaError_t e = launch_qmv_mma(local, c->qmv_ws->ptr, c->dev->sm_count, c->stream, &name, decode_may_overlap(c, local), &sp);
+    if (e == cudaErrorNotSupported && a.pro) {
+        cudaGetLastError();
+        set_last_error("qmatmul_sharded_push_pro: the prologue needs M <= 8, no K split, and for the rms-norm K within 16 k-blocks of 128 packed bytes");
+        return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    }
     if (e != cudaSuccess) return map_cuda_error(e, name);
     c->last_kernel = name;
     c->launches++;
@@ -283,6 +288,45 @@ LuxBackendError qmatmul_sharded_push(LuxCudaSymmBuffer* sb, LuxBackendBuffer* x,
         bx->last_stream = bw->last_stream = bs->last_stream = bb->last_stream = sb->view.last_stream = c->stream;
         return LUX_BACKEND_OK;
     }
+    LuxBackendError le = push_decode_at(sb, a, 0);
+    if (le == LUX_BACKEND_OK) bx->last_stream = bw->last_stream = bs->last_stream = bb->last_stream = sb->view.last_stream = c->stream;
+    return le;
+}
+
+LuxBackendError qmatmul_sharded_push_pro(LuxCudaSymmBuffer* sb, LuxBackendBuffer* x, LuxBackendBuffer* wq, LuxBackendBuffer* scales,
+                                         LuxBackendBuffer* biases, int M, int K, int Nl, int bits, int group, LuxBackendDtype y_dtype,
+                                         int prologue, size_t x_ld, float eps) {
+    if (!sb) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    Context* c = sb->ctx;
+    Buffer *bx = as_buf(x), *bw = as_buf(wq), *bs = as_buf(scales), *bb = as_buf(biases);
+    if (!bx || !bw || !bs || !bb) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (y_dtype != LUX_DTYPE_BFLOAT16 && y_dtype != LUX_DTYPE_FLOAT32) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (prologue != LUX_CUDA_PRO_RMS_NORM && prologue != LUX_CUDA_PRO_SUM3) return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    if (!sb->attached) {
+        set_last_error("qmatmul_sharded_push_pro: symm_attach has not been called");
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    }
+    if (M < 1 || M > 8 || Nl < 1 || (Nl & 15) || K < 1 || (bits != 4 && bits != 8) ||
+        (group != 32 && group != 64 && group != 128) || K % group) {
+        set_last_error("qmatmul_sharded_push_pro: needs 1 <= M <= 8, N_local a multiple of 16, bits 4|8, group 32|64|128");
+        return LUX_BACKEND_ERROR_NOT_SUPPORTED;
+    }
+    const size_t ys = y_dtype == LUX_DTYPE_BFLOAT16 ? 2 : 4;
+    const size_t ld = (size_t)Nl * sb->world;
+    const size_t need_ld = prologue == LUX_CUDA_PRO_SUM3 ? (size_t)3 * K : (size_t)K;
+    if (x_ld < need_ld || (x_ld & 7) || ((size_t)(M - 1) * x_ld + need_ld) * 2 > bx->bytes || (size_t)Nl * K * bits / 8 > bw->bytes ||
+        (size_t)Nl * (K / group) * 2 > bs->bytes || (size_t)Nl * (K / group) * 2 > bb->bytes || (size_t)M * ld * ys > sb->bytes) {
+        set_last_error("qmatmul_sharded_push_pro: a buffer is smaller than its shape needs (x is [M][x_ld], x_ld a multiple of 8)");
+        return LUX_BACKEND_ERROR_INVALID_ARGUMENT;
+    }
+    QmmArgs a{bx->ptr, (const uint32_t*)bw->ptr, bs->ptr, bb->ptr, sb->view.ptr, M, K, Nl, bits, group,
+              LUX_DTYPE_BFLOAT16, LUX_DTYPE_BFLOAT16, (int)y_dtype};
+    a.pro = prologue;
+    a.x_ld = (int)x_ld;
+    a.eps = eps;
+    a.error = c->err_dev;
+    std::lock_guard<std::mutex> lk(c->mu);
+    DeviceGuard g(c->dev->device());
     LuxBackendError le = push_decode_at(sb, a, 0);
     if (le == LUX_BACKEND_OK) bx->last_stream = bw->last_stream = bs->last_stream = bb->last_stream = sb->view.last_stream = c->stream;
     return le;
@@ -390,6 +434,7 @@ void fill_symm_entries(lux_gpu_quant_vtbl* t) {
     t->symm_free = symm_free;
     t->qmatmul_sharded_push = qmatmul_sharded_push;
     t->qmatmul_sharded_push_batch = qmatmul_sharded_push_batch;
+    t->qmatmul_sharded_push_pro = qmatmul_sharded_push_pro;
 }
 
 }  // namespace luxcuda

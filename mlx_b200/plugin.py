@@ -142,6 +142,7 @@ class QuantVtbl(C.Structure):  # include/lux_cuda_quant.h: lux_gpu_quant_vtbl
         # version >= 5
         ("qmatmul_batch", _fn(_i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i)),
         ("qmatmul_sharded_push_batch", _fn(_i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i)),
+        ("qmatmul_sharded_push_pro", _fn(_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _sz, C.c_float)),
     ]
 
 
@@ -482,6 +483,13 @@ class SymmBuffer:
         self.ctx.plugin.check(
             self.ctx.plugin.quant.qmatmul_sharded_push(self.handle, x.handle, wq.handle, scales.handle, biases.handle,
                                                        M, K, N_local, bits, group, y_dtype), "qmatmul_sharded_push")
+
+    def qmatmul_pro(self, x, wq, scales, biases, M, K, N_local, bits, group, y_dtype, prologue, x_ld, eps=0.0):
+        """qmatmul with PRO_RMS_NORM | PRO_SUM3 applied to the (whole, gathered) x as the kernel loads it (M <= 8)."""
+        self.ctx.plugin.check(
+            self.ctx.plugin.quant.qmatmul_sharded_push_pro(self.handle, x.handle, wq.handle, scales.handle, biases.handle,
+                                                           M, K, N_local, bits, group, y_dtype, prologue, x_ld, eps),
+            "qmatmul_sharded_push_pro")
 
     def qmatmul_batch(self, xs, wqs, scales, biases, y_offsets, Ms, K, N_local, bits, group, y_dtype):
         """n independent matmuls of one column-sharded shape; item i's y[M_i, world*N_local] lies at byte offset

@@ -33,6 +33,12 @@ BATCHES = [  # (K, N_local, bits, group, [M of every item])
     (11008, 512, 4, 64, [8, 2, 16]),   # split-K: single pushes at the items' offsets
     (2048, 2752, 8, 128, [7, 9, 16, 1]),
 ]
+PROLOGUES = [  # (M, K, N_local, bits, group, prologue): 1 = rms-norm, 2 = sum of three column blocks
+    (8, 4096, 1536, 4, 64, 1),
+    (8, 4096, 512, 4, 64, 2),
+    (3, 2048, 2752, 8, 128, 1),
+    (5, 8192, 256, 4, 64, 2),   # sum3 with K split over CTAs
+]
 
 
 def main():
@@ -115,10 +121,46 @@ def main():
         for u in up:
             for h in u:
                 h.free()
+    # Prologues on a sharded layer (qmatmul_sharded_push_pro): x is a wider buffer (three column blocks for sum3);
+    # the gathered result must be the unsharded qmatmul_pro's, bit for bit (the row statistics of the rms-norm are
+    # computed by every CTA from the same fragments in the same order, whatever its share of the columns).
+    from mlx_b200.plugin import PRO_RMS_NORM, PRO_SUM3
+    for case, (M, K, nl, bits, group, which) in enumerate(PROLOGUES):
+        N = nl * world
+        x_ld = 3 * K if which == PRO_SUM3 else K + 64
+        wq, s, b = O.make_layer(N, K, bits, group, O.BF16, config_id=10, layer=case)
+        x = O.make_x(M, x_ld, O.BF16, config_id=10, tag=case)
+        sl = slice(rank * nl, (rank + 1) * nl)
+        bx, bw, bs, bb = ctx.upload(x), ctx.upload(wq[sl]), ctx.upload(s[sl]), ctx.upload(b[sl])
+        sb = SymmBuffer(ctx, rank, world, (M, N), np.uint16)
+        mine = torch.tensor(list(sb.export()), dtype=torch.uint8, device="cuda")
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        sb.attach([bytes(t.cpu().tolist()) for t in every])
+        dist.barrier()
+        for rep in range(5):
+            sb.qmatmul_pro(bx, bw, bs, bb, M, K, nl, bits, group, BF16, which, x_ld, 1e-6)
+        ctx.sync()
+        got = sb.to_host()
+        dist.barrier()
+        if rank == 0:
+            fw, fs, fb = ctx.upload(wq), ctx.upload(s), ctx.upload(b)
+            ref = ctx.empty((M, N), np.uint16)
+            ctx.qmatmul_pro(bx, fw, fs, fb, ref, M, K, N, bits, group, BF16, which, x_ld, 1e-6)
+            if not np.array_equal(got, ref.to_host()):
+                bad = np.argwhere(got != ref.to_host())
+                print(f"MISMATCH prologue case {case}: {len(bad)} elements, first {bad[:4].tolist()}", flush=True)
+                os._exit(3)
+            for h in (fw, fs, fb, ref):
+                h.free()
+        dist.barrier()
+        sb.free()
+        for h in (bx, bw, bs, bb):
+            h.free()
     ctx.sync()
     dist.barrier()
     if rank == 0:
-        print(f"SYMM_RANKS_OK world={world} cases={len(SHAPES)} batches={len(BATCHES)}", flush=True)
+        print(f"SYMM_RANKS_OK world={world} cases={len(SHAPES)} batches={len(BATCHES)} prologues={len(PROLOGUES)}", flush=True)
     dist.destroy_process_group()
 
 

@@ -61,7 +61,7 @@ def test_descriptor_and_layout():
 def test_quant_table():
     p = mlx_b200.Plugin(require_gpu=False)
     q = p.quant
-    assert q.magic == P.QUANT_MAGIC and q.version == 6 and q.size == C.sizeof(P.QuantVtbl)
+    assert q.magic == P.QUANT_MAGIC and q.version == 7 and q.size == C.sizeof(P.QuantVtbl)
     getter = p.lib.lux_gpu_cuda_quant_vtbl()
     assert C.addressof(getter.contents) == p.vtbl._reserved[0]
     for name, _ in P.QuantVtbl._fields_[4:]:
@@ -96,6 +96,7 @@ def test_null_arguments_are_errors_not_crashes():
     assert q.symm_buffer(None) is None
     assert q.qmatmul_sharded_push(None, None, None, None, None, 1, 64, 16, 4, 64, 2) == P.ERR_INVALID
     assert q.qmatmul_sharded_push_batch(None, 1, None, None, None, None, None, None, 64, 16, 4, 64, 2) == P.ERR_INVALID
+    assert q.qmatmul_sharded_push_pro(None, None, None, None, None, 1, 64, 16, 4, 64, 2, P.PRO_SUM3, 192, 0.0) == P.ERR_INVALID
     q.symm_free(None)
     v.buffer_free(None, None)
     v.destroy_context(None)
