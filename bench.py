@@ -1001,15 +1001,21 @@ def run_ours(args, rank, world):
             y_all_handle, y_symm_handle = _h(y_all), None
         else:
             assert [b_off[it] for it in b_items] == y_off
+            # every rank ends with all outputs whole; the hosts read them back ONCE between them: rank r its 1/world
+            # share of the result buffer (a view into the symmetric buffer), not every rank everything
             y_all, y_views = None, []
-            y_all_handle, y_symm_handle = _h(symm_all.buffer), _h(symm_all)
+            share = (yo // world) & ~255
+            share_off = rank * share
+            share_len = share if rank < world - 1 else yo - share_off
+            share_view = ctx.wrap(symm_all.buffer.device_ptr + share_off, share_len)
+            y_all_handle, y_symm_handle = _h(share_view), _h(symm_all)
         arr = lambda hs: (C.c_void_p * nb)(*hs)
         keep = {"x": arr([_h(v) for v in x_views]), "wq": arr([_h(layers[r][0]) for M, r in b_items]),
                 "scales": arr([_h(layers[r][1]) for M, r in b_items]), "biases": arr([_h(layers[r][2]) for M, r in b_items]),
                 "y": arr([_h(v) for v in y_views]) if y_views else None, "y_offset": (C.c_size_t * nb)(*y_off),
                 "M": (C.c_int * nb)(*[M for M, r in b_items])}
         adr = lambda a: C.cast(a, C.c_void_p).value if a is not None else None
-        bt = Batch(_h(x_all), x_all_pin.ctypes.data, xo, y_all_handle, y_all_pin.ctypes.data, yo, nb, adr(keep["x"]), adr(keep["wq"]),
+        bt = Batch(_h(x_all), x_all_pin.ctypes.data, xo, y_all_handle, y_all_pin.ctypes.data, yo if world == 1 else share_len, nb, adr(keep["x"]), adr(keep["wq"]),
                    adr(keep["scales"]), adr(keep["biases"]), adr(keep["y"]), adr(keep["y_offset"]), adr(keep["M"]), y_symm_handle,
                    K_DEC, N_DEC, BITS, GROUP, BF16)
         drv.lux_bench_e2e_batch.restype = C.c_int
@@ -1076,13 +1082,31 @@ def run_ours(args, rank, world):
                       "how": "one copy in, one qmatmul" + ("_sharded_push" if world > 1 else "") + ", one blocking copy out per matmul"}
         e2e_batch_step()
         bad = []
-        for y_back in [e2e_batch[7]] + ([e2e_two[7]] if e2e_two is not None else []):
-            for it in ((1, 0), (8, R_SETS - 1), (16, R_SETS // 2)):
-                i = b_items.index(it)
-                o, cnt = e2e_batch[1]["y_offset"][i] // 2, it[0] * n_total
-                if not np.array_equal(np.asarray(y_back[o:o + cnt]).reshape(it[0], n_total), item_host(it)):
-                    bad.append(it)
-        e2e_checked = f"FAILED: outputs {bad} read back differ" if bad else "three outputs as read back to the host bit-identical to the batched sweep's"
+        if world == 1:
+            for y_back in [e2e_batch[7]] + ([e2e_two[7]] if e2e_two is not None else []):
+                for it in ((1, 0), (8, R_SETS - 1), (16, R_SETS // 2)):
+                    i = b_items.index(it)
+                    o, cnt = e2e_batch[1]["y_offset"][i] // 2, it[0] * n_total
+                    if not np.array_equal(np.asarray(y_back[o:o + cnt]).reshape(it[0], n_total), item_host(it)):
+                        bad.append(it)
+            e2e_checked = f"FAILED: outputs {bad} read back differ" if bad else "three outputs as read back to the host bit-identical to the batched sweep's"
+        else:
+            # this rank's share as read back against the same bytes of its result buffer, and item (M=16, middle set) of that
+            # buffer against the single sharded call (all ranks make the call)
+            flat = symm_all.buffer.to_host((symm_all.buffer.nbytes,), np.uint8)
+            if not np.array_equal(np.asarray(e2e_batch[7]).view(np.uint8)[:share_len], flat[share_off:share_off + share_len]):
+                bad.append(f"share of rank {rank}")
+            it = (16, R_SETS // 2)
+            launch(*it)
+            if not np.array_equal(item_host(it), y_dev[it[0]].to_host((it[0], n_total), np.uint16)):
+                bad.append(it)
+            import torch
+            t = torch.tensor([len(bad)], dtype=torch.int64, device="cuda")
+            dist.all_reduce(t)
+            if int(t.item()) and not bad:
+                bad = ["(on another rank)"]
+            e2e_checked = (f"FAILED: {bad} read back differ" if bad else
+                           "every rank's share as read back bit-identical to its result buffer, whose items are the single sharded calls'")
         if bad:
             print(e2e_checked, file=sys.stderr, flush=True)
         e2e_one = None
@@ -1095,7 +1119,7 @@ def run_ours(args, rank, world):
         e2e_calls = 0
         ms_e2e = timed(lambda: [e2e_batch_step() for _ in range(e2e_steps)], 4, 5)
         e2e_value = sweep_bytes * e2e_reps * e2e_steps / ms_e2e / 1e6
-    h2d = sum(M * K_DEC * 2 for M in M_SWEEP) * R_SETS * e2e_reps
+    h2d = sum(M * K_DEC * 2 for M in M_SWEEP) * R_SETS * e2e_reps * world  # summed over the ranks (x is replicated: every rank copies it in)
     d2h = sum(M * n_total * 2 for M in M_SWEEP) * R_SETS * e2e_reps
 
     peaks, which = measured_peaks()
@@ -1176,7 +1200,9 @@ def run_ours(args, rank, world):
                 "driver": "python" if e2e_native is None else "C host loop (bench_e2e.c) over the plugin's entry points",
                 "note": ("per sweep of 48 independent matmuls, pinned host buffers: ONE buffer_copy_from_host_async of every item's x, ONE "
                          + ("qmatmul_batch" if world == 1 else "qmatmul_sharded_push_batch") + " call, ONE blocking buffer_copy_to_host of "
-                         "every item's y; weights stay resident like the core's tensors (src/gpu_core.cpp:47-76)"
+                         + ("every item's y" if world == 1 else f"this rank's 1/{world} share of the result buffer (every rank ends with all outputs "
+                            "whole; the hosts read them back once between them; both byte counts are summed over the ranks)")
+                         + "; weights stay resident like the core's tensors (src/gpu_core.cpp:47-76)"
                          + ("; the host keeps two contexts (streams) and reads sweep r-1 back while sweep r computes" if e2e_two is not None else ""))
                         if e2e_single else
                         "per call, pinned host buffers: buffer_copy_from_host_async(x) + qmatmul + buffer_copy_to_host(y, blocking); weights stay resident "
