@@ -818,7 +818,29 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_batch_kernel(const __grid_con
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int ci = blockIdx.x;
-    const int rt_lo = (int)((long long)p.n_rt * ci / p.chunks), rt_hi = (int)((long long)p.n_rt * (ci + 1) / p.chunks);
+    // The row tiles are dealt out in p.chunks ranges of floor or ceil(n_rt / chunks) tiles, range c = [n_rt*c/chunks,
+    // n_rt*(c+1)/chunks).  This CTA takes range (blockIdx.x + i) mod chunks of matmul i: nothing synchronises the CTAs
+    // between matmuls, so what counts is a CTA's total over the launch, and rotating the ranges evens out the one
+    // tile by which they differ (4 or 5 tiles at 688 tiles on 148 SMs: 7 % between the longest and the average).
+    // A range follows from the one before by additions (q, rem = n_rt / chunks, n_rt % chunks; acc = rem*(c+1) mod chunks).
+    const int rt_q = p.n_rt / p.chunks, rt_rem = p.n_rt % p.chunks;
+    auto next_range = [&](int& c, int& lo, int& hi, int& acc) {
+        if (++c == p.chunks) {
+            c = 0;
+            lo = 0;
+            hi = rt_q;
+            acc = rt_rem;
+        } else {
+            lo = hi;
+            acc += rt_rem;
+            const int e = acc >= p.chunks ? 1 : 0;
+            acc -= e ? p.chunks : 0;
+            hi = lo + rt_q + e;
+        }
+    };
+    int rt_c = ci, rt_lo = (int)((long long)p.n_rt * ci / p.chunks), rt_hi = (int)((long long)p.n_rt * (ci + 1) / p.chunks);
+    int rt_acc = (int)(((long long)rt_rem * (ci + 1)) % p.chunks);
+    int f_c = rt_c, f_lo = rt_lo, f_hi = rt_hi, f_acc = rt_acc;  // the same for the matmul whose weights are being fetched
     const int kb_lo = 0, kb_hi = p.nkb;
     const int nkl = kb_hi - kb_lo;
     const int tb = p.tb;
@@ -868,14 +890,15 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_batch_kernel(const __grid_con
             else cp_async4(f_dst + 2048, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(f_sb) & ~uintptr_t(3)));  // a lone scale travels with its neighbour
             // on to the task after it
             f_dst = f_dst + kStageBytes == ring_lo + D * kStageBytes ? ring_lo : f_dst + kStageBytes;
-            if (++f_rt == min(f_b0 + tb, rt_hi)) {  // next run: next k-block of the batch, else first k-block of the next batch
+            if (++f_rt == min(f_b0 + tb, f_hi)) {  // next run: next k-block of the batch, else first k-block of the next batch
                 f_kb += kWarps;
                 if (f_kb >= kb_hi) {
                     f_kb = kb_lo + warp;
                     f_b0 += tb;
                 }
-                if (f_b0 >= rt_hi && ++f_pi < p.n_items) {  // on to the next matmul: same tiles, its weights
-                    f_b0 = rt_lo;
+                if (f_b0 >= f_hi && ++f_pi < p.n_items) {  // on to the next matmul: the next range of tiles, its weights
+                    next_range(f_c, f_lo, f_hi, f_acc);
+                    f_b0 = f_lo;
                     wbase = reinterpret_cast<const unsigned char*>(p.items[f_pi].wq) + t * 16;
                     sb_src = lane < 16 ? p.items[f_pi].scales : p.items[f_pi].biases;
                 }
@@ -910,6 +933,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_batch_kernel(const __grid_con
     uint32_t sboff[2][2];      // byte offsets of this lane's scales inside a stage, by row half r and piece h
 #pragma unroll 1
     for (int pi = 0; pi < p.n_items; pi++) {
+    if (pi) next_range(rt_c, rt_lo, rt_hi, rt_acc);
     const __nv_bfloat16* x_cur = p.items[pi].x;
     void* y_cur = p.items[pi].y;
     const int M_cur = p.items[pi].M;
