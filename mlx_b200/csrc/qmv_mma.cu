@@ -804,14 +804,24 @@ __device__ __forceinline__ void store_tile_item(void* y, int M, int N, int ld, i
 // written by a rank's last CTA to finish -- behind a system-wide fence, every CTA having fenced its own stores
 // before it counted itself in -- into every peer's flag words; that CTA then waits (bounded) for the peers' done
 // words, so that the launch ends with y whole on this rank and stream order is all a consumer needs.
-template <int BITS, int MT, bool SH>
+//
+// DEEP (M <= 8, at most 8 bytes of scales per row and k-block): five ring stages per warp instead of four, in stages
+// of 2304 bytes (the scales and biases of a row in 8-byte slots instead of 16-byte ones).  Every matmul ends with
+// the block meeting twice around the sum and the store; meanwhile the rings stand full and nothing new is requested.
+// With four tasks in flight per warp instead of three, a matmul's four or five tasks per warp are (nearly) all on
+// their way before the previous matmul's end, so the memory system keeps working through it.
+constexpr int kDeepDepth = 5, kDeepStageBytes = 2048 + 256;
+template <int BITS, int MT, bool SH, bool DEEP>
 __global__ void __launch_bounds__(kThreads, 1) qmv_batch_kernel(const __grid_constant__ BatchParams p) {
     constexpr int XV = BITS == 4 ? 8 : 4;  // x fragments (uint4) per lane per k-block per 8-row block
     constexpr int KB = 1024 / BITS;        // weights per k-block (128 bytes per row)
     constexpr int E4 = MT * 32;            // float4 per partial
-    constexpr int D = ring_depth(MT);      // ring stages of a warp
+    static_assert(!DEEP || MT == 1, "the deep ring is for up to 8 rows of x");
+    constexpr int D = DEEP ? kDeepDepth : ring_depth(MT);       // ring stages of a warp
+    constexpr int kStageBytes = DEEP ? kDeepStageBytes : luxcuda::kStageBytes;
+    constexpr int kSlot = DEEP ? 8 : 16;                         // bytes of a row's scales (and of its biases) in a stage
     extern __shared__ __align__(16) unsigned char smem[];
-    float4* part = reinterpret_cast<float4*>(smem + ring_bytes(MT));   // [tb][nkl][MT][32]; ring: [kWarps][D][kStageBytes]
+    float4* part = reinterpret_cast<float4*>(smem + kWarps * D * kStageBytes);   // [tb][nkl][MT][32]; ring: [kWarps][D][kStageBytes]
     // after the partials (MT == 2): the x fragments of rows 8..15, [warp][fragment][lane]
     uint4* xs = reinterpret_cast<uint4*>(smem + p.xs_off) + (threadIdx.x >> 5) * (XV * 32) + (threadIdx.x & 31);
 
@@ -885,9 +895,10 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_batch_kernel(const __grid_con
             cp_async16(f_dst + 512, f_p0 + 64);
             cp_async16(f_dst + 1024, f_p1);
             cp_async16(f_dst + 1536, f_p1 + 64);
-            if (p.sb_bytes == 16) cp_async16(f_dst + 2048, f_sb);
-            else if (p.sb_bytes == 8) cp_async8(f_dst + 2048, f_sb);
-            else cp_async4(f_dst + 2048, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(f_sb) & ~uintptr_t(3)));  // a lone scale travels with its neighbour
+            const uint32_t sb_dst = f_dst + 2048 - lane * (16 - kSlot);  // (f_dst is this lane's 16-byte slot of the stage)
+            if (!DEEP && p.sb_bytes == 16) cp_async16(sb_dst, f_sb);
+            else if (p.sb_bytes == 8) cp_async8(sb_dst, f_sb);
+            else cp_async4(sb_dst, reinterpret_cast<const void*>(reinterpret_cast<uintptr_t>(f_sb) & ~uintptr_t(3)));  // a lone scale travels with its neighbour
             // on to the task after it
             f_dst = f_dst + kStageBytes == ring_lo + D * kStageBytes ? ring_lo : f_dst + kStageBytes;
             if (++f_rt == min(f_b0 + tb, f_hi)) {  // next run: next k-block of the batch, else first k-block of the next batch
@@ -959,7 +970,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_batch_kernel(const __grid_con
                     const int par = p.sb_bytes == 2 ? ((slot * gpr + kb) & 1) : 0;
 #pragma unroll
                     for (int h = 0; h < 2; h++)
-                        sboff[r][h] = 2048 - lane * 16 + slot * 16 + ((((h * (KB / 2) + t * (KB / 8)) >> p.gshift) + par) << 1);
+                        sboff[r][h] = 2048 - lane * 16 + slot * kSlot + ((((h * (KB / 2) + t * (KB / 8)) >> p.gshift) + par) << 1);
                 }
                 float4* dstp = part + (kb - kb_lo) * E4 + lane;
 #pragma unroll 1
@@ -977,7 +988,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_batch_kernel(const __grid_con
                                          : "=r"(w[r][h].x), "=r"(w[r][h].y), "=r"(w[r][h].z), "=r"(w[r][h].w)
                                          : "r"(src_c + (r * 2 + h) * 512));
                             asm volatile("ld.shared.u16 %0, [%1];" : "=r"(s[r][h]) : "r"(src_c + sboff[r][h]));
-                            asm volatile("ld.shared.u16 %0, [%1+256];" : "=r"(b[r][h]) : "r"(src_c + sboff[r][h]));
+                            asm volatile("ld.shared.u16 %0, [%1+%2];" : "=r"(b[r][h]) : "r"(src_c + sboff[r][h]), "n"(16 * kSlot));
                         }
                     const bool fast = scales_fast_ok4(s[0][0], s[0][1], s[1][0], s[1][1]);
                     float acc[MT][2][4];  // two independent accumulation chains per 8-row block of x
@@ -1076,7 +1087,8 @@ struct Plan {
 constexpr size_t kCounterBytes = 4096;
 constexpr int kMaxSplitTiles = (int)(kCounterBytes / sizeof(unsigned int));
 
-bool make_plan(const QmmArgs& a, int sm_count, Plan* pl, bool sharded = false) {
+// ring_override: bytes of the warps' rings when the kernel is not the standard one (the batched kernel's deep ring)
+bool make_plan(const QmmArgs& a, int sm_count, Plan* pl, bool sharded = false, size_t ring_override = 0) {
     if (a.x_dtype != LUX_DTYPE_BFLOAT16 || a.sb_dtype != LUX_DTYPE_BFLOAT16) return false;
     if (a.bits != 4 && a.bits != 8) return false;
     if (a.M < 1 || a.M > 16 || a.N < 1 || sm_count < 1) return false;
@@ -1106,7 +1118,7 @@ bool make_plan(const QmmArgs& a, int sm_count, Plan* pl, bool sharded = false) {
     const int nkl_max = (pl->nkb + ks - 1) / ks;
     const size_t per_tile = (size_t)nkl_max * pl->mt * 512;
     const size_t xs_bytes = pl->mt == 2 ? (size_t)kWarps * (a.bits == 4 ? 8 : 4) * 512 : 0;  // x fragments of rows 8..15
-    const size_t ring = (size_t)ring_bytes(pl->mt);
+    const size_t ring = ring_override ? ring_override : (size_t)ring_bytes(pl->mt);
     const size_t avail = (size_t)kSmemLimit - ring - xs_bytes;
     // column-sharded launches stage every finished tile once more (16 rows of x x 16 columns) for the peers
     const size_t yt_tile = sharded ? (a.y_dtype == LUX_DTYPE_BFLOAT16 ? 512 : 1024) : 0;
@@ -1234,9 +1246,9 @@ cudaError_t launch_qmv_mma(const QmmArgs& a, void* workspace, int sm_count, cuda
 
 // Several matmuls of one shape in one launch (qmv_batch_kernel).  All items: the shape of items[0] but for M, with
 // M on the same side of 8; bf16; no K split for that shape.  cudaErrorNotSupported otherwise.
-template <int BITS, int MT, bool SH>
+template <int BITS, int MT, bool SH, bool DEEP>
 cudaError_t launch_batch_t(const BatchParams& p, const Plan& pl, cudaStream_t stream) {
-    auto kern = qmv_batch_kernel<BITS, MT, SH>;
+    auto kern = qmv_batch_kernel<BITS, MT, SH, DEEP>;
     static std::atomic<size_t> attr_smem[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1259,6 +1271,15 @@ cudaError_t launch_qmv_batch(const QmmArgs* items, int n, int sm_count, cudaStre
     for (int i = 0; i < n; i++) mmax = std::max(mmax, items[i].M);
     a0.M = mmax;
     if (!make_plan(a0, sm_count, &pl, sh) || pl.ks != 1) return cudaErrorNotSupported;
+    // The deep ring (see the kernel) when a CTA's tiles of a matmul still fit into one batch beside it
+    bool deep = false;
+    if (pl.mt == 1 && pl.sb_bytes <= 8 && !getenv("LUXCUDA_QMV_BATCH_NO_DEEP")) {
+        Plan dp;
+        if (make_plan(a0, sm_count, &dp, sh, (size_t)kWarps * kDeepDepth * kDeepStageBytes) && dp.ks == 1 && dp.tb >= pl.tb) {
+            pl = dp;
+            deep = true;
+        }
+    }
     BatchParams p;
     p.ld = a0.N; p.col0 = 0; p.yt_off = pl.yt_off;
     p.error = nullptr;
@@ -1290,12 +1311,14 @@ cudaError_t launch_qmv_batch(const QmmArgs* items, int n, int sm_count, cudaStre
     }
     if (a0.bits == 4) {
         if (name) *name = sh ? (pl.mt == 1 ? "qmv_batch<4,m8,push>" : "qmv_batch<4,m16,push>") : (pl.mt == 1 ? "qmv_batch<4,m8>" : "qmv_batch<4,m16>");
-        if (sh) return pl.mt == 1 ? launch_batch_t<4, 1, true>(p, pl, stream) : launch_batch_t<4, 2, true>(p, pl, stream);
-        return pl.mt == 1 ? launch_batch_t<4, 1, false>(p, pl, stream) : launch_batch_t<4, 2, false>(p, pl, stream);
+        if (deep) return sh ? launch_batch_t<4, 1, true, true>(p, pl, stream) : launch_batch_t<4, 1, false, true>(p, pl, stream);
+        if (sh) return pl.mt == 1 ? launch_batch_t<4, 1, true, false>(p, pl, stream) : launch_batch_t<4, 2, true, false>(p, pl, stream);
+        return pl.mt == 1 ? launch_batch_t<4, 1, false, false>(p, pl, stream) : launch_batch_t<4, 2, false, false>(p, pl, stream);
     }
     if (name) *name = sh ? (pl.mt == 1 ? "qmv_batch<8,m8,push>" : "qmv_batch<8,m16,push>") : (pl.mt == 1 ? "qmv_batch<8,m8>" : "qmv_batch<8,m16>");
-    if (sh) return pl.mt == 1 ? launch_batch_t<8, 1, true>(p, pl, stream) : launch_batch_t<8, 2, true>(p, pl, stream);
-    return pl.mt == 1 ? launch_batch_t<8, 1, false>(p, pl, stream) : launch_batch_t<8, 2, false>(p, pl, stream);
+    if (deep) return sh ? launch_batch_t<8, 1, true, true>(p, pl, stream) : launch_batch_t<8, 1, false, true>(p, pl, stream);
+    if (sh) return pl.mt == 1 ? launch_batch_t<8, 1, true, false>(p, pl, stream) : launch_batch_t<8, 2, true, false>(p, pl, stream);
+    return pl.mt == 1 ? launch_batch_t<8, 1, false, false>(p, pl, stream) : launch_batch_t<8, 2, false, false>(p, pl, stream);
 }
 
 // ---------------------------------------------------------------------------------

@@ -268,7 +268,12 @@ def test_scale_extremes_bit_exact(ctx, oracle, bits, group):
 
 
 @pytest.mark.parametrize("K,N,bits,group,Ms", [(4096, 1200, 4, 64, [1, 4, 8, 16, 3, 12, 8, 1]), (2048, 528, 8, 128, [2, 16, 16, 7]),
-                                                  (1024, 100, 4, 32, [5]), (8192, 64, 4, 64, [8, 1, 16])])
+                                                  (1024, 100, 4, 32, [5]), (8192, 64, 4, 64, [8, 1, 16]),
+                                                  # more matmuls than CTAs (the CTAs' tile ranges rotate from one matmul to the
+                                                  # next and wrap around), 4 bytes of scales per row and k-block
+                                                  (2048, 272, 4, 128, [8, 1, 3, 5, 2, 7, 4, 6, 8, 1, 2, 3, 4, 5, 6, 7, 8, 1, 2, 3]),
+                                                  (1024, 304, 8, 32, [1, 8, 4]), (2048, 2400, 8, 64, [6, 2, 16, 9, 1]),
+                                                  (4096, 11008, 4, 64, [1, 8, 8, 3, 16])])
 def test_batch_equals_single_calls(ctx, oracle, K, N, bits, group, Ms):
     """qmatmul_batch runs independent decode matmuls of one shape in as few persistent launches as their M allow (the
     last shape is one whose K the decode kernel splits over CTAs: the call then runs them one by one).  Either way
