@@ -40,7 +40,7 @@ import numpy as np
 # dram__bytes_read.sum + dram__bytes_write.sum of one qmv_mma launch (M=1) of this workload, from an ncu capture
 # of `bench.py --kernel-only --no-graph` (counters cannot be read inside the timed run)
 NCU_TRAFFIC_BYTES = 25461632.0
-NCU_TRAFFIC_BYTES_BATCH = 920277760.0  # one qmv_batch<4,m8> launch of the sweep (ncu, dram read + write)
+NCU_TRAFFIC_BYTES_BATCH = 919669248.0  # one qmv_batch<4,m8> launch of the sweep (ncu, dram read + write)
 SWEEPS_PER_GRAPH = 5  # sweeps (of 4 x 12 launches) recorded in the CUDA graph the timed step replays
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
