@@ -157,10 +157,58 @@ def main():
         sb.free()
         for h in (bx, bw, bs, bb):
             h.free()
+    # The batched call again with the ranks drifting apart: no barrier between the calls, two alternating sets of
+    # activations (so that a store that came late or early would show), and EVERY rank checks the whole buffer
+    # after EVERY call against the unsharded matmuls it has computed itself.
+    import time
+    K, nl, bits, group = 4096, 1376, 4, 64
+    N = nl * world
+    Ms = [1, 8, 4, 16, 3, 16, 8, 1, 12, 5, 2, 7]
+    layers = [O.make_layer(N, K, bits, group, O.BF16, config_id=11, layer=i) for i in range(len(Ms))]
+    sl = slice(rank * nl, (rank + 1) * nl)
+    loc = [(ctx.upload(l[0][sl]), ctx.upload(l[1][sl]), ctx.upload(l[2][sl])) for l in layers]
+    xsets = [[ctx.upload(O.make_x(M, K, O.BF16, config_id=11, tag=10 * v + i)) for i, M in enumerate(Ms)] for v in range(2)]
+    offs, total = [], 0
+    for M in Ms:
+        offs.append(total)
+        total += M * N * 2
+    want = []
+    for v in range(2):
+        flat = np.zeros(total // 2, np.uint16)
+        for i, M in enumerate(Ms):
+            fw, fs, fb = ctx.upload(layers[i][0]), ctx.upload(layers[i][1]), ctx.upload(layers[i][2])
+            y = ctx.empty((M, N), np.uint16)
+            ctx.qmatmul(xsets[v][i], fw, fs, fb, y, M, K, N, bits, group, BF16, BF16, BF16)
+            flat[offs[i] // 2: offs[i] // 2 + M * N] = y.to_host().reshape(-1)
+            for h in (fw, fs, fb, y):
+                h.free()
+        want.append(flat)
+    sb = SymmBuffer(ctx, rank, world, (total // 2,), np.uint16)
+    mine = torch.tensor(list(sb.export()), dtype=torch.uint8, device="cuda")
+    every = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(every, mine)
+    sb.attach([bytes(t.cpu().tolist()) for t in every])
+    dist.barrier()
+    rng = np.random.default_rng(rank)
+    bad = 0
+    for it in range(60):
+        v = it & 1
+        sb.qmatmul_batch(xsets[v], [l[0] for l in loc], [l[1] for l in loc], [l[2] for l in loc], offs, Ms, K, nl, bits, group, BF16)
+        if it % 3 == rank % 3:
+            time.sleep(float(rng.uniform(0, 0.002)))
+        if not np.array_equal(sb.to_host(), want[v]):  # (synchronises this rank only)
+            bad += 1
+    t = torch.tensor([bad], dtype=torch.int64, device="cuda")
+    dist.all_reduce(t)
     ctx.sync()
     dist.barrier()
+    if int(t.item()):
+        if rank == 0:
+            print(f"MISMATCH drifting ranks: {int(t.item())} calls left a buffer that differs", flush=True)
+        os._exit(3)
+    sb.free()
     if rank == 0:
-        print(f"SYMM_RANKS_OK world={world} cases={len(SHAPES)} batches={len(BATCHES)} prologues={len(PROLOGUES)}", flush=True)
+        print(f"SYMM_RANKS_OK world={world} cases={len(SHAPES)} batches={len(BATCHES)} prologues={len(PROLOGUES)} drifting_calls=60", flush=True)
     dist.destroy_process_group()
 
 
