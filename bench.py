@@ -776,11 +776,10 @@ def run_ours(args, rank, world):
                 return b_y[it].to_host()
         else:
             import torch
-            b_off, rows = {}, 0
-            for it in b_items:
-                b_off[it] = rows * n_total * 2
-                rows += it[0]
-            symm_all = mlx_b200.plugin.SymmBuffer(ctx, rank, world, (rows, n_total), np.uint16)
+            from mlx_b200.shard import batch_layout
+            offs, total_bytes_y = batch_layout([M for M, r in b_items], n_total)
+            b_off = dict(zip(b_items, offs))
+            symm_all = mlx_b200.plugin.SymmBuffer(ctx, rank, world, (total_bytes_y // 2,), np.uint16)
             mine = torch.tensor(list(symm_all.export()), dtype=torch.uint8, device="cuda")
             every = [torch.empty_like(mine) for _ in range(world)]
             dist.all_gather(every, mine)
@@ -981,12 +980,9 @@ def run_ours(args, rank, world):
                         ("y_offset", C.c_void_p), ("M", C.c_void_p), ("y_symm", C.c_void_p),
                         ("K", C.c_int32), ("N", C.c_int32), ("bits", C.c_int32), ("group", C.c_int32), ("dtype", C.c_int32)]
         nb = len(b_items)
-        x_off, y_off, xo, yo = [], [], 0, 0
-        for M, r in b_items:
-            x_off.append(xo)
-            y_off.append(yo)
-            xo += M * K_DEC * 2
-            yo += M * n_total * 2
+        from mlx_b200.shard import batch_layout, readback_share
+        x_off, xo = batch_layout([M for M, r in b_items], K_DEC)
+        y_off, yo = batch_layout([M for M, r in b_items], n_total)
         x_all = ctx.empty((xo // 2,), np.uint16)
         x_all_pin = ctx.pinned_array((xo // 2,), np.uint16)
         for (M, r), o in zip(b_items, x_off):
@@ -1004,9 +1000,7 @@ def run_ours(args, rank, world):
             # every rank ends with all outputs whole; the hosts read them back ONCE between them: rank r its 1/world
             # share of the result buffer (a view into the symmetric buffer), not every rank everything
             y_all, y_views = None, []
-            share = (yo // world) & ~255
-            share_off = rank * share
-            share_len = share if rank < world - 1 else yo - share_off
+            share_off, share_len = readback_share(rank, world, yo)
             share_view = ctx.wrap(symm_all.buffer.device_ptr + share_off, share_len)
             y_all_handle, y_symm_handle = _h(share_view), _h(symm_all)
         arr = lambda hs: (C.c_void_p * nb)(*hs)

@@ -17,6 +17,7 @@ import mlx_b200  # noqa: E402
 import oracle as O  # noqa: E402
 from mlx_b200 import BF16  # noqa: E402
 from mlx_b200.plugin import SymmBuffer  # noqa: E402
+from mlx_b200.shard import batch_layout  # noqa: E402
 
 SHAPES = [  # (M, K, N_local, bits, group)
     (8, 11008, 512, 4, 64),    # split-K
@@ -89,10 +90,7 @@ def main():
         xs = [O.make_x(M, K, O.BF16, config_id=9, tag=10 * case + i) for i, M in enumerate(Ms)]
         sl = slice(rank * nl, (rank + 1) * nl)
         up = [(ctx.upload(x), ctx.upload(l[0][sl]), ctx.upload(l[1][sl]), ctx.upload(l[2][sl])) for x, l in zip(xs, layers)]
-        offs, total = [], 0
-        for M in Ms:
-            offs.append(total)
-            total += M * N * 2
+        offs, total = batch_layout(Ms, N)
         sb = SymmBuffer(ctx, rank, world, (total // 2,), np.uint16)
         mine = torch.tensor(list(sb.export()), dtype=torch.uint8, device="cuda")
         every = [torch.empty_like(mine) for _ in range(world)]
@@ -168,10 +166,7 @@ def main():
     sl = slice(rank * nl, (rank + 1) * nl)
     loc = [(ctx.upload(l[0][sl]), ctx.upload(l[1][sl]), ctx.upload(l[2][sl])) for l in layers]
     xsets = [[ctx.upload(O.make_x(M, K, O.BF16, config_id=11, tag=10 * v + i)) for i, M in enumerate(Ms)] for v in range(2)]
-    offs, total = [], 0
-    for M in Ms:
-        offs.append(total)
-        total += M * N * 2
+    offs, total = batch_layout(Ms, N)
     want = []
     for v in range(2):
         flat = np.zeros(total // 2, np.uint16)
