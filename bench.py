@@ -126,7 +126,7 @@ class ClockSampler:
 # ---------------------------------------------------------------------------
 # CPU baseline (the oracle; test infrastructure used here only as the baseline)
 # ---------------------------------------------------------------------------
-def cpu_baseline(budget_s=12.0):
+def cpu_baseline(limit_s=12.0):
     import oracle as O
     wq, s, b = O.make_layer(N_DEC, K_DEC, BITS, GROUP, O.BF16, config_id=2)
     xs = {M: O.make_x(M, K_DEC, O.BF16, config_id=2, tag=M) for M in M_SWEEP}
@@ -139,7 +139,7 @@ def cpu_baseline(budget_s=12.0):
             nbytes += alg_bytes(M)
         sweeps += 1
         dt = time.perf_counter() - t0
-        if dt > budget_s or sweeps >= 50:
+        if dt > limit_s or sweeps >= 50:
             break
     return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
             "sample": f"{sweeps} sweep(s) of M in {list(M_SWEEP)} over one 11008x4096 4-bit layer, "
