@@ -2,7 +2,8 @@
 
 The plugin is compiled against the reference's UNCHANGED ABI header
 (include/lux/gpu/backend_plugin.h), taken where it lies in the reference tree
-(``LUX_REFERENCE_INCLUDE``, else a directory ``reference`` beside this repository); the header is not
+(``LUX_REFERENCE_INCLUDE`` or ``LUX_REFERENCE_ROOT``, else a directory ``reference`` beside this repository or
+beside one of the directories above it); the header is not
 copied into this repository.  On a machine without the reference tree the
 prebuilt library is used as is.
 """
@@ -24,8 +25,29 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "--expt-relaxed-constexpr"]
 
 
+def reference_root():
+    """The reference tree: ``LUX_REFERENCE_ROOT``, else a directory ``reference`` beside this repository or beside
+    one of the directories above it (a checkout of the repository further down still finds it)."""
+    env = os.environ.get("LUX_REFERENCE_ROOT")
+    if env:
+        return env if os.path.isdir(env) else None
+    d = os.path.realpath(ROOT)
+    while True:
+        parent = os.path.dirname(d)
+        if parent == d:
+            return None
+        cand = os.path.join(parent, "reference")
+        if os.path.exists(os.path.join(cand, "include", "lux", "gpu", "backend_plugin.h")):
+            return cand
+        d = parent
+
+
 def reference_include():
-    for cand in (os.environ.get("LUX_REFERENCE_INCLUDE"), os.path.join(os.path.dirname(os.path.realpath(ROOT)), "reference", "include")):
+    cands = [os.environ.get("LUX_REFERENCE_INCLUDE")]
+    root = reference_root()
+    if root:
+        cands.append(os.path.join(root, "include"))
+    for cand in cands:
         if cand and os.path.exists(os.path.join(cand, "lux", "gpu", "backend_plugin.h")):
             return cand
     return None

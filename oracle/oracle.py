@@ -27,12 +27,29 @@ __all__ = [
 TOL = {BF16: 1e-2, F32: 1e-4}
 
 
+def _reference_root():
+    """The reference tree: $REF, else a directory ``reference`` beside this repository or beside a directory above it."""
+    env = os.environ.get("REF")
+    if env:
+        return env if os.path.isdir(env) else None
+    d = os.path.dirname(os.path.realpath(_HERE))
+    while True:
+        parent = os.path.dirname(d)
+        if parent == d:
+            return None
+        cand = os.path.join(parent, "reference")
+        if os.path.exists(os.path.join(cand, "src", "gpu_core.cpp")):
+            return cand
+        d = parent
+
+
 def build(force=False):
     """Compile the oracle (and the reference core when its tree is present)."""
     src = os.path.join(_HERE, "qmm_oracle.c")
     stale = (not os.path.exists(_LIB_PATH)) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
-    if force or stale or (os.path.isdir(os.environ.get("REF", os.path.join(os.path.dirname(os.path.dirname(os.path.realpath(_HERE))), "reference"))) and not os.path.exists(os.path.join(_HERE, "_ref", "test_gpu_core"))):
-        subprocess.run(["make", "-C", _HERE, "all"], check=True, stdout=subprocess.DEVNULL)
+    ref = _reference_root()
+    if force or stale or (ref and not os.path.exists(os.path.join(_HERE, "_ref", "test_gpu_core"))):
+        subprocess.run(["make", "-C", _HERE, "all"] + ([f"REF={ref}"] if ref else []), check=True, stdout=subprocess.DEVNULL)
     return _LIB_PATH
 
 
