@@ -926,7 +926,7 @@ def run_ours(args, rank, world):
     # e2e: host buffers in, host buffers out, through the base vtable copies (blocking, reference semantics)
     e2e_calls = 0
     e2e_steps = max(1, min(args.steps, 5))
-    e2e_reps = max(1, min(args.reps, 20))
+    e2e_reps = max(1, args.reps)  # an end-to-end step is a step of the timed region above: the same sweeps
     # page-locked host buffers on both sides, as a serving host keeps them
     x_pin, y_pin = {}, {}
     for M in M_SWEEP:
@@ -1189,6 +1189,7 @@ def run_ours(args, rank, world):
         "gemm_sharded": gemm_sharded,
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps, "sweeps_per_step": e2e_reps,
                 **({"matmuls": e2e_calls, "us_per_matmul": ms_e2e * 1e3 / max(1, e2e_calls)} if e2e_single else
                    {"calls": e2e_calls, "us_per_call": ms_e2e * 1e3 / max(1, e2e_calls)}),
                 "driver": "python" if e2e_native is None else "C host loop (bench_e2e.c) over the plugin's entry points",
