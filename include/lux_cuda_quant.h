@@ -228,6 +228,8 @@ typedef struct lux_gpu_quant_vtbl {
                                    LuxBackendDtype y_dtype, int prologue, size_t x_ld, float eps);
 
     /* --- several independent decode matmuls of one shape in one call (version >= 5) ---
+     * (The reference's matmul slot, op_matmul_f32, backend_plugin.h:129, takes one matmul per call and its public
+     * API forwards them one by one, src/gpu_core.cpp:450-474: this entry has no counterpart there.)
      * y[i] = x[i] . dequant(wq[i], scales[i], biases[i])^T for i < n: n layers (or n requests on one layer) of the
      * same K, N, bits, group, bf16, each with its own M[i] <= 16.  The same bits as n calls of qmatmul.  The matmuls
      * run in as few launches as their shapes allow (those with M <= 8 together, those with M > 8 together, up to 48
@@ -241,6 +243,8 @@ typedef struct lux_gpu_quant_vtbl {
                                      LuxBackendDtype y_dtype);
 
     /* --- several independent column-sharded decode matmuls of one shape in one call (version >= 6) ---
+     * (No counterpart in the reference, whose multi-device support ends at create_context(device_index),
+     * backend_plugin.h:84.)
      * qmatmul_batch for a layer whose columns are sharded over ranks: item i's full output y_i[M[i], world*Nl]
      * lies at byte offset y_offset[i] (a multiple of 16; the outputs do not overlap) of the symmetric buffer, on
      * every rank; this rank computes columns [rank*Nl, (rank+1)*Nl) of every item and the kernel stores them
